@@ -1,0 +1,175 @@
+/*
+ * qfg.h - C ABI of the B200 (sm_100a) implementation of the `qwen.fused_gemm` decode path.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, enqueues work on the
+ * CUDA stream it is given and returns a status code; none synchronises, and none of the
+ * *_compute / qfg_argmax_rows calls allocates, copies to the host or calls back, so they can
+ * be captured in a CUDA graph.  Device pointers are raw `void*`; a stream is the
+ * `cudaStream_t` value passed as `void*` (NULL = the legacy default stream).
+ *
+ * The entry points are the operator interface of the reference library
+ * libqwen_fused_gemm_r5.so with the ONNX Runtime types peeled off: a *_create call takes what
+ * the reference reads from node attributes at kernel creation, a *_compute call takes what
+ * the reference reads from its OrtKernelContext.  Each declaration cites the reference
+ * interface it replaces (paths inside the reference project).  The ORT shim
+ * (qwen38_flash_ops_b200/csrc/ort_shim/fused_gemm_ort.cc) maps `RegisterCustomOps`,
+ * domain `qwen.fused_gemm`, onto these calls one to one.
+ *
+ * Element types use the ONNX TensorProto codes the reference switches on.
+ */
+#ifndef QFG_H_
+#define QFG_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define QFG_API __attribute__((visibility("default")))
+#else
+#define QFG_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QFG_MAX_WEIGHTS 4 /* skinny::kMaxSeg, src/fused_gemm/skinny_gemm.cuh:41 */
+#define QFG_MAX_OUTPUTS 8 /* skinny::kMaxOut, src/fused_gemm/skinny_gemm.cuh:39 */
+
+/* Status codes; the values of OK / FAIL / INVALID_ARGUMENT equal OrtErrorCode's, which is what
+ * the reference returns through OrtStatus (src/fused_gemm/fused_gemm.cu:589-591, :836-838). */
+typedef enum qfg_status {
+  QFG_OK = 0,
+  QFG_FAIL = 1,             /* a CUDA call failed; qfg_last_error() holds "<Op>: <cuda string>" */
+  QFG_INVALID_ARGUMENT = 2, /* bad attributes, shapes or element types; nothing was launched */
+  QFG_NOT_IMPLEMENTED = 9
+} qfg_status;
+
+/* ONNX tensor element types accepted on this path. */
+typedef enum qfg_dtype {
+  QFG_FLOAT = 1,
+  QFG_UINT8 = 2,        /* block-16 NVFP4, [K, N * 9 / 16] */
+  QFG_INT64 = 7,
+  QFG_FLOAT16 = 10,
+  QFG_BFLOAT16 = 16,
+  QFG_FLOAT8E4M3FN = 17 /* [K, N] with an optional per-column scale */
+} qfg_dtype;
+
+/* A 2-D weight tensor as the op receives it: `cols` is the stored width (N for BF16 / FP8,
+ * N * 9 / 16 for NVFP4), exactly the shape ORT reports for the input. */
+typedef struct qfg_tensor2d {
+  const void* data; /* device pointer, row-major */
+  int32_t dtype;    /* qfg_dtype */
+  int64_t rows;     /* K */
+  int64_t cols;
+} qfg_tensor2d;
+
+typedef struct qfg_skinny_gemm qfg_skinny_gemm;
+typedef struct qfg_dequant qfg_dequant;
+typedef struct qfg_lmhead qfg_lmhead;
+
+/* Message of the last non-OK status returned on the calling thread ("" if none). */
+QFG_API const char* qfg_last_error(void);
+/* "qfg-b200 <version> sm_100a". */
+QFG_API const char* qfg_version(void);
+
+/* ---------------------------------------------------------------- SkinnyGemm
+ * y_j[..., width_j] = x[..., K] @ W_i[K, N_i] column-sliced over the outputs of weight i.
+ *
+ * Replaces SkinnyGemmKernelState's constructor (src/fused_gemm/fused_gemm.cu:476-501; the
+ * op schema is SkinnyGemmOp, :818-840).  Attributes: `seg_outs` (number of outputs slicing
+ * each weight), `widths` (output widths in order), optional `w_scale` (host floats, the
+ * concatenated per-column scales of the quantised weights, uploaded once here), optional
+ * `trigger` (0 off, 1 = release programmatic-dependent-launch dependents at kernel start,
+ * 2 = after the K loop; a non-zero value is overridden by the environment variable
+ * SKINNY_TRIGGER_FORCE as in the reference, :105-113).  Fails with QFG_INVALID_ARGUMENT
+ * unless 1 <= n_seg <= 4 and sum(seg_outs) == n_widths <= 8. */
+QFG_API int qfg_skinny_gemm_create(const int64_t* seg_outs, int n_seg, const int64_t* widths, int n_widths,
+                           const float* w_scale, size_t n_w_scale, int trigger, qfg_skinny_gemm** out);
+
+/* Replaces SkinnyGemmKernelState::ComputeV2 (src/fused_gemm/fused_gemm.cu:507-592) for every
+ * row count: `m` = product of x's leading dims, `k` = its last dim, x is BF16 [m, k];
+ * `weights[i]` are the variadic weight inputs; `outs[j]` are caller-allocated BF16 [m, width_j]
+ * buffers (ORT allocates them through GetOutput in the reference).  The same checks apply:
+ * weight rows == k, widths add up to N, N % 4 == 0, k even, NVFP4 stored width == N * 9 / 16.
+ * Stricter than the reference where it misreads memory: weights of one call must share one
+ * element type, a BF16/FP8 weight must be 4-byte aligned per row and an NVFP4 weight needs
+ * N % 64 == 0.  Rows are processed eight at a time, so any m >= 1 is accepted; row r of an
+ * m-row call is computed with the arithmetic of the one-row call on that row. */
+QFG_API int qfg_skinny_gemm_compute(const qfg_skinny_gemm* op, const void* x, int64_t m, int64_t k,
+                            const qfg_tensor2d* weights, int n_weights, void* const* outs, int n_outs,
+                            void* stream);
+
+/* Launch options that are not node attributes.  "pdl_wait" = 1 launches the kernel with the
+ * programmatic-stream-serialisation attribute and makes it wait for its predecessor
+ * (griddepcontrol.wait) only after its first weight tiles are in flight.  "plan" pins the
+ * launch geometry ("wn=4,wk=2,ks=1,stages=4,cluster=8,ctas=296"); used by the tuning sweeps. */
+QFG_API int qfg_skinny_gemm_set_option(qfg_skinny_gemm* op, const char* key, const char* value);
+
+/* Writes a one-line description of the launch plan chosen for these shapes into buf. */
+QFG_API int qfg_skinny_gemm_describe(const qfg_skinny_gemm* op, int64_t k, const qfg_tensor2d* weights, int n_weights,
+                             char* buf, size_t buf_len);
+
+/* Diagnostic, needs no device: the launch plan for `nseg` weights of `n[i]` columns, element
+ * type `dtype`, K rows, rows aligned to `row_align` (16, 8 or 4) bytes, on a GPU with `sm_count`
+ * SMs; `spec` (may be NULL) is a "plan" override as above.  No counterpart in the reference, whose
+ * planner is the table at src/fused_gemm/fused_gemm.cu:125-175. */
+QFG_API int qfg_plan_describe(int dtype, int64_t k, const int64_t* n, int nseg, int row_align, int sm_count,
+                              const char* spec, char* buf, size_t buf_len);
+
+/* Replaces ~SkinnyGemmKernelState (src/fused_gemm/fused_gemm.cu:503-505): frees the uploaded scales. */
+QFG_API void qfg_skinny_gemm_destroy(qfg_skinny_gemm* op);
+
+/* ---------------------------------------------------------------- ArgmaxRows
+ * idx[r] = argmax_v x[r, v] with numpy semantics (lowest index on ties, the first NaN wins,
+ * -0 == +0); `val` (may be NULL) receives the maximum as FP32.
+ * Replaces ArgmaxRowsKernelState::ComputeV2 (src/fused_gemm/fused_gemm.cu:735-778) and
+ * skinny::LaunchArgmaxRows (src/fused_gemm/argmax_rows.cuh:192-204).  dtype is BFLOAT16,
+ * FLOAT16 or FLOAT; rows == 0 is a no-op; vocab must be in [1, INT_MAX). */
+QFG_API int qfg_argmax_rows(int dtype, const void* x, int64_t rows, int64_t vocab, int64_t* idx, float* val,
+                    void* stream);
+
+/* ---------------------------------------------------------------- DequantWeightBf16
+ * Replaces DequantWeightBf16KernelState's constructor (src/fused_gemm/fused_gemm.cu:850-884):
+ * attributes `n_cols` (required, multiple of 8), `col_offset` (default 0, multiple of 8),
+ * `widths` (default [n_cols]; positive multiples of 8 that add up to n_cols, at most 8),
+ * optional `w_scale` indexed by output column. */
+QFG_API int qfg_dequant_create(int64_t n_cols, int64_t col_offset, const int64_t* widths, int n_widths,
+                       const float* w_scale, size_t n_w_scale, qfg_dequant** out);
+
+/* Replaces DequantWeightBf16KernelState::ComputeV2 (src/fused_gemm/fused_gemm.cu:890-953):
+ * outs[i] is BF16 [w.rows, widths[i]].  BF16: column-slice copy; FP8: bf16(float(q) * s[col]);
+ * NVFP4: bf16(e2m1 * e4m3_block_scale * s[col]). */
+QFG_API int qfg_dequant_compute(const qfg_dequant* op, const qfg_tensor2d* w, void* const* outs, int n_outs,
+                        void* stream);
+QFG_API void qfg_dequant_destroy(qfg_dequant* op);
+
+/* ---------------------------------------------------------------- fused LM head
+ * SkinnyGemm over one weight followed by ArgmaxRows over the BF16-rounded logits, in one
+ * kernel: the logits are never written unless `logits` is non-NULL.  The reference runs the
+ * two ops back to back (SkinnyGemmOp then ArgmaxRowsOp, src/fused_gemm/fused_gemm.cu:781-840);
+ * this call returns what that chain returns.
+ *
+ * `col_offset` is added to every index, so a rank holding columns [c0, c1) of a sharded
+ * vocabulary reports global indices.  `key` (may be NULL) receives per row a 64-bit word that
+ * orders (value, index) pairs exactly like ArgmaxRows does - larger is better - which is the
+ * payload the N-sharded LM head all-gathers; qfg_lmhead_combine folds the gathered words.
+ *
+ * `workspace` is qfg_lmhead_workspace_bytes() bytes of device memory that must be zero before
+ * the first call; each call leaves it zero again.  Calls that share a workspace must not
+ * overlap on the GPU. */
+QFG_API size_t qfg_lmhead_workspace_bytes(void);
+QFG_API int qfg_lmhead_create(const float* w_scale, size_t n_w_scale, int trigger, qfg_lmhead** out);
+QFG_API int qfg_lmhead_compute(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
+                       int64_t n, int64_t col_offset, void* workspace, int64_t* idx, float* val,
+                       uint64_t* key, void* logits, void* stream);
+QFG_API int qfg_lmhead_set_option(qfg_lmhead* op, const char* key, const char* value);
+QFG_API void qfg_lmhead_destroy(qfg_lmhead* op);
+
+/* Fold `ranks` gathered key rows (keys[rank * m + row]) into idx[row] / val[row]. */
+QFG_API int qfg_lmhead_combine(const uint64_t* keys, int ranks, int64_t m, int64_t* idx, float* val, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QFG_H_ */

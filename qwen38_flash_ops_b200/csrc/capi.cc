@@ -1,0 +1,540 @@
+// Host layer behind the C ABI of include/qfg.h: attribute validation, per-call shape and type
+// checks, segment tables, launch planning and error reporting.  It plays the part of the
+// reference's Ort::CustomOpBase kernel-state structs (src/fused_gemm/fused_gemm.cu:468-593 for
+// SkinnyGemm, :731-779 for ArgmaxRows, :842-954 for DequantWeightBf16) with ORT's tensor and
+// attribute accessors replaced by plain arguments.  Nothing here synchronises, and the compute
+// entry points neither allocate nor copy, so they are legal inside a stream capture.
+#include <cuda_runtime.h>
+
+#include <climits>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "qfg_internal.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int Fail(int code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+
+struct InvalidArgument : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
+int Alignment(const void* base, long long pitch) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(base);
+  for (int v = 16; v >= 4; v >>= 1) {
+    if (a % v == 0 && pitch % v == 0) return v;
+  }
+  return 0;
+}
+
+float* UploadScales(const float* host, size_t n, const char* op) {
+  if (host == nullptr || n == 0) return nullptr;
+  float* dev = nullptr;
+  if (cudaMalloc(&dev, n * sizeof(float)) != cudaSuccess ||
+      cudaMemcpy(dev, host, n * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) {
+    cudaFree(dev);
+    cudaGetLastError();
+    throw std::runtime_error(std::string(op) + ": failed to upload w_scale");
+  }
+  return dev;
+}
+
+// Optional `trigger` attribute; SKINNY_TRIGGER_FORCE=<n> overrides a non-zero value.
+int ResolveTrigger(int attr) {
+  const char* e = std::getenv("SKINNY_TRIGGER_FORCE");
+  return (attr != 0 && e != nullptr) ? std::atoi(e) : attr;
+}
+
+int EnvInt(const char* name, int dflt) {
+  const char* e = std::getenv(name);
+  return e != nullptr ? std::atoi(e) : dflt;
+}
+
+}  // namespace
+
+struct qfg_skinny_gemm {
+  std::vector<int> seg_outs;
+  std::vector<int> widths;
+  int trigger = 0;
+  float* d_w_scale = nullptr;
+  size_t w_scale_len = 0;
+  int pdl_wait = 0;
+  int force_slow = 0;
+  std::string plan_spec;
+};
+
+struct qfg_dequant {
+  int64_t n_cols = 0;
+  int64_t col_offset = 0;
+  std::vector<int> widths;
+  float* d_w_scale = nullptr;
+  size_t w_scale_len = 0;
+};
+
+struct qfg_lmhead {
+  qfg_skinny_gemm gemm;
+};
+
+namespace {
+
+struct Prepared {
+  qfg::GemmParams params;
+  qfg::PlanInput plan_in;
+  int mode = 0;
+};
+
+// Shape / type checks and segment tables of one call (fused_gemm.cu:512-572).  `outs` may be
+// null when only the plan is wanted.
+Prepared Prepare(const qfg_skinny_gemm& op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weights,
+                 int n_weights, void* const* outs, int n_outs, bool need_outs) {
+  const int nseg = static_cast<int>(op.seg_outs.size());
+  if (n_weights != nseg) throw InvalidArgument("SkinnyGemm: input count");
+  if (m < 1) throw InvalidArgument("SkinnyGemm: M must be >= 1");
+  if (k < 1 || k > INT_MAX) throw InvalidArgument("SkinnyGemm: bad K");
+  if (k % 2 != 0) throw InvalidArgument("SkinnyGemm: K must be even");
+  if (need_outs && n_outs != static_cast<int>(op.widths.size())) throw InvalidArgument("SkinnyGemm: output count");
+  if (need_outs && (x == nullptr || reinterpret_cast<uintptr_t>(x) % 4 != 0))
+    throw InvalidArgument("SkinnyGemm: x must be a 4-byte aligned device pointer");
+
+  Prepared pr;
+  qfg::GemmParams& p = pr.params;
+  p.x = static_cast<const uint16_t*>(x);
+  p.K = static_cast<int>(k);
+  p.nseg = nseg;
+  p.trigger = op.trigger;
+  p.pdl_wait = op.pdl_wait;
+  p.force_slow = op.force_slow;
+  int o = 0;
+  size_t scale_off = 0;
+  int row_align = 16;
+  for (int s = 0; s < nseg; ++s) {
+    const qfg_tensor2d& w = weights[s];
+    if (w.rows != k) throw InvalidArgument("SkinnyGemm: weight shape");
+    qfg::Segment& sg = p.seg[s];
+    sg.out_begin = o;
+    long long begin = 0;
+    for (int i = 0; i < op.seg_outs[s]; ++i, ++o) {
+      if (op.widths[o] < 1) throw InvalidArgument("SkinnyGemm: widths must be positive");
+      p.out[o] = need_outs ? static_cast<uint16_t*>(outs[o]) : nullptr;
+      if (need_outs && outs[o] == nullptr) throw InvalidArgument("SkinnyGemm: null output");
+      p.col_begin[o] = static_cast<int>(begin);
+      p.width[o] = op.widths[o];
+      begin += op.widths[o];
+    }
+    sg.out_end = o;
+    if (begin > INT_MAX) throw InvalidArgument("SkinnyGemm: N too large");
+    sg.n = static_cast<int>(begin);
+    int mode;
+    if (w.dtype == QFG_BFLOAT16) {
+      if (w.cols != begin) throw InvalidArgument("SkinnyGemm: widths do not add up to N");
+      mode = qfg::kBf16;
+      sg.pitch = 2 * begin;
+    } else if (w.dtype == QFG_FLOAT8E4M3FN) {
+      if (w.cols != begin) throw InvalidArgument("SkinnyGemm: FP8 widths do not add up to N");
+      mode = qfg::kFp8;
+      sg.pitch = begin;
+    } else if (w.dtype == QFG_UINT8) {
+      if (begin % 16 != 0 || w.cols != (begin * 9) / 16)
+        throw InvalidArgument("SkinnyGemm: NVFP4 packed width must equal N * 9 / 16");
+      if (begin % 64 != 0) throw InvalidArgument("SkinnyGemm: NVFP4 needs N % 64 == 0 (4-byte aligned rows)");
+      mode = qfg::kNvfp4;
+      sg.pitch = (begin * 9) / 16;
+    } else {
+      throw InvalidArgument("SkinnyGemm: unsupported weight element type");
+    }
+    if (mode != qfg::kBf16 && op.d_w_scale != nullptr && scale_off + static_cast<size_t>(begin) <= op.w_scale_len) {
+      sg.w_scale = op.d_w_scale + scale_off;
+      scale_off += static_cast<size_t>(begin);
+    }
+    if (sg.n % 4 != 0) throw InvalidArgument("SkinnyGemm: N must be a multiple of 4");
+    if (s == 0) {
+      pr.mode = mode;
+    } else if (mode != pr.mode) {
+      throw InvalidArgument("SkinnyGemm: all weights of one call must share one element type");
+    }
+    sg.w = static_cast<const uint8_t*>(w.data);
+    sg.total_bytes = sg.pitch * k;
+    if (need_outs) {
+      if (w.data == nullptr) throw InvalidArgument("SkinnyGemm: null weight");
+      const int a = Alignment(w.data, sg.pitch);
+      if (a == 0) throw InvalidArgument("SkinnyGemm: weight rows must be 4-byte aligned");
+      row_align = std::min(row_align, a);
+    } else {
+      row_align = std::min(row_align, Alignment(nullptr, sg.pitch) == 0 ? 4 : Alignment(nullptr, sg.pitch));
+    }
+    pr.plan_in.n[s] = sg.n;
+  }
+  for (int s = 0; s < nseg; ++s) {
+    p.seg[s].vec = row_align;
+    p.seg[s].svec = row_align;
+  }
+  pr.plan_in.K = p.K;
+  pr.plan_in.nseg = nseg;
+  pr.plan_in.mode = pr.mode;
+  pr.plan_in.row_align = row_align;
+  pr.plan_in.sm_count = qfg::DeviceSmCount();
+  return pr;
+}
+
+qfg::Plan PlanFor(const qfg_skinny_gemm& op, qfg::PlanInput in, int rows) {
+  in.max_rows = rows;
+  qfg::Plan plan = qfg::ChoosePlan(in);
+  std::string spec = op.plan_spec;
+  if (spec.empty()) {
+    const char* e = std::getenv("QFG_PLAN");
+    if (e != nullptr) spec = e;
+  }
+  if (!spec.empty() && !qfg::ApplyPlanOverrides(spec, in, &plan)) throw InvalidArgument("SkinnyGemm: bad plan override");
+  return plan;
+}
+
+// Launches row blocks of at most eight rows; only the last block may release PDL dependents
+// (skinny_gemm.cuh:661-676 does the same with blocks of four).
+void Run(const qfg_skinny_gemm& op, Prepared& pr, int64_t m, cudaStream_t stream, const char* name) {
+  const qfg::Plan plan = PlanFor(op, pr.plan_in, static_cast<int>(std::min<int64_t>(m, qfg::kMaxRows)));
+  qfg::GemmParams base = pr.params;
+  int64_t done = 0;
+  while (done < m) {
+    const int chunk = static_cast<int>(std::min<int64_t>(m - done, qfg::kMaxRows));
+    qfg::GemmParams q = base;
+    q.M = chunk;
+    q.x = base.x + static_cast<size_t>(done) * base.K;
+    if (done + chunk < m) q.trigger = 0;
+    const int n_out = base.seg[base.nseg - 1].out_end;
+    for (int o = 0; o < n_out; ++o) {
+      if (base.out[o] != nullptr) q.out[o] = base.out[o] + static_cast<size_t>(done) * base.width[o];
+    }
+    if (q.lm) {
+      if (m > qfg::kMaxRows) throw InvalidArgument(std::string(name) + ": at most 8 rows per call");
+    }
+    cudaError_t err = qfg::LaunchSkinnyGemm(pr.mode, q, plan, stream);
+    if (err == cudaSuccess) err = cudaGetLastError();
+    if (err != cudaSuccess) throw std::runtime_error(std::string(name) + ": " + cudaGetErrorString(err));
+    done += chunk;
+  }
+}
+
+void InitGemmOp(qfg_skinny_gemm* op, const int64_t* seg_outs, int n_seg, const int64_t* widths, int n_widths,
+                const float* w_scale, size_t n_w_scale, int trigger, const char* name) {
+  if (n_seg < 0 || n_widths < 0 || (n_seg > 0 && seg_outs == nullptr) || (n_widths > 0 && widths == nullptr))
+    throw InvalidArgument(std::string(name) + ": bad seg_outs/widths");
+  long long total = 0;
+  for (int i = 0; i < n_seg; ++i) {
+    if (seg_outs[i] < 1 || seg_outs[i] > qfg::kMaxOut) throw InvalidArgument(std::string(name) + ": bad seg_outs/widths");
+    op->seg_outs.push_back(static_cast<int>(seg_outs[i]));
+    total += seg_outs[i];
+  }
+  for (int i = 0; i < n_widths; ++i) {
+    if (widths[i] < 1 || widths[i] > INT_MAX) throw InvalidArgument(std::string(name) + ": bad seg_outs/widths");
+    op->widths.push_back(static_cast<int>(widths[i]));
+  }
+  if (op->seg_outs.empty() || op->seg_outs.size() > static_cast<size_t>(qfg::kMaxSeg) || total != n_widths ||
+      total > qfg::kMaxOut) {
+    throw InvalidArgument(std::string(name) + ": bad seg_outs/widths");
+  }
+  op->trigger = ResolveTrigger(trigger);
+  op->pdl_wait = EnvInt("QFG_PDL_WAIT", 0);
+  const cudaError_t err = qfg::ConfigureSkinnyGemmKernels();
+  if (err != cudaSuccess) throw std::runtime_error(std::string(name) + ": " + cudaGetErrorString(err));
+  op->d_w_scale = UploadScales(w_scale, n_w_scale, name);
+  op->w_scale_len = op->d_w_scale != nullptr ? n_w_scale : 0;
+}
+
+int SetGemmOption(qfg_skinny_gemm* op, const char* key, const char* value) {
+  if (op == nullptr || key == nullptr || value == nullptr) return Fail(QFG_INVALID_ARGUMENT, "set_option: null argument");
+  const std::string k = key;
+  if (k == "pdl_wait") op->pdl_wait = std::atoi(value);
+  else if (k == "force_slow") op->force_slow = std::atoi(value);
+  else if (k == "plan") op->plan_spec = value;
+  else if (k == "trigger") op->trigger = std::atoi(value);
+  else return Fail(QFG_INVALID_ARGUMENT, "set_option: unknown key " + k);
+  return QFG_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* qfg_last_error(void) { return g_last_error.c_str(); }
+const char* qfg_version(void) { return "qfg-b200 0.1 sm_100a"; }
+
+int qfg_skinny_gemm_create(const int64_t* seg_outs, int n_seg, const int64_t* widths, int n_widths,
+                           const float* w_scale, size_t n_w_scale, int trigger, qfg_skinny_gemm** out) {
+  if (out == nullptr) return Fail(QFG_INVALID_ARGUMENT, "SkinnyGemm: null handle pointer");
+  *out = nullptr;
+  qfg_skinny_gemm* op = new qfg_skinny_gemm();
+  try {
+    InitGemmOp(op, seg_outs, n_seg, widths, n_widths, w_scale, n_w_scale, trigger, "SkinnyGemm");
+  } catch (const std::exception& e) {
+    delete op;
+    return Fail(QFG_INVALID_ARGUMENT, e.what());
+  }
+  *out = op;
+  return QFG_OK;
+}
+
+int qfg_skinny_gemm_compute(const qfg_skinny_gemm* op, const void* x, int64_t m, int64_t k,
+                            const qfg_tensor2d* weights, int n_weights, void* const* outs, int n_outs,
+                            void* stream) {
+  if (op == nullptr || weights == nullptr || outs == nullptr) return Fail(QFG_FAIL, "SkinnyGemm: null argument");
+  try {
+    Prepared pr = Prepare(*op, x, m, k, weights, n_weights, outs, n_outs, true);
+    Run(*op, pr, m, static_cast<cudaStream_t>(stream), "SkinnyGemm");
+    return QFG_OK;
+  } catch (const InvalidArgument& e) {
+    return Fail(QFG_INVALID_ARGUMENT, e.what());
+  } catch (const std::exception& e) {
+    return Fail(QFG_FAIL, e.what());
+  }
+}
+
+int qfg_skinny_gemm_set_option(qfg_skinny_gemm* op, const char* key, const char* value) {
+  return SetGemmOption(op, key, value);
+}
+
+int qfg_skinny_gemm_describe(const qfg_skinny_gemm* op, int64_t k, const qfg_tensor2d* weights, int n_weights,
+                             char* buf, size_t buf_len) {
+  if (op == nullptr || weights == nullptr || buf == nullptr || buf_len == 0)
+    return Fail(QFG_INVALID_ARGUMENT, "describe: null argument");
+  try {
+    Prepared pr = Prepare(*op, nullptr, 1, k, weights, n_weights, nullptr, 0, false);
+    const qfg::Plan plan = PlanFor(*op, pr.plan_in, qfg::kMaxRows);
+    const std::string d = qfg::DescribePlan(plan, pr.plan_in);
+    std::snprintf(buf, buf_len, "%s", d.c_str());
+    return QFG_OK;
+  } catch (const std::exception& e) {
+    return Fail(QFG_INVALID_ARGUMENT, e.what());
+  }
+}
+
+int qfg_plan_describe(int dtype, int64_t k, const int64_t* n, int nseg, int row_align, int sm_count,
+                      const char* spec, char* buf, size_t buf_len) {
+  if (n == nullptr || buf == nullptr || buf_len == 0 || nseg < 1 || nseg > qfg::kMaxSeg || k < 1 || k > INT_MAX ||
+      (row_align != 16 && row_align != 8 && row_align != 4) || sm_count < 1) {
+    return Fail(QFG_INVALID_ARGUMENT, "plan_describe: bad argument");
+  }
+  qfg::PlanInput in;
+  in.K = static_cast<int>(k);
+  in.nseg = nseg;
+  in.mode = dtype == QFG_BFLOAT16 ? qfg::kBf16 : dtype == QFG_FLOAT8E4M3FN ? qfg::kFp8 : qfg::kNvfp4;
+  if (dtype != QFG_BFLOAT16 && dtype != QFG_FLOAT8E4M3FN && dtype != QFG_UINT8)
+    return Fail(QFG_INVALID_ARGUMENT, "plan_describe: unsupported weight element type");
+  for (int s = 0; s < nseg; ++s) {
+    if (n[s] < 1 || n[s] > INT_MAX) return Fail(QFG_INVALID_ARGUMENT, "plan_describe: bad width");
+    in.n[s] = static_cast<int>(n[s]);
+  }
+  in.row_align = row_align;
+  in.sm_count = sm_count;
+  qfg::Plan plan = qfg::ChoosePlan(in);
+  if (spec != nullptr && spec[0] != 0 && !qfg::ApplyPlanOverrides(spec, in, &plan))
+    return Fail(QFG_INVALID_ARGUMENT, "plan_describe: bad plan override");
+  std::string d = qfg::DescribePlan(plan, in);
+  d += ",seg_tiles=";
+  for (int s = 0; s < nseg; ++s) d += (s ? "/" : "") + std::to_string(plan.tiles[s]);
+  std::snprintf(buf, buf_len, "%s", d.c_str());
+  return QFG_OK;
+}
+
+void qfg_skinny_gemm_destroy(qfg_skinny_gemm* op) {
+  if (op == nullptr) return;
+  cudaFree(op->d_w_scale);
+  delete op;
+}
+
+int qfg_argmax_rows(int dtype, const void* x, int64_t rows, int64_t vocab, int64_t* idx, float* val, void* stream) {
+  if (dtype != QFG_BFLOAT16 && dtype != QFG_FLOAT16 && dtype != QFG_FLOAT)
+    return Fail(QFG_INVALID_ARGUMENT, "ArgmaxRows: logits must be BF16/FP16/FP32");
+  if (vocab < 1 || rows < 0) return Fail(QFG_INVALID_ARGUMENT, "ArgmaxRows: bad shape");
+  if (rows == 0) return QFG_OK;
+  if (x == nullptr || idx == nullptr) return Fail(QFG_INVALID_ARGUMENT, "ArgmaxRows: null argument");
+  if (vocab >= INT_MAX) return Fail(QFG_FAIL, std::string("ArgmaxRows: ") + cudaGetErrorString(cudaErrorInvalidValue));
+  const size_t elem = dtype == QFG_FLOAT ? 4 : 2;
+  if (reinterpret_cast<uintptr_t>(x) % elem != 0) return Fail(QFG_INVALID_ARGUMENT, "ArgmaxRows: misaligned logits");
+  // the grid's y extent caps one launch at 65535 rows
+  for (int64_t r0 = 0; r0 < rows; r0 += 65535) {
+    const int64_t n = std::min<int64_t>(65535, rows - r0);
+    cudaError_t err = qfg::LaunchArgmaxRows(dtype, static_cast<const uint8_t*>(x) + static_cast<size_t>(r0) * vocab * elem,
+                                            n, vocab, idx + r0, val != nullptr ? val + r0 : nullptr,
+                                            static_cast<cudaStream_t>(stream));
+    if (err == cudaSuccess) err = cudaGetLastError();
+    if (err != cudaSuccess) return Fail(QFG_FAIL, std::string("ArgmaxRows: ") + cudaGetErrorString(err));
+  }
+  return QFG_OK;
+}
+
+int qfg_dequant_create(int64_t n_cols, int64_t col_offset, const int64_t* widths, int n_widths,
+                       const float* w_scale, size_t n_w_scale, qfg_dequant** out) {
+  if (out == nullptr) return Fail(QFG_INVALID_ARGUMENT, "DequantWeightBf16: null handle pointer");
+  *out = nullptr;
+  qfg_dequant* op = new qfg_dequant();
+  try {
+    op->n_cols = n_cols;
+    op->col_offset = col_offset;
+    for (int i = 0; i < n_widths; ++i) {
+      if (widths[i] > INT_MAX) throw InvalidArgument("DequantWeightBf16: invalid widths or col_offset");
+      op->widths.push_back(static_cast<int>(widths[i]));
+    }
+    if (op->widths.empty()) op->widths.push_back(static_cast<int>(n_cols));
+    long long sum_w = 0;
+    for (int v : op->widths) {
+      if (v <= 0 || v % 8 != 0)
+        throw InvalidArgument("DequantWeightBf16: each width must be a positive multiple of 8");
+      sum_w += v;
+    }
+    if (sum_w != n_cols || op->widths.size() > static_cast<size_t>(qfg::kMaxOut) || col_offset < 0 || col_offset % 8 != 0)
+      throw InvalidArgument("DequantWeightBf16: invalid widths or col_offset");
+    op->d_w_scale = UploadScales(w_scale, n_w_scale, "DequantWeightBf16");
+    op->w_scale_len = op->d_w_scale != nullptr ? n_w_scale : 0;
+  } catch (const std::exception& e) {
+    delete op;
+    return Fail(QFG_INVALID_ARGUMENT, e.what());
+  }
+  *out = op;
+  return QFG_OK;
+}
+
+int qfg_dequant_compute(const qfg_dequant* op, const qfg_tensor2d* w, void* const* outs, int n_outs, void* stream) {
+  if (op == nullptr || w == nullptr || outs == nullptr) return Fail(QFG_FAIL, "DequantWeightBf16: null argument");
+  try {
+    const int64_t N = op->n_cols;
+    if (N <= 0 || N % 8 != 0 || w->rows < 0 || w->rows > INT_MAX || N > INT_MAX)
+      throw InvalidArgument("DequantWeightBf16: invalid shape");
+    if (n_outs != static_cast<int>(op->widths.size())) throw InvalidArgument("DequantWeightBf16: output count");
+    if (op->d_w_scale != nullptr && op->w_scale_len < static_cast<size_t>(N))
+      throw InvalidArgument("DequantWeightBf16: w_scale shorter than n_cols");
+    qfg::DequantParams p;
+    const int64_t co = op->col_offset;
+    if (w->dtype == QFG_BFLOAT16 && w->cols >= co + N) {
+      p.mode = qfg::kBf16;
+      p.row_stride = static_cast<int>(w->cols);
+      p.aligned = reinterpret_cast<uintptr_t>(w->data) % 16 == 0 && w->cols % 8 == 0;
+    } else if (w->dtype == QFG_FLOAT8E4M3FN && w->cols >= co + N) {
+      p.mode = qfg::kFp8;
+      p.row_stride = static_cast<int>(w->cols);
+      p.aligned = reinterpret_cast<uintptr_t>(w->data) % 8 == 0 && w->cols % 8 == 0;
+    } else if (w->dtype == QFG_UINT8 && N % 16 == 0 && co % 16 == 0 && w->cols * 16 >= (co + N) * 9 &&
+               (w->cols * 16) % 9 == 0) {
+      p.mode = qfg::kNvfp4;
+      p.row_stride = static_cast<int>((w->cols * 16) / 9);
+      p.aligned = reinterpret_cast<uintptr_t>(w->data) % 4 == 0 && w->cols % 4 == 0;
+    } else {
+      throw InvalidArgument("DequantWeightBf16: unsupported input type/shape");
+    }
+    if (w->data == nullptr && w->rows > 0) throw InvalidArgument("DequantWeightBf16: null weight");
+    p.w = static_cast<const uint8_t*>(w->data);
+    p.w_scale = op->d_w_scale;
+    p.K = static_cast<int>(w->rows);
+    p.N = static_cast<int>(N);
+    p.col_offset = static_cast<int>(co);
+    p.num_outs = static_cast<int>(op->widths.size());
+    int col_off = 0;
+    for (int i = 0; i < p.num_outs; ++i) {
+      if (outs[i] == nullptr || reinterpret_cast<uintptr_t>(outs[i]) % 16 != 0)
+        throw InvalidArgument("DequantWeightBf16: outputs must be 16-byte aligned");
+      p.out[i] = static_cast<uint16_t*>(outs[i]);
+      p.col_begin[i] = col_off;
+      p.width[i] = op->widths[i];
+      col_off += op->widths[i];
+    }
+    cudaError_t err = qfg::LaunchDequant(p, static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) throw std::runtime_error(std::string("DequantWeightBf16: ") + cudaGetErrorString(err));
+    return QFG_OK;
+  } catch (const InvalidArgument& e) {
+    return Fail(QFG_INVALID_ARGUMENT, e.what());
+  } catch (const std::exception& e) {
+    return Fail(QFG_FAIL, e.what());
+  }
+}
+
+void qfg_dequant_destroy(qfg_dequant* op) {
+  if (op == nullptr) return;
+  cudaFree(op->d_w_scale);
+  delete op;
+}
+
+size_t qfg_lmhead_workspace_bytes(void) { return 128; }
+
+int qfg_lmhead_create(const float* w_scale, size_t n_w_scale, int trigger, qfg_lmhead** out) {
+  if (out == nullptr) return Fail(QFG_INVALID_ARGUMENT, "LmHead: null handle pointer");
+  *out = nullptr;
+  qfg_lmhead* op = new qfg_lmhead();
+  try {
+    // geometry is per call (the vocabulary shard width is an argument), so the attribute lists
+    // hold a placeholder of one weight with one output
+    const int64_t one = 1;
+    InitGemmOp(&op->gemm, &one, 1, &one, 1, w_scale, n_w_scale, trigger, "LmHead");
+  } catch (const std::exception& e) {
+    delete op;
+    return Fail(QFG_INVALID_ARGUMENT, e.what());
+  }
+  *out = op;
+  return QFG_OK;
+}
+
+int qfg_lmhead_compute(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
+                       int64_t n, int64_t col_offset, void* workspace, int64_t* idx, float* val, uint64_t* key,
+                       void* logits, void* stream) {
+  if (op == nullptr || weight == nullptr) return Fail(QFG_FAIL, "LmHead: null argument");
+  try {
+    if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 8 != 0)
+      throw InvalidArgument("LmHead: workspace must be an 8-byte aligned device pointer");
+    if (n < 1 || n > INT_MAX || col_offset < 0 || col_offset + n > 0xFFFFFFFELL)
+      throw InvalidArgument("LmHead: bad vocabulary range");
+    if (m < 1 || m > qfg::kMaxRows) throw InvalidArgument("LmHead: 1 <= rows <= 8");
+    qfg_skinny_gemm call = op->gemm;  // same attributes, this call's width
+    call.widths[0] = static_cast<int>(n);
+    void* outs[1] = {logits};
+    Prepared pr = Prepare(call, x, m, k, weight, 1, outs, 1, false);
+    if (x == nullptr || reinterpret_cast<uintptr_t>(x) % 4 != 0 || weight->data == nullptr)
+      throw InvalidArgument("LmHead: null or misaligned input");
+    const int a = Alignment(weight->data, pr.params.seg[0].pitch);
+    if (a == 0) throw InvalidArgument("LmHead: weight rows must be 4-byte aligned");
+    pr.params.seg[0].vec = pr.params.seg[0].svec = a;
+    pr.plan_in.row_align = a;
+    pr.params.out[0] = static_cast<uint16_t*>(logits);
+    pr.params.lm = 1;
+    pr.params.lm_keys = static_cast<unsigned long long*>(workspace);
+    pr.params.lm_count = reinterpret_cast<unsigned int*>(static_cast<unsigned long long*>(workspace) + qfg::kMaxRows);
+    pr.params.lm_idx = reinterpret_cast<long long*>(idx);
+    pr.params.lm_val = val;
+    pr.params.lm_key_out = reinterpret_cast<unsigned long long*>(key);
+    pr.params.lm_col_offset = col_offset;
+    Run(call, pr, m, static_cast<cudaStream_t>(stream), "LmHead");
+    call.d_w_scale = nullptr;
+    return QFG_OK;
+  } catch (const InvalidArgument& e) {
+    return Fail(QFG_INVALID_ARGUMENT, e.what());
+  } catch (const std::exception& e) {
+    return Fail(QFG_FAIL, e.what());
+  }
+}
+
+int qfg_lmhead_set_option(qfg_lmhead* op, const char* key, const char* value) {
+  return SetGemmOption(op != nullptr ? &op->gemm : nullptr, key, value);
+}
+
+void qfg_lmhead_destroy(qfg_lmhead* op) {
+  if (op == nullptr) return;
+  cudaFree(op->gemm.d_w_scale);
+  delete op;
+}
+
+int qfg_lmhead_combine(const uint64_t* keys, int ranks, int64_t m, int64_t* idx, float* val, void* stream) {
+  if (keys == nullptr || ranks < 1 || m < 1) return Fail(QFG_INVALID_ARGUMENT, "LmHead: bad combine arguments");
+  cudaError_t err = qfg::LaunchLmheadCombine(keys, ranks, m, idx, val, static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return Fail(QFG_FAIL, std::string("LmHead: ") + cudaGetErrorString(err));
+  return QFG_OK;
+}
+
+}  // extern "C"

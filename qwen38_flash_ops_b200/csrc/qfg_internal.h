@@ -1,0 +1,140 @@
+// Internal interfaces between the host layer (capi.cc, planner.cc) and the kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+#include "qfg.h"
+
+namespace qfg {
+
+constexpr int kMaxSeg = QFG_MAX_WEIGHTS;
+constexpr int kMaxOut = QFG_MAX_OUTPUTS;
+constexpr int kMaxRows = 8;  // rows of x one launch handles (the n = 8 side of m16n8k16)
+
+enum WeightMode : int { kBf16 = 0, kFp8 = 1, kNvfp4 = 2 };
+
+// Per-mode geometry of the streaming kernel: a thread owns `kColsPerThread` columns of four
+// weight rows per k-step, fetched as one shared-memory load of `kBytesPerThread` per row.
+struct ModeGeom {
+  int cols_per_thread;   // 8 (BF16), 16 (FP8), 16 (NVFP4)
+  int bytes_per_thread;  // 16, 16, 8
+  int cols_per_warp;     // 8 thread groups side by side
+  int bytes_per_warp;    // per weight row
+};
+inline ModeGeom GeomOf(int mode) {
+  switch (mode) {
+    case kBf16: return {8, 16, 64, 128};
+    case kFp8: return {16, 16, 128, 128};
+    default: return {16, 8, 128, 64};
+  }
+}
+
+// Launch geometry.  It depends on (K, segment widths, weight type) only - never on the
+// number of rows - so that a row's reduction order is the same in every call.
+struct Plan {
+  int wn = 4;       // warps side by side along N
+  int wk = 2;       // warps splitting each stage along K
+  int ks = 1;       // k-steps (16 rows) per warp per stage
+  int stages = 4;   // depth of the shared-memory ring
+  int cluster = 1;  // CTAs splitting K, reduced through distributed shared memory
+  int tiles[kMaxSeg] = {0, 0, 0, 0};  // column tiles per segment
+  int gran = 16;    // columns per granule of the balanced column partition
+  int threads() const { return 32 * wn * wk; }
+  int rows_per_stage() const { return 16 * wk * ks; }
+};
+
+struct Segment {
+  const uint8_t* w = nullptr;
+  const float* w_scale = nullptr;
+  long long pitch = 0;        // bytes per stored row
+  long long total_bytes = 0;  // K * pitch
+  int n = 0;
+  int tile_begin = 0;
+  int tiles = 0;
+  int granules = 0;
+  int out_begin = 0;
+  int out_end = 0;
+  int vec = 16;   // cp.async width for the weight bytes of a row
+  int svec = 4;   // cp.async width for the NVFP4 scale bytes of a row
+};
+
+struct GemmParams {
+  const uint16_t* x = nullptr;  // BF16 [M, K]
+  int M = 0;
+  int K = 0;
+  int nseg = 0;
+  Segment seg[kMaxSeg];
+  uint16_t* out[kMaxOut] = {};
+  int col_begin[kMaxOut] = {};
+  int width[kMaxOut] = {};
+  int trigger = 0;
+  int pdl_wait = 0;
+  int force_slow = 0;  // testing: always take the BF16-MMA path of the quantised modes
+  // plan
+  int wn = 4, wk = 2, ks = 1, stages = 4, cluster = 1, gran = 16;
+  int xpitch = 0;       // elements per x row in shared memory
+  int ring_bytes = 0;   // stages * stage_bytes
+  int stage_bytes = 0;
+  int tile_row_bytes = 0;   // wn * bytes_per_warp
+  int scale_row_bytes = 0;  // NVFP4: shared-memory bytes per row of the scale region
+  // fused LM head (argmax over the BF16-rounded outputs of segment 0)
+  int lm = 0;
+  unsigned long long* lm_keys = nullptr;  // [kMaxRows] workspace, zero between calls
+  unsigned int* lm_count = nullptr;       // workspace counter, zero between calls
+  long long* lm_idx = nullptr;
+  float* lm_val = nullptr;
+  unsigned long long* lm_key_out = nullptr;
+  long long lm_col_offset = 0;
+};
+
+// planner.cc
+struct PlanInput {
+  int K = 0;
+  int nseg = 0;
+  int n[kMaxSeg] = {};
+  int mode = 0;
+  int row_align = 16;  // min over segments of the alignment (16 / 8 / 4) of base and pitch
+  int sm_count = 148;
+  int max_rows = kMaxRows;
+};
+Plan ChoosePlan(const PlanInput& in);
+// Applies "key=value,..." overrides (wn, wk, ks, stages, cluster, ctas, gran); returns false on a bad key.
+bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan);
+void FitRing(const PlanInput& in, int rows, Plan* plan);
+void DistributeTiles(const PlanInput& in, int total_tiles, Plan* plan);
+size_t SmemBytes(const Plan& plan, int mode, int rows, int K);
+std::string DescribePlan(const Plan& plan, const PlanInput& in);
+
+// skinny_gemm.cu
+cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStream_t stream);
+int DeviceSmCount();
+cudaError_t ConfigureSkinnyGemmKernels();
+
+// argmax_rows.cu
+cudaError_t LaunchArgmaxRows(int dtype, const void* x, int64_t rows, int64_t vocab, int64_t* idx, float* val,
+                             cudaStream_t stream);
+cudaError_t LaunchLmheadCombine(const uint64_t* keys, int ranks, int64_t m, int64_t* idx, float* val,
+                                cudaStream_t stream);
+
+// dequant_bf16.cu
+struct DequantParams {
+  const uint8_t* w = nullptr;
+  const float* w_scale = nullptr;
+  int mode = 0;
+  int K = 0;
+  int N = 0;            // columns produced
+  int row_stride = 0;   // logical columns of a stored row
+  int col_offset = 0;
+  int num_outs = 1;
+  uint16_t* out[kMaxOut] = {};
+  int col_begin[kMaxOut] = {};
+  int width[kMaxOut] = {};
+  int aligned = 1;      // vector loads are legal for every row
+};
+cudaError_t LaunchDequant(const DequantParams& p, cudaStream_t stream);
+
+}  // namespace qfg

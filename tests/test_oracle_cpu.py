@@ -1,0 +1,215 @@
+"""Pins the CPU oracle: decode tables against ml_dtypes, the dequant / GEMM / argmax restatement
+against the formulas the reference's own op tests assert (tests/test_load.py of the reference,
+re-expressed with torch on the CPU), the numpy oracle against the C oracle, and both against
+fixtures produced by the reference's kernels on a B200 (tests/golden)."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import cpu as C
+from oracle import oracle as O
+from qwen38_flash_ops_b200 import packing as P
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_e4m3_table_matches_ml_dtypes():
+    ml = pytest.importorskip("ml_dtypes")
+    codes = np.arange(256, dtype=np.uint8)
+    ref = codes.view(ml.float8_e4m3fn).astype(np.float32)
+    assert np.array_equal(np.isnan(ref), np.isnan(O.E4M3))
+    ok = ~np.isnan(ref)
+    assert np.array_equal(ref[ok], O.E4M3[ok])
+    assert np.array_equal(P.e4m3_decode(codes)[ok], ref[ok])
+
+
+def test_e2m1_table_matches_ml_dtypes():
+    ml = pytest.importorskip("ml_dtypes")
+    if not hasattr(ml, "float4_e2m1fn"):
+        pytest.skip("ml_dtypes without float4_e2m1fn")
+    # float4 arrays are stored one value per byte in ml_dtypes
+    vals = np.arange(16, dtype=np.uint8).view(ml.float4_e2m1fn).astype(np.float32)
+    mine = O.e2m1_scaled(np.arange(16, dtype=np.uint8), np.full(16, 0.5, np.float32))  # scale 1 -> s_half 0.5
+    assert np.array_equal(vals, mine)
+    assert np.signbit(mine[8]) and mine[8] == 0.0  # nibble 0x8 is -0
+
+
+def test_e4m3_encode_matches_torch_cast():
+    rng = np.random.default_rng(0)
+    x = (rng.standard_normal(20000) * rng.choice([1e-3, 0.1, 1, 30, 200], 20000)).astype(np.float32)
+    x = np.clip(x, -448, 448)
+    ref = torch.from_numpy(x).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    got = P.e4m3_encode(x)
+    assert np.array_equal(ref, got)
+
+
+def test_fp8_dequant_formula_of_reference_test():
+    # tests/test_load.py:322-342 of the reference: seed 5, K 256, N 128, scale = amax/448,
+    # expected = (w_fp8.float() * scale).bfloat16(), asserted bit-exact.
+    gen = torch.Generator().manual_seed(5)
+    K, N = 256, 128
+    w = (torch.randn(K, N, generator=gen) * 0.05).bfloat16()
+    amax = w.float().abs().amax(dim=0).clamp(min=1e-8)
+    scale = (amax / 448.0).numpy().astype(np.float32)
+    w_fp8 = (w.float() / torch.from_numpy(scale)[None, :]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    ref = (w_fp8.float() * torch.from_numpy(scale)[None, :]).bfloat16().view(torch.int16).numpy().view(np.uint16)
+    q = w_fp8.view(torch.uint8).numpy()
+    assert np.array_equal(O.dequant_weight_bf16(O.MODE_FP8, q, N, 0, scale), ref)
+    assert np.array_equal(C.dequant_bf16(O.MODE_FP8, q, N, 0, scale), ref)
+    # and the column-slice / col_offset addressing (fused_gemm.cu:218-223)
+    assert np.array_equal(O.dequant_weight_bf16(O.MODE_FP8, q, 64, 64, scale[64:]), ref[:, 64:])
+    assert np.array_equal(C.dequant_bf16(O.MODE_FP8, q, 64, 64, scale[64:]), ref[:, 64:])
+
+
+def test_fp8_gemm_formula_of_reference_test():
+    # tests/test_load.py:344-372: y_ref = (x.float() @ deq.float()).bfloat16(); M=2 relative error < 1 %,
+    # and the one-BF16-ULP criterion of bf16_ulp_close (:83-86).
+    gen = torch.Generator().manual_seed(5)
+    K, N = 256, 128
+    x = torch.randn(1, 2, K, generator=gen).bfloat16()
+    w = (torch.randn(K, N, generator=gen) * 0.05).bfloat16()
+    amax = w.float().abs().amax(dim=0).clamp(min=1e-8)
+    scale = (amax / 448.0).numpy().astype(np.float32)
+    w_fp8 = (w.float() / torch.from_numpy(scale)[None, :]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    deq = (w_fp8.float() * torch.from_numpy(scale)[None, :]).bfloat16()
+    y_ref = (x.float().reshape(2, K) @ deq.float()).bfloat16().float().numpy()
+    xb = x.reshape(2, K).view(torch.int16).numpy().view(np.uint16)
+    outs, sums, mags = O.skinny_gemm(xb, [(O.MODE_FP8, w_fp8.view(torch.uint8).numpy())], [2], [64, 64], scale)
+    y = O.bf16_to_f32(np.concatenate(outs, axis=1))
+    rel = np.linalg.norm(y - y_ref) / np.linalg.norm(y_ref)
+    assert rel < 0.01
+    # dequantise-then-MatMul rounds every weight to BF16 first while the fused op scales the
+    # sum, so the two differ in the last bit here and there; the reference asserts only the 1 %
+    # bound for this path, and most elements agree to one BF16 ULP
+    assert np.mean(np.abs(y - y_ref) <= 2.0 ** -7 * np.abs(y_ref) + 1e-30) > 0.8
+
+
+def test_argmax_formula_of_reference_test():
+    # tests/test_load.py:192-205: rows 5, V 4099, planted tie -> 17, indices and max exact.
+    rows, vocab = 5, 4099
+    gen = torch.Generator().manual_seed(3)
+    for dtype, code in ((torch.bfloat16, 0), (torch.float32, 2)):
+        x = torch.randn(rows, vocab, generator=gen).to(dtype)
+        x[1, 17] = x[1, 3000] = x.max() + 1
+        mx = x.float().max(dim=1)
+        idx, val = O.argmax_rows(x.float().numpy())
+        assert idx[1] == 17
+        keep = np.array([r != 1 for r in range(rows)])
+        assert np.array_equal(idx[keep], mx.indices.numpy()[keep])
+        assert np.array_equal(val, mx.values.numpy())
+        raw = x.view(torch.int16).numpy().view(np.uint16) if code == 0 else x.numpy()
+        cidx, cval = C.argmax_rows(code, raw)
+        assert np.array_equal(cidx, idx) and np.array_equal(cval, val)
+
+
+def test_argmax_nan_zero_and_ties():
+    x = np.zeros((4, 37), np.float32)
+    x[0, 5] = -0.0
+    x[0, 9] = 0.0                      # all equal (+-0): index 0
+    x[1, 20] = np.nan
+    x[1, 30] = np.nan
+    x[1, 3] = 1e30                     # first NaN wins
+    x[2, :] = -np.inf                  # all -inf: index 0
+    x[3, 36] = 7.0
+    idx, val = O.argmax_rows(x)
+    assert list(idx) == [0, 20, 0, 36]
+    assert np.isnan(val[1]) and val[3] == 7.0
+    cidx, cval = C.argmax_rows(2, x)
+    assert np.array_equal(cidx, idx)
+    h = x.astype(np.float16).view(np.uint16)
+    cidx, _ = C.argmax_rows(1, h)
+    assert np.array_equal(cidx, idx)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_numpy_and_c_oracle_agree(mode):
+    rng = np.random.default_rng(10 + mode)
+    K, N, M = 192, 320, 3
+    x = P.synth_x(rng, M, K)
+    w = P.synth_weight(rng, K, N)
+    scale = None
+    if mode == 0:
+        wq = P.f32_to_bf16_bits(w)
+    elif mode == 1:
+        wq, scale = P.quantize_fp8_per_column(w)
+    else:
+        wq = P.pack_nvfp4(w)
+        scale = rng.uniform(0.5, 2.0, N).astype(np.float32)
+    outs, sums, mags = O.skinny_gemm(x, [(mode, wq)], [2], [64, 256], scale)
+    co, cs, cm = C.skinny_gemm(mode, x, wq, N, scale)
+    assert np.array_equal(np.concatenate(outs, axis=1), co)
+    assert np.allclose(sums[0], cs, rtol=1e-12, atol=0)
+    assert np.allclose(mags[0], cm, rtol=1e-12, atol=0)
+    if mode != 0:
+        assert np.array_equal(O.dequant_weight_bf16(mode, wq, 64, 64, None if scale is None else scale[:64]),
+                              C.dequant_bf16(mode, wq, 64, 64, None if scale is None else scale[:64]))
+    ok = O.gemm_within_tolerance(C.chain_f32(mode, x, wq, N, scale), cs, cm, K)
+    # the unfused FP32 chain agrees with the fused definition within the stated bar (+1 ULP for the
+    # per-weight BF16 rounding of dequantise-then-MatMul when a w_scale is present)
+    assert ok.mean() > 0.8
+
+
+def test_nvfp4_special_scale_bytes():
+    # E4M3 subnormal, zero, negative and NaN scale codes; nibble 0x8 is -0
+    K, N = 4, 64
+    rng = np.random.default_rng(3)
+    packed = rng.integers(0, 256, (K, N * 9 // 16), dtype=np.uint8)
+    packed[0, N // 2:] = [0x00, 0x01, 0x87, 0x7F]
+    packed[1, N // 2:] = [0xFF, 0x08, 0x7E, 0xFE]
+    packed[2, 0] = 0x88
+    vals = O.decode_weights_exact(2, packed, N)
+    assert np.all(vals[0, :16] == 0)
+    assert np.all(np.isnan(vals[0, 48:64])) and np.all(np.isnan(vals[1, 0:16]))
+    d = O.dequant_weight_bf16(2, packed, N)
+    assert np.array_equal(d, C.dequant_bf16(2, packed, N))
+    assert np.all(d[0, 48:64] == 0x7FFF)
+    s = O.E4M3[packed[2, N // 2]]
+    assert vals[2, 0] == 0 and np.signbit(vals[2, 0]) != np.signbit(s)  # -0 * scale
+
+
+def test_combine_pairs_matches_unsharded_argmax():
+    rng = np.random.default_rng(5)
+    V, rows = 1024, 6
+    x = rng.standard_normal((rows, V)).astype(np.float32)
+    x[2, 100] = x[2, 900] = 9.0          # tie across shards -> lowest global index
+    x[3, 700] = np.nan
+    x[3, 10] = np.nan                    # first NaN wins
+    idx, val = O.argmax_rows(x)
+    for shards in (2, 4, 8):
+        w = V // shards
+        vs = np.empty((shards, rows), np.float32)
+        ix = np.empty((shards, rows), np.int64)
+        for s in range(shards):
+            i, v = O.argmax_rows(x[:, s * w:(s + 1) * w])
+            vs[s], ix[s] = v, i + s * w
+        ci, cv = O.combine_pairs(vs, ix)
+        assert np.array_equal(ci, idx)
+        assert np.array_equal(np.isnan(cv), np.isnan(val)) and np.array_equal(cv[~np.isnan(cv)], val[~np.isnan(val)])
+
+
+def test_golden_fixtures_from_reference_kernels():
+    """Outputs of the reference's own kernels (compiled for sm_100a, run on a B200) for seeded
+    inputs; tests/golden/make_golden.py wrote them.  The oracle must reproduce them: argmax
+    bit-exactly, GEMM within the stated tolerance."""
+    files = sorted(glob.glob(os.path.join(GOLDEN, "ref_*.npz")))
+    if not files:
+        pytest.skip("no fixtures generated yet")
+    for f in files:
+        z = np.load(f)
+        kind = str(z["kind"])
+        if kind == "argmax":
+            idx, val = C.argmax_rows(int(z["dtype_code"]), z["x"])
+            assert np.array_equal(idx, z["idx"]), f
+            assert np.array_equal(val.view(np.uint32), z["val"].view(np.uint32)), f
+        elif kind == "gemm":
+            mode, n = int(z["mode"]), int(z["n"])
+            scale = z["w_scale"] if "w_scale" in z.files and z["w_scale"].size else None
+            out, sums, mags = C.skinny_gemm(mode, z["x"], z["w"], n, scale)
+            ok = O.gemm_within_tolerance(z["y"], sums, mags, z["x"].shape[1])
+            assert ok.all(), f
+            # and the oracle's own rounding differs from the reference kernel by at most one BF16 ULP
+            diff = np.abs(out.astype(np.int32) - z["y"].astype(np.int32))
+            assert np.mean(diff <= 1) > 0.999, f
