@@ -1,0 +1,439 @@
+#!/usr/bin/env python3
+"""Benchmark of the decode weight-streaming path (SkinnyGemm / fused LM head) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--rows M]
+
+Headline workload: the NVFP4 LM head (K 5120, vocabulary 151936, `UINT8 [5120, 85464]`, 437.6 MB
+of packed weights - larger than L2, so every step streams from HBM) fused with ArgmaxRows.  One
+step is one call on one batch of M rows; with N > 1 GPUs the vocabulary is split by columns
+(128-column granules), every rank runs the fused kernel on its shard and the ranks all-gather
+their per-row (max, index) keys over NCCL - total work is fixed, so scaling is strong.  The metric
+is weight bytes per second over all GPUs.  Rank 0 prints one JSON line.
+
+`--impl reference` times the CPU restatement of the unfused chain the op replaces (dequantise ->
+MatMul with FP32 accumulation -> ArgMax) on the host cores, on a bounded column sample of the
+same workload; the reference project has no CPU implementation of its own, and ONNX Runtime is
+not installed here.  Where the reference's CUDA kernels were compiled for sm_100a
+(oracle/_ref) their time on the same workload is reported beside it.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "nvfp4_skinny_gemm_weight_stream"
+UNIT = "TB/s"
+HEAD = "C5_nvfp4_lmhead_5120x151936"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f).get("hbm_gbs", 6459.6), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for s in self.samples:
+            parts = [p.strip() for p in s.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def time_region(torch, fn, steps, warmup, dist=None):
+    """W warm-up calls, then exactly `steps` calls bracketed by barrier + synchronize; device time
+    from CUDA events on the launching stream; max over ranks."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def time_graph_rotation(torch, make_call, n_buffers, reps=20, warmup=3):
+    """Per-call device time of a short kernel: a CUDA graph holding one call per weight copy
+    (copies total more than 16x L2, so every call streams from HBM), replayed `reps` times."""
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for i in range(n_buffers):
+            make_call(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for i in range(n_buffers):
+                make_call(i)
+        for _ in range(warmup):
+            g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) * 1000.0 / n_buffers)
+    return statistics.median(times), min(times)
+
+
+def bench_small_configs(torch, quick=False):
+    """Configs C1-C4 (50-100 MB, L2-sized): device-timed us/call under buffer rotation, weight GB/s."""
+    from qwen38_flash_ops_b200 import SkinnyGemm
+    from qwen38_flash_ops_b200 import workloads as W
+
+    peak, _ = peaks()
+    out = {}
+    for name, wl in W.CONFIGS.items():
+        if wl.fused_argmax:
+            continue
+        copies = max(2, min(48, -(-(2 << 30) // wl.weight_bytes)))
+        if quick:
+            copies = min(copies, 8)
+        sets, scales = [], None
+        for c in range(copies):
+            ws = []
+            sc = []
+            for i, n in enumerate(wl.ns):
+                w, s = W.make_weight(wl.mode, wl.k, n, seed=1000 * c + i)
+                ws.append(w)
+                sc.append(s)
+            sets.append(ws)
+            if c == 0 and wl.mode == W.MODE_FP8:
+                scales = torch.cat(sc).cpu().numpy()
+        seg_outs = [len(w) for w in wl.seg_widths]
+        widths = [w for ws_ in wl.seg_widths for w in ws_]
+        res = {"weight_bytes": wl.weight_bytes, "copies": copies}
+        for m in sorted({1, 2, 4, wl.m}):
+            x = W.make_x(m, wl.k, seed=7)
+            outs = [torch.empty((m, w), dtype=torch.bfloat16, device="cuda") for w in widths]
+            for label, pdl in (("", 0), ("_pdl", 1)):
+                op = SkinnyGemm(seg_outs, widths, w_scale=scales, trigger=(wl.trigger or 2) if pdl else wl.trigger)
+                op.set_option("pdl_wait", pdl)
+                med, best = time_graph_rotation(torch, lambda i: op(x, *sets[i], out=outs), copies)
+                res[f"M{m}{label}"] = {"us": round(med, 3), "us_best": round(best, 3),
+                                       "GBps": round(wl.weight_bytes / med / 1e3, 1),
+                                       "frac_of_measured_hbm": round(wl.weight_bytes / med / 1e3 / peak, 4),
+                                       "frac_of_8TBps": round(wl.weight_bytes / med / 1e3 / 8000.0, 4)}
+        res["plan"] = SkinnyGemm(seg_outs, widths, w_scale=scales).describe(wl.k, *sets[0])
+        out[name] = res
+        del sets
+        torch.cuda.empty_cache()
+    return out
+
+
+def cpu_baseline(m, k, sample_cols, seed=11):
+    """The unfused chain on the host cores over the first `sample_cols` columns of the head."""
+    import numpy as np
+
+    from oracle import cpu as C
+    from qwen38_flash_ops_b200 import packing as P
+
+    rng = np.random.default_rng(seed)
+    x = P.synth_x(rng, m, k)
+    packed = rng.integers(0, 256, (k, sample_cols * 9 // 16), dtype=np.uint8)
+    packed[:, sample_cols // 2:] = rng.integers(0x18, 0x40, (k, sample_cols // 16), dtype=np.uint8)
+    C.chain_f32(2, x, packed[:, :], sample_cols)  # warm-up (thread pool, page faults)
+    t0 = time.perf_counter()
+    logits = C.chain_f32(2, x, packed, sample_cols)
+    C.argmax_rows(0, logits)
+    dt = time.perf_counter() - t0
+    nbytes = k * sample_cols * 9 // 16
+    return {"value": round(nbytes / dt / 1e12, 6), "unit": UNIT, "cores": C.num_threads(), "kind": "port",
+            "sample": f"dequantise + MatMul(FP32 acc) + ArgMax over {sample_cols} of 151936 columns, "
+                      f"M={m}, K={k}: {nbytes / 1e6:.1f} MB of packed weights in {dt * 1e3:.1f} ms",
+            "seconds": round(dt, 4)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from qwen38_flash_ops_b200 import workloads as W
+
+    wl = W.CONFIGS[HEAD]
+    m = args.rows
+    sample_cols = wl.ns[0]
+    runs = []
+    for _ in range(args.warmup):
+        cpu_baseline(m, wl.k, sample_cols)
+    t_all = time.perf_counter()
+    for _ in range(args.steps):
+        runs.append(cpu_baseline(m, wl.k, sample_cols))
+    total = time.perf_counter() - t_all
+    secs = statistics.median(r["seconds"] for r in runs)
+    nbytes = wl.k * sample_cols * 9 // 16
+    value = nbytes / secs / 1e12
+    base = dict(runs[0])
+    base["value"] = round(value, 6)
+    line = {"impl": "reference", "metric": METRIC, "value": round(value, 6), "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(secs * 1e3, 3),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 weights, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": HEAD, "rows": m, "sample_cols": sample_cols,
+                       "note": "each step is the whole head once on the host cores; value = weight bytes / time"},
+            "cpu_baseline": base,
+            "e2e": {"value": round(value, 6), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "wall_s": round(total, 2)}
+    try:
+        line["ref_kernel_sm100a"] = time_reference_gpu_kernels(m)
+    except Exception as exc:  # no GPU, or the reference kernels were never compiled
+        line["ref_kernel_sm100a"] = {"unavailable": str(exc)[:200]}
+    print(json.dumps(line), flush=True)
+
+
+def time_reference_gpu_kernels(m):
+    """The reference project's own kernels (its generic launch configuration) recompiled for
+    sm_100a, on the head workload: SkinnyGemm then ArgmaxRows, as the reference runs them."""
+    import torch
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device")
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import _util as U
+    from qwen38_flash_ops_b200 import workloads as W
+
+    if U.ref_lib() is None:
+        raise RuntimeError("oracle/_ref/libref_kernels.so not built")
+    wl = W.CONFIGS[HEAD]
+    n = wl.ns[0]
+    w, _ = W.make_weight(wl.mode, wl.k, n, seed=1)
+    x = W.make_x(m, wl.k, seed=7)
+
+    def call():
+        y = U.ref_skinny_gemm(x, [w], [2], [n], [None], [1], [n])[0]
+        U.ref_argmax_rows(y)
+
+    ms = time_region(torch, call, 20, 5)
+    us = ms * 1000.0 / 20
+    return {"us_per_call": round(us, 2), "TBps": round(wl.weight_bytes / us / 1e6, 4), "rows": m,
+            "what": "skinny::LaunchT<M,8,256,C,4> + LaunchArgmaxRows, unfused, eager launches"}
+
+
+def run_ours(args):
+    import torch
+
+    from qwen38_flash_ops_b200 import _lib, packing
+    from qwen38_flash_ops_b200 import workloads as W
+    from qwen38_flash_ops_b200.lmhead_shard import ShardedLmHead
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    _lib.load()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+    wl = W.CONFIGS[HEAD]
+    m, k, n_total = args.rows, wl.k, wl.ns[0]
+    c0, c1 = packing.shard_columns(n_total, world)[rank]
+    n_local = c1 - c0
+    shard, _ = W.make_weight(wl.mode, k, n_local, seed=100 + rank)
+    head = ShardedLmHead(shard, n_local, c0)
+    x = W.make_x(m, k, seed=7)
+    if world > 1:
+        dist.broadcast(x, 0)
+    shard_bytes = k * n_local * 9 // 16
+    total_bytes = wl.weight_bytes
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    # kernel-resident timing: inputs already in HBM
+    ms = time_region(torch, lambda: head.step(x), args.steps, args.warmup, dist)
+    clocks = sampler.stop() if rank == 0 else None
+    us_step = ms * 1000.0 / args.steps
+    value = total_bytes / us_step / 1e6
+
+    # the fused kernel alone on this rank (no collective): the roofline figure
+    ms_k = time_region(torch, lambda: head.head(x, shard, n_local, col_offset=c0, out=head_out(head, m, torch)),
+                       args.steps, args.warmup, dist)
+    us_kernel = ms_k * 1000.0 / args.steps
+
+    # end to end: host x -> device, fused head (+ all-gather + fold), index and value back to the host
+    x_host = x.cpu().pin_memory()
+    x_dev = torch.empty_like(x)
+    idx_host = torch.empty(m, dtype=torch.int64).pin_memory()
+    val_host = torch.empty(m, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        idx, val = head.step(x_dev)
+        idx_host.copy_(idx, non_blocking=True)
+        val_host.copy_(val, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    ms_e = time_region(torch, e2e_step, args.steps, args.warmup, dist)
+    us_e2e = ms_e * 1000.0 / args.steps
+
+    if rank != 0:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = peaks()
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            t = json.load(f).get("SkinnyGemmKernel_nvfp4_lmhead")
+            if t:
+                traffic = t["dram_bytes_per_weight_byte"] * shard_bytes
+    line = {
+        "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(us_step / 1000.0, 6), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 weights, f16 x f16 -> f32 mma", "data": "synthetic",
+        "config": {"workload": HEAD, "rows": m, "k": k, "n": n_total, "weight_bytes": total_bytes,
+                   "parallelism": f"vocab-sharded x{world}" if world > 1 else "single GPU",
+                   "l2": "inputs larger than L2 (437.6 MB of weights per step" +
+                         (f", {shard_bytes / 1e6:.1f} MB per rank)" if world > 1 else ")"),
+                   "plan": describe_plan(head, k, shard)},
+        "us_per_call": round(us_step, 2),
+        "frac_of_8TBps": round(value / 8.0 / world, 4),
+        "roofline": {"bound": "hbm", "achieved": round(shard_bytes / us_kernel / 1e3, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(shard_bytes / us_kernel / 1e3 / peak, 4), "traffic": traffic,
+                     "peak_source": f"{peak_kind} copy bandwidth", "kernel": "SkinnyGemmKernel<NVFP4> (fused argmax)",
+                     "kernel_us": round(us_kernel, 2), "algorithmic_bytes": shard_bytes},
+        "e2e": {"value": round(total_bytes / us_e2e / 1e6, 4), "unit": UNIT, "h2d_bytes_per_step": x.numel() * 2,
+                "d2h_bytes_per_step": m * 12, "us_per_step": round(us_e2e, 2)},
+        "gpu_launches": args.steps * (1 if world == 1 else 2),
+        "clocks": clocks,
+    }
+    if world == 1 and not args.skip_cpu:
+        line["cpu_baseline"] = cpu_baseline(m, k, n_total)
+    if world == 1 and not args.headline_only:
+        line["all_configs"] = bench_small_configs(torch, quick=args.quick)
+        per_m = {}
+        for mm in (1, 2, 4):
+            xm = W.make_x(mm, k, seed=7)
+            outm = head_out(head, mm, torch)
+            msm = time_region(torch, lambda: head.head(xm, shard, n_local, col_offset=c0, out=outm), args.steps,
+                              args.warmup)
+            usm = msm * 1000.0 / args.steps
+            per_m[f"M{mm}"] = {"us": round(usm, 2), "GBps": round(shard_bytes / usm / 1e3, 1),
+                               "frac_of_measured_hbm": round(shard_bytes / usm / 1e3 / peak, 4),
+                               "frac_of_8TBps": round(shard_bytes / usm / 1e3 / 8000.0, 4)}
+        line["all_configs"][HEAD] = per_m
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+_OUT_CACHE = {}
+
+
+def head_out(head, m, torch):
+    if m not in _OUT_CACHE:
+        _OUT_CACHE[m] = (torch.empty(m, dtype=torch.int64, device="cuda"),
+                         torch.empty(m, dtype=torch.float32, device="cuda"),
+                         torch.empty(m, dtype=torch.int64, device="cuda"))
+    return _OUT_CACHE[m]
+
+
+def describe_plan(head, k, shard):
+    from qwen38_flash_ops_b200 import _lib
+
+    n = shard.shape[1] * 16 // 9
+    align = 16 if (shard.data_ptr() % 16 == 0 and shard.shape[1] % 16 == 0) else 8 if shard.shape[1] % 8 == 0 else 4
+    p = _lib.plan_describe(_lib.QFG_UINT8, k, [n], align)
+    return ",".join(f"{a}={b}" for a, b in p.items() if a != "seg_tiles")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=4, help="rows of x per step (1-4 in the benchmark)")
+    ap.add_argument("--headline-only", action="store_true", help="skip the C1-C4 sweep")
+    ap.add_argument("--quick", action="store_true", help="fewer weight copies in the C1-C4 sweep")
+    ap.add_argument("--skip-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        if args.steps > 20:
+            args.steps = 20
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -128,6 +128,13 @@ Plan ChoosePlan(const PlanInput& in) {
       p.wk = 8 / wn;
       p.cluster = c;
       p.gran = gran;
+      // the K slice of eight x rows must fit beside a minimal ring, whatever the row count of a call
+      {
+        Plan probe = p;
+        probe.ks = 1;
+        probe.stages = 3;
+        if (c < 8 && SmemBytes(probe, in.mode, kMaxRows, in.K) > 200 * 1024) continue;
+      }
       const int max_cols = wn * g.cols_per_warp;
       const int min_tiles = MinTiles(in, max_cols, gran);
       int tiles = std::max(min_tiles, target / c);

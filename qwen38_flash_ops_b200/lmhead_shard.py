@@ -1,0 +1,86 @@
+"""N-column sharding of the fused LM head over the GPUs of one node.
+
+Every rank holds its own re-packed NVFP4 shard `[K, 9 * N_r / 16]` (a column shard is not a
+contiguous slice of the packed tensor, see packing.nvfp4_column_slice) and the replicated
+activations.  One step is: the fused SkinnyGemm + ArgmaxRows kernel over the local columns,
+which emits per row a 64-bit key ordering (value, global index) pairs exactly like ArgmaxRows;
+one all-gather of those keys (8 bytes per row per rank, over NCCL / NVLink on GPUs); a fold of
+the gathered keys.  Larger key = better pair: larger value, then lower index; NaN above all.
+
+The reference has no distributed code; this is the sharding BASELINE's LM-head case asks for.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import packing
+
+
+def pack_key(val: np.ndarray, idx: np.ndarray) -> np.ndarray:
+    """Host restatement of the key the kernel emits, for checking gathered payloads."""
+    v = np.asarray(val, dtype=np.float32).copy()
+    v[v == 0] = 0.0  # -0 and +0 compare equal
+    b = v.view(np.uint32).astype(np.uint64)
+    ord_ = np.where(b & 0x80000000, (~b) & 0xFFFFFFFF, b | 0x80000000)
+    ord_ = np.where(np.isnan(v), np.uint64(0xFFFFFFFF), ord_)
+    return (ord_.astype(np.uint64) << np.uint64(32)) | (np.uint64(0xFFFFFFFF) - np.asarray(idx, dtype=np.uint64))
+
+
+def unpack_key(key: np.ndarray):
+    key = np.asarray(key).view(np.uint64) if np.asarray(key).dtype != np.uint64 else np.asarray(key)
+    ord_ = (key >> np.uint64(32)).astype(np.uint32)
+    bits = np.where(ord_ & 0x80000000, ord_ & 0x7FFFFFFF, ~ord_).astype(np.uint32)
+    bits = np.where(ord_ == 0xFFFFFFFF, np.uint32(0x7FC00000), bits)
+    idx = (np.uint64(0xFFFFFFFF) - (key & np.uint64(0xFFFFFFFF))).astype(np.int64)
+    return bits.view(np.float32), idx
+
+
+def fold_keys_host(keys: np.ndarray):
+    """[ranks, m] gathered keys -> (idx, val); the host mirror of the device fold."""
+    best = np.asarray(keys).view(np.uint64).reshape(keys.shape).max(axis=0)
+    val, idx = unpack_key(best)
+    return idx, val
+
+
+class ShardedLmHead:
+    """One rank of the N-sharded LM head.
+
+    `shard` is this rank's packed weight (CUDA uint8 tensor [K, 9 * n_local / 16]) covering global
+    columns [col_begin, col_begin + n_local).  `group` is a torch.distributed process group (NCCL
+    for CUDA tensors); with world size 1 no collective is issued.
+    """
+
+    def __init__(self, shard, n_local: int, col_begin: int, group=None, w_scale=None):
+        import torch
+        import torch.distributed as dist
+
+        from .ops import LmHeadArgmax
+
+        self.shard = shard
+        self.n_local = int(n_local)
+        self.col_begin = int(col_begin)
+        self.group = group
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.head = LmHeadArgmax(w_scale=w_scale, device=shard.device)
+        self._torch = torch
+        self._dist = dist
+        self._gathered = None
+
+    @staticmethod
+    def column_range(n_total: int, rank: int, world: int, granule: int = 128):
+        return packing.shard_columns(n_total, world, granule)[rank]
+
+    def step(self, x):
+        """x: BF16 [m, K] on this rank's GPU (replicated).  Returns (idx int64 [m], val float32 [m]),
+        identical on every rank."""
+        from .ops import lmhead_combine
+
+        torch = self._torch
+        idx, val, key = self.head(x, self.shard, self.n_local, col_offset=self.col_begin)
+        if self.world == 1:
+            return idx, val
+        m = key.numel()
+        if self._gathered is None or self._gathered.numel() != self.world * m:
+            self._gathered = torch.empty(self.world * m, dtype=torch.int64, device=key.device)
+        self._dist.all_gather_into_tensor(self._gathered, key, group=self.group)
+        return lmhead_combine(self._gathered, self.world, m)

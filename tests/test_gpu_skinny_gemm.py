@@ -1,0 +1,302 @@
+"""GPU parity of SkinnyGemm through the C ABI against the CPU oracle (and, where it was built,
+against the reference project's own kernels recompiled for sm_100a).
+
+Tolerance: every output within one BF16 ULP (relative 2^-7) of the FP32-accumulated reference,
+plus the accumulation-order term K * 2^-24 * sum|x*w| that any FP32 accumulation is subject to;
+the literal 2^-7 criterion is additionally asserted on outputs that do not cancel."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import bits, to_dev
+from oracle import cpu as C
+from oracle import oracle as O
+from qwen38_flash_ops_b200 import QfgError, SkinnyGemm, _lib
+from qwen38_flash_ops_b200 import packing as P
+from qwen38_flash_ops_b200 import packing_torch as PT
+
+import _util as U
+
+pytestmark = pytest.mark.gpu
+
+
+def run_case(rng, mode, M, K, seg_widths, with_scale=None, plan=None, force_slow=False, x_bits=None):
+    """seg_widths: list (per weight) of lists of output widths."""
+    seg_outs = [len(w) for w in seg_widths]
+    widths = [w for ws in seg_widths for w in ws]
+    ns = [sum(ws) for ws in seg_widths]
+    x = P.synth_x(rng, M, K) if x_bits is None else x_bits
+    stored, scales = [], []
+    for n in ns:
+        arr, s = U.make_weight(rng, mode, K, n, with_scale)
+        stored.append(arr)
+        scales.append(s)
+    w_scale = None
+    if any(s is not None for s in scales):
+        w_scale = np.concatenate([s if s is not None else np.ones(n, np.float32) for s, n in zip(scales, ns)])
+    op = SkinnyGemm(seg_outs, widths, w_scale=w_scale)
+    if plan:
+        op.set_option("plan", plan)
+    if force_slow:
+        op.set_option("force_slow", 1)
+    outs = op(to_dev(x, "bf16"), *[U.dev_weight(a, mode) for a in stored])
+    torch.cuda.synchronize()
+    o = 0
+    exact = []
+    for i, n in enumerate(ns):
+        got = np.concatenate([bits(outs[o + j]).reshape(M, -1) for j in range(seg_outs[i])], axis=1)
+        s = scales[i] if w_scale is not None and mode != 0 else None
+        exact.append(U.check_against_oracle(mode, x, stored[i], n, s, got, K, f"mode{mode} M{M} K{K} seg{i}"))
+        o += seg_outs[i]
+    return outs, exact
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+def test_small_shapes(cuda, mode, M):
+    rng = np.random.default_rng(100 * mode + M)
+    run_case(rng, mode, M, 256, [[128]])
+    run_case(rng, mode, M, 256, [[64, 64]], with_scale=True)          # the reference test's split (one weight, two outputs)
+    run_case(rng, mode, M, 1040, [[192], [64, 128, 64]], with_scale=True)  # two weights, four outputs
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_ragged_shapes(cuda, mode):
+    rng = np.random.default_rng(7 + mode)
+    n_odd = 192 if mode == 2 else 132          # NVFP4 needs N % 64 == 0; the others N % 4 == 0
+    run_case(rng, mode, 2, 250, [[n_odd]])     # K even but not a multiple of 16
+    run_case(rng, mode, 3, 34, [[64]])         # K smaller than one stage
+    run_case(rng, mode, 1, 2, [[64]])
+    if mode != 2:
+        run_case(rng, mode, 4, 320, [[4]])     # the reference's 4-column segment
+        run_case(rng, mode, 2, 512, [[324 - 4], [4]])
+    run_case(rng, mode, 5, 512, [[320]])       # more than four rows in one pass
+    run_case(rng, mode, 8, 512, [[320]])
+    run_case(rng, mode, 11, 512, [[320]])      # two passes of eight and three rows
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("plan", ["wn=1,wk=8,cluster=1", "wn=2,wk=4,cluster=2,ctas=6", "wn=4,wk=2,cluster=4,stages=3",
+                                  "wn=8,wk=1,cluster=8,ks=2,stages=5", "wn=2,wk=2,cluster=1,ks=3,stages=2",
+                                  "wn=4,wk=1,cluster=2,ctas=40"])
+def test_every_plan_shape(cuda, mode, plan):
+    rng = np.random.default_rng(sum(map(ord, plan)) + mode)
+    run_case(rng, mode, 3, 2304, [[1280, 256], [512]], with_scale=True, plan=plan)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_row_independence_and_determinism(cuda, mode):
+    """Row r of an M-row call is bit-identical to the one-row call on that row, and a repeated
+    call is bit-identical to the first."""
+    rng = np.random.default_rng(40 + mode)
+    K, N = 1536, 640
+    arr, s = U.make_weight(rng, mode, K, N, True)
+    x = P.synth_x(rng, 8, K)
+    # make the rows differ in scale by orders of magnitude (row-wise power-of-two prescale)
+    xf = O.bf16_to_f32(x)
+    xf *= np.array([1, 1e-3, 300, 1, 2e4, 1e-6, 1, 1], np.float32)[:, None]
+    x = P.f32_to_bf16_bits(xf)
+    op = SkinnyGemm([1], [N], w_scale=s if mode != 0 else None)
+    w = U.dev_weight(arr, mode)
+    full = bits(op(to_dev(x, "bf16"), w)[0])
+    again = bits(op(to_dev(x, "bf16"), w)[0])
+    assert np.array_equal(full, again)
+    for M in (1, 2, 4):
+        part = bits(op(to_dev(x[:M], "bf16"), w)[0])
+        assert np.array_equal(part, full[:M]), f"M={M} differs from the 8-row call"
+    for r in range(8):
+        one = bits(op(to_dev(x[r:r + 1], "bf16"), w)[0])
+        assert np.array_equal(one[0], full[r]), f"row {r} differs from its one-row call"
+    U.check_against_oracle(mode, x, arr, N, s if mode != 0 else None, full, K, "row-scaled")
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_wide_dynamic_range_takes_bf16_path(cuda, mode):
+    """x whose K slice spans more than 2^28 is not exactly representable in FP16 after the
+    power-of-two prescale; the CTA then runs the BF16 MMA on exact BF16 operands.  Both paths
+    must satisfy the tolerance; on ordinary inputs they must agree bit for bit."""
+    rng = np.random.default_rng(50 + mode)
+    K, N = 1024, 384
+    arr, s = U.make_weight(rng, mode, K, N, True)
+    x = O.bf16_to_f32(P.synth_x(rng, 2, K))
+    x[0, 5] = 3e30
+    x[0, 6] = 1e-30
+    x[1, 100] = np.float32(2.0 ** -120)
+    xb = P.f32_to_bf16_bits(x)
+    op = SkinnyGemm([1], [N], w_scale=s)
+    w = U.dev_weight(arr, mode)
+    got = bits(op(to_dev(xb, "bf16"), w)[0])
+    U.check_against_oracle(mode, xb, arr, N, s, got, K, "wide range")
+    # inf / nan inputs propagate like IEEE arithmetic
+    x2 = O.bf16_to_f32(P.synth_x(rng, 2, K))
+    x2[0, 3] = np.inf
+    x2[1, 4] = np.nan
+    xb2 = P.f32_to_bf16_bits(x2)
+    got2 = O.bf16_to_f32(bits(op(to_dev(xb2, "bf16"), w)[0]))
+    ref2, _, _ = C.skinny_gemm(mode, xb2, arr, N, s)
+    ref2 = O.bf16_to_f32(ref2)
+    assert np.array_equal(np.isnan(got2), np.isnan(ref2))
+    assert np.array_equal(np.isinf(got2), np.isinf(ref2))
+    # ordinary inputs: forced BF16 path == FP16 path
+    xo = P.synth_x(rng, 4, K)
+    fast = bits(op(to_dev(xo, "bf16"), w)[0])
+    op.set_option("force_slow", 1)
+    slow = bits(op(to_dev(xo, "bf16"), w)[0])
+    U.check_against_oracle(mode, xo, arr, N, s, slow, K, "forced bf16 path")
+    assert np.array_equal(fast, slow), f"{np.count_nonzero(fast != slow)} outputs differ between the two MMA paths"
+
+
+def test_guard_bands_untouched(cuda):
+    rng = np.random.default_rng(60)
+    K, widths = 512, [64, 192, 64]
+    for mode in (0, 1, 2):
+        arr, s = U.make_weight(rng, mode, K, sum(widths), True)
+        for M in (1, 4, 7):
+            x = P.synth_x(rng, M, K)
+            pad = 64
+            bufs = [torch.full((M * w + 2 * pad,), -12851, dtype=torch.int16, device="cuda") for w in widths]  # 0xCDCD
+            outs = [b[pad:pad + M * w].view(torch.bfloat16).view(M, w) for b, w in zip(bufs, widths)]
+            op = SkinnyGemm([3], widths, w_scale=s if mode != 0 else None)
+            op(to_dev(x, "bf16"), U.dev_weight(arr, mode), out=outs)
+            torch.cuda.synchronize()
+            for b, w in zip(bufs, widths):
+                h = b.cpu().numpy()
+                assert np.all(h[:pad] == -12851) and np.all(h[pad + M * w:] == -12851)
+            got = np.concatenate([bits(o) for o in outs], axis=1)
+            U.check_against_oracle(mode, x, arr, sum(widths), s if mode != 0 else None, got, K, "guard")
+
+
+@pytest.mark.parametrize("trigger,pdl_wait", [(0, 0), (1, 0), (2, 0), (1, 1), (2, 1)])
+def test_cuda_graph_capture_and_pdl(cuda, trigger, pdl_wait):
+    """The compute call is capturable; replaying the graph gives the eager result.  With the
+    PDL trigger set, a chain of dependent calls (each consuming the previous output as x) stays
+    correct when the kernels are launched with programmatic stream serialisation."""
+    rng = np.random.default_rng(70)
+    K = N = 512
+    arr, _ = U.make_weight(rng, 2, K, N)
+    w = U.dev_weight(arr, 2)
+    x0 = to_dev(P.synth_x(rng, 4, K), "bf16")
+    op = SkinnyGemm([1], [N], trigger=trigger)
+    op.set_option("pdl_wait", pdl_wait)
+    plain = SkinnyGemm([1], [N])
+
+    def chain(o, x):
+        y1 = o(x, w)[0]
+        y2 = o(y1, w)[0]
+        return o(y2, w)[0]
+
+    expect = bits(chain(plain, x0))
+    eager = bits(chain(op, x0))
+    assert np.array_equal(eager, expect)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        chain(op, x0)  # warm-up on the capture stream
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            y = chain(op, x0)
+        for _ in range(3):
+            g.replay()
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(y), expect)
+
+
+def test_argument_errors(cuda):
+    rng = np.random.default_rng(80)
+    K, N = 256, 128
+    x = to_dev(P.synth_x(rng, 2, K), "bf16")
+    wb = U.dev_weight(P.f32_to_bf16_bits(P.synth_weight(rng, K, N)), 0)
+    op = SkinnyGemm([1], [N])
+    with pytest.raises(QfgError) as e:
+        op(x, wb, wb)                                   # input count
+    assert e.value.code == _lib.QFG_INVALID_ARGUMENT
+    with pytest.raises(QfgError):
+        op(x[:, :254].contiguous(), wb)                 # weight rows != K
+    with pytest.raises(QfgError):
+        SkinnyGemm([1], [N - 4])(x, wb)                 # widths do not add up to N
+    with pytest.raises(QfgError):
+        SkinnyGemm([1], [130])(x, U.dev_weight(np.zeros((K, 130), np.uint16), 0))   # N % 4
+    with pytest.raises(QfgError):
+        SkinnyGemm([1], [N])(x, torch.zeros((K, N * 9 // 16 + 1), dtype=torch.uint8, device="cuda"))
+    with pytest.raises(QfgError):
+        SkinnyGemm([1], [48])(x, torch.zeros((K, 27), dtype=torch.uint8, device="cuda"))  # NVFP4 N % 64
+    with pytest.raises(QfgError):
+        SkinnyGemm([1], [N])(x, torch.zeros((K, N), dtype=torch.float32, device="cuda"))   # element type
+    with pytest.raises(QfgError):
+        SkinnyGemm([1, 1], [N, N])(x, wb, U.dev_weight(np.zeros((K, N), np.uint8), 1))     # mixed types
+    xo = to_dev(P.synth_x(rng, 2, 255), "bf16")
+    with pytest.raises(QfgError):
+        SkinnyGemm([1], [N])(xo, U.dev_weight(np.zeros((255, N), np.uint16), 0))           # odd K
+    # after all those refusals the op still works
+    y = op(x, wb)[0]
+    torch.cuda.synchronize()
+    assert y.shape == (2, N)
+
+
+CONFIGS = {
+    # name: (mode, M, K, seg widths)
+    "C1_bf16": (0, 1, 5120, [[5120]]),
+    "C2_fp8_qkv": (1, 2, 5120, [[8192], [1024], [1024]]),
+    "C3_nvfp4_gate_up": (2, 1, 5120, [[17408], [17408]]),
+    "C4_nvfp4_down": (2, 4, 17408, [[5120]]),
+}
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_baseline_configs_full_size(cuda, name):
+    """The benchmark configurations at full size: weights generated and packed on the GPU, the C
+    oracle (FP64 accumulation, all host cores) as the checker, plus the reference kernels."""
+    mode, M, K, seg_widths = CONFIGS[name]
+    gen = torch.Generator(device="cuda").manual_seed(0x5EED0000 + len(name))
+    rng = np.random.default_rng(0x5EED0000 + len(name))
+    x = P.synth_x(rng, M, K)
+    xd = to_dev(x, "bf16")
+    ws, scales, ns = [], [], []
+    for wsz in seg_widths:
+        n = sum(wsz)
+        w = torch.randn(K, n, generator=gen, device="cuda") * 0.02
+        if mode == 0:
+            ws.append(w.bfloat16())
+            scales.append(None)
+        elif mode == 1:
+            q, s = PT.quantize_fp8_per_column_torch(w)
+            ws.append(q)
+            scales.append(s)
+        else:
+            ws.append(PT.pack_nvfp4_torch(w))
+            scales.append(None)
+        ns.append(n)
+        del w
+    w_scale = torch.cat(scales).cpu().numpy() if mode == 1 else None
+    seg_outs = [len(w) for w in seg_widths]
+    widths = [w for wsz in seg_widths for w in wsz]
+    op = SkinnyGemm(seg_outs, widths, w_scale=w_scale, trigger=2 if name.startswith("C4") else 0)
+    outs = op(xd, *ws)
+    torch.cuda.synchronize()
+    for i, n in enumerate(ns):
+        host = ws[i].view(torch.uint8).cpu().numpy() if mode != 0 else bits(ws[i])
+        s = scales[i].cpu().numpy() if scales[i] is not None else None
+        U.check_against_oracle(mode, x, host, n, s, bits(outs[i]), K, f"{name} seg{i}")
+    if U.ref_lib() is not None:
+        r = U.ref_skinny_gemm(xd, ws, [mode] * len(ws), ns, scales, seg_outs, widths)
+        torch.cuda.synchronize()
+        for a, b in zip(outs, r):
+            d = np.abs(bits(a).astype(np.int32) - bits(b).astype(np.int32))
+            assert np.mean(d <= 1) > 0.999, f"{name}: differs from the reference kernel by more than one BF16 ULP"
+
+
+def test_linearity_at_full_size(cuda):
+    """Size-independent property at a benchmark size: y(x with one element doubled) - y(x) equals
+    that element times the weight row, exactly representable here, within the output rounding."""
+    K, N = 5120, 17408
+    gen = torch.Generator(device="cuda").manual_seed(99)
+    pk = PT.pack_nvfp4_torch(torch.randn(K, N, generator=gen, device="cuda") * 0.02)
+    op = SkinnyGemm([1], [N])
+    x = torch.zeros(2, K, dtype=torch.bfloat16, device="cuda")
+    x[0, 1234] = 1.0
+    x[1, 4321] = -2.0
+    y = op(x, pk)[0].float().cpu().numpy()
+    host = pk.cpu().numpy()
+    rows = O.decode_weights_exact(2, host[[1234, 4321]], N)
+    assert np.array_equal(y[0], rows[0])      # one-hot x reads back the dequantised row exactly
+    assert np.array_equal(y[1], -2.0 * rows[1])
