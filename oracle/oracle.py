@@ -47,7 +47,13 @@ def f32_to_bf16(x: np.ndarray) -> np.ndarray:
 
 
 def f16_to_f32(bits: np.ndarray) -> np.ndarray:
-    return np.asarray(bits, dtype=np.uint16).view(np.float16).astype(np.float32)
+    """FP16 bits -> float32; a NaN becomes the canonical 0x7FFFFFFF that cvt.f32.f16 (the
+    `__half2float` of argmax_rows.cuh:35) returns whatever the payload."""
+    h = np.asarray(bits, dtype=np.uint16).view(np.float16)
+    f = h.astype(np.float32)
+    u = f.view(np.uint32).copy()
+    u[np.isnan(h)] = 0x7FFFFFFF
+    return u.view(np.float32)
 
 
 def _e4m3fn_table() -> np.ndarray:
@@ -154,9 +160,6 @@ def skinny_gemm(x_bits: np.ndarray, weights, seg_outs, widths, w_scale=None, col
             scale_off += n
         acc = np.empty((M, n), dtype=np.float64)
         mag = np.empty((M, n), dtype=np.float64)
-        wv_all = None
-        if mode == MODE_NVFP4:
-            wv_all = None  # decoded per block below to bound memory
         for c0 in range(0, n, col_block):
             c1 = min(n, c0 + col_block)
             if mode == MODE_BF16:

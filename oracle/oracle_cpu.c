@@ -67,7 +67,12 @@ static inline float f16_to_f32(uint16_t h) {
   if (e == 0) {
     v = ldexpf((float)m, -24);
   } else if (e == 31) {
-    v = m ? NAN : INFINITY;
+    if (m) { /* cvt.f32.f16 returns the canonical NaN 0x7FFFFFFF whatever the payload */
+      const uint32_t canon = 0x7FFFFFFFu;
+      memcpy(&v, &canon, 4);
+      return v;
+    }
+    v = INFINITY;
   } else {
     v = ldexpf(1.0f + (float)m / 1024.0f, e - 15);
   }

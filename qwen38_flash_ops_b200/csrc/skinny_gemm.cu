@@ -659,9 +659,23 @@ __global__ void __launch_bounds__(kMaxThreads, 2) SkinnyGemmKernel(const GemmPar
   }
 }
 
+// Largest dynamic shared-memory request any of the kernels accepts: the opt-in limit of the
+// device minus the kernel's static shared memory.
+int g_max_dynamic_smem = 0;
+
 template <int MODE>
 cudaError_t ConfigureKernel() {
-  return cudaFuncSetAttribute(SkinnyGemmKernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  int dev = 0, optin = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  err = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  if (err != cudaSuccess) return err;
+  cudaFuncAttributes fa;
+  err = cudaFuncGetAttributes(&fa, SkinnyGemmKernel<MODE>);
+  if (err != cudaSuccess) return err;
+  const int dyn = optin - static_cast<int>(fa.sharedSizeBytes);
+  if (g_max_dynamic_smem == 0 || dyn < g_max_dynamic_smem) g_max_dynamic_smem = dyn;
+  return cudaFuncSetAttribute(SkinnyGemmKernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn);
 }
 
 template <int MODE>
@@ -735,7 +749,7 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
   const int kslice_max = ((ksteps + plan.cluster - 1) / plan.cluster) * 16;
   p.xpitch = ((kslice_max + 63) & ~63) + 16;  // 32 bytes off a 128-byte multiple: rows land in distinct banks
   const size_t smem = static_cast<size_t>(p.ring_bytes) + static_cast<size_t>(p.M) * p.xpitch * 2;
-  if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
+  if (g_max_dynamic_smem > 0 && smem > static_cast<size_t>(g_max_dynamic_smem)) return cudaErrorInvalidConfiguration;
   int tiles = 0;
   for (int s = 0; s < p.nseg; ++s) {
     p.seg[s].tile_begin = tiles;
