@@ -414,6 +414,43 @@ def describe_plan(head, k, shard):
     return ",".join(f"{a}={b}" for a, b in p.items() if a != "seg_tiles")
 
 
+def run_profile_case(args):
+    """A few plain calls of one workload, for `ncu` (small launch count, no timing loop):
+    python bench.py --profile-case C3_nvfp4_gate_up_5120x34816 --iters 3 [--rows M] [--copies C]"""
+    import torch
+
+    from qwen38_flash_ops_b200 import LmHeadArgmax, SkinnyGemm
+    from qwen38_flash_ops_b200 import workloads as W
+
+    wl = W.CONFIGS[args.profile_case]
+    m = args.rows if args.rows else wl.m
+    sets, scales = [], None
+    for c in range(args.copies):
+        ws, sc = [], []
+        for i, n in enumerate(wl.ns):
+            w, s_ = W.make_weight(wl.mode, wl.k, n, seed=1000 * c + i)
+            ws.append(w)
+            sc.append(s_)
+        sets.append(ws)
+        if c == 0 and wl.mode == W.MODE_FP8:
+            scales = torch.cat(sc).cpu().numpy()
+    x = W.make_x(m, wl.k, seed=7)
+    if wl.fused_argmax:
+        op = LmHeadArgmax()
+        call = lambda i: op(x, sets[i % args.copies][0], wl.ns[0])
+    else:
+        seg_outs = [len(w) for w in wl.seg_widths]
+        widths = [w for ws_ in wl.seg_widths for w in ws_]
+        op = SkinnyGemm(seg_outs, widths, w_scale=scales, trigger=wl.trigger)
+        call = lambda i: op(x, *sets[i % args.copies])
+    torch.cuda.synchronize()
+    for i in range(args.iters):
+        call(i)
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": args.profile_case, "rows": m, "iters": args.iters, "copies": args.copies,
+                      "weight_bytes": wl.weight_bytes}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -424,7 +461,15 @@ def main():
     ap.add_argument("--headline-only", action="store_true", help="skip the C1-C4 sweep")
     ap.add_argument("--quick", action="store_true", help="fewer weight copies in the C1-C4 sweep")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--profile-case", default=None, help="run a few plain calls of this workload (for ncu) and exit")
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--copies", type=int, default=3, help="weight copies rotated through by --profile-case")
     args = ap.parse_args()
+    if args.profile_case:
+        if "--rows" not in sys.argv:
+            args.rows = 0
+        run_profile_case(args)
+        return
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

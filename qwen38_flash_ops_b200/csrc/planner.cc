@@ -19,10 +19,21 @@ namespace {
 
 double BytesPerCol(int mode) { return mode == kBf16 ? 2.0 : mode == kFp8 ? 1.0 : 0.5; }
 
-int Granule(int mode, int row_align) {
+int Granule(int mode, int row_align, bool direct) {
   const ModeGeom g = GeomOf(mode);
+  if (direct) return g.cols_per_thread;  // a thread's chunk is one aligned 8/16-byte load
   const int cols_per_vec = static_cast<int>(row_align / BytesPerCol(mode));
   return std::max(g.cols_per_thread, cols_per_vec);
+}
+
+// The register-streaming kernel needs whole thread chunks and rows aligned to its load width.
+bool DirectEligible(const PlanInput& in) {
+  const ModeGeom g = GeomOf(in.mode);
+  if (in.row_align < g.bytes_per_thread) return false;
+  for (int s = 0; s < in.nseg; ++s) {
+    if (in.n[s] % g.cols_per_thread != 0) return false;
+  }
+  return true;
 }
 
 int MinTiles(const PlanInput& in, int max_cols, int gran) {
@@ -43,7 +54,7 @@ int MinTiles(const PlanInput& in, int max_cols, int gran) {
 // increasing order), so unlike the rest of the plan they may depend on the row count.
 void FitRing(const PlanInput& in, int rows, Plan* p) {
   const ModeGeom g = GeomOf(in.mode);
-  const int tb = p->wn * g.bytes_per_warp + (in.mode == kNvfp4 ? p->wn * 8 + 16 : 0);
+  const int tb = p->wn * g.bytes_per_warp + (in.mode == kNvfp4 ? (p->wn * 8 + 16 + 15) & ~15 : 0);
   // stages of about 8 KiB, ring of about 64 KiB
   p->ks = std::min(4, std::max(1, 8192 / (16 * p->wk * tb)));
   const int stage = 16 * p->wk * p->ks * tb;
@@ -56,11 +67,11 @@ void FitRing(const PlanInput& in, int rows, Plan* p) {
 size_t SmemBytes(const Plan& plan, int mode, int rows, int K) {
   const ModeGeom g = GeomOf(mode);
   const int tb = plan.wn * g.bytes_per_warp;
-  const int srb = mode == kNvfp4 ? plan.wn * 8 + 16 : 0;
+  const int srb = mode == kNvfp4 ? (plan.wn * 8 + 16 + 15) & ~15 : 0;
   const int stage = (plan.rows_per_stage() * (tb + srb) + 127) & ~127;
   const int tnc = plan.wn * g.cols_per_warp;
   const int red = (plan.wk + (plan.cluster > 1 ? 1 : 0)) * rows * tnc * 4;
-  const int ring = (std::max(plan.stages * stage, red) + 127) & ~127;
+  const int ring = (std::max(plan.direct ? 0 : plan.stages * stage, red) + 127) & ~127;
   const int ksteps = (K + 15) / 16;
   const int kslice = ((ksteps + plan.cluster - 1) / plan.cluster) * 16;
   const int xpitch = ((kslice + 63) & ~63) + 16;
@@ -109,52 +120,69 @@ void DistributeTiles(const PlanInput& in, int total_tiles, Plan* plan) {
   for (int s = in.nseg; s < kMaxSeg; ++s) plan->tiles[s] = 0;
 }
 
+// Candidate launch shapes are scored by how much of the machine they keep busy:
+//   lane efficiency  - columns a CTA can hold versus columns its tile actually has;
+//   balance          - CTAs versus the resident CTA slots of whole waves (16 warps per SM);
+//   pipeline length  - k-steps per warp, so that fill and drain of the load pipeline amortise;
+//   row width        - contiguous bytes a CTA reads per weight row.
 Plan ChoosePlan(const PlanInput& in) {
   const ModeGeom g = GeomOf(in.mode);
   const double bpc = BytesPerCol(in.mode);
-  const int target = 2 * in.sm_count;
   long long sum_n = 0;
   for (int s = 0; s < in.nseg; ++s) sum_n += in.n[s];
-  const int gran = Granule(in.mode, in.row_align);
+  const bool direct = DirectEligible(in);
+  const int gran = Granule(in.mode, in.row_align, direct);
+  long long granules = 0;
+  for (int s = 0; s < in.nseg; ++s) granules += (in.n[s] + gran - 1) / gran;
+  const int ksteps = (in.K + 15) / 16;
+  const int max_warps = direct ? 16 : 8;
 
   Plan best;
   double best_score = -1.0;
   for (int c = 1; c <= 8; c *= 2) {
     if (c > 1 && in.K / c < 256) continue;
-    for (int wn = 1; wn <= 8; wn *= 2) {
-      if (in.mode == kNvfp4 && wn < 2 && sum_n >= 256) continue;  // 64-byte rows defeat the swizzle
-      Plan p;
-      p.wn = wn;
-      p.wk = 8 / wn;
-      p.cluster = c;
-      p.gran = gran;
-      // the K slice of eight x rows must fit beside a minimal ring, whatever the row count of a call
-      {
-        Plan probe = p;
-        probe.ks = 1;
-        probe.stages = 3;
-        if (c < 8 && SmemBytes(probe, in.mode, kMaxRows, in.K) > 200 * 1024) continue;
-      }
-      const int max_cols = wn * g.cols_per_warp;
-      const int min_tiles = MinTiles(in, max_cols, gran);
-      int tiles = std::max(min_tiles, target / c);
-      long long granules = 0;
-      for (int s = 0; s < in.nseg; ++s) granules += (in.n[s] + gran - 1) / gran;
-      tiles = static_cast<int>(std::min<long long>(tiles, std::max<long long>(granules, 1)));
-      const int ctas = tiles * c;
-      const double width = static_cast<double>(sum_n) / tiles;
-      const double row_bytes = width * bpc;
-      const double lane_eff = static_cast<double>(sum_n) / (static_cast<double>(tiles) * max_cols);
-      const int waves = (ctas + target - 1) / target;
-      const double balance = static_cast<double>(ctas) / (static_cast<double>(waves) * target);
-      const double fill = std::min(1.0, static_cast<double>(ctas) / target);
-      double score = std::min(1.0, row_bytes / 256.0) * (0.5 + 0.5 * lane_eff) * balance * fill;
-      score *= 1.0 - 0.02 * std::log2(static_cast<double>(c));
-      if (waves > 1) score *= 0.8;
-      if (score > best_score) {
-        best_score = score;
-        best = p;
-        DistributeTiles(in, tiles, &best);
+    for (int wn = 1; wn <= 8; ++wn) {
+      if (!direct && (wn & (wn - 1)) != 0) continue;                 // the ring's swizzle wants 2^n warps
+      if (!direct && in.mode == kNvfp4 && wn < 2 && sum_n >= 256) continue;
+      for (int wk = 1; wn * wk <= max_warps; wk *= 2) {
+        Plan p;
+        p.wn = wn;
+        p.wk = wk;
+        p.cluster = c;
+        p.gran = gran;
+        p.direct = direct ? 1 : 0;
+        p.ks = 1;
+        p.stages = 3;
+        // eight x rows must fit beside the partial sums, whatever the row count of a call
+        const size_t smem = SmemBytes(p, in.mode, kMaxRows, in.K);
+        if (smem > 200 * 1024 && c < 8) continue;
+        const int per_sm = std::max(1, std::min(16 / (wn * wk), static_cast<int>((220 * 1024) / std::max<size_t>(smem, 1))));
+        const int slots = per_sm * in.sm_count;
+        const int max_cols = wn * g.cols_per_warp;
+        const int min_tiles = MinTiles(in, max_cols, gran);
+        for (int waves = 1; waves <= 4; ++waves) {
+          int tiles = std::max(min_tiles, waves * slots / c);
+          tiles = static_cast<int>(std::min<long long>(tiles, std::max<long long>(granules, 1)));
+          const int ctas = tiles * c;
+          const int need = (ctas + slots - 1) / slots;
+          const double balance = static_cast<double>(ctas) / (static_cast<double>(need) * slots);
+          const double widest = std::ceil(static_cast<double>(granules) / tiles) * gran;
+          const double lane_eff = std::min(1.0, (static_cast<double>(sum_n) / tiles) / max_cols) *
+                                  ((static_cast<double>(sum_n) / tiles) / std::max(widest, 1.0));
+          const double warps_per_sm = std::min(16.0, static_cast<double>(per_sm * wn * wk));
+          const double steps = static_cast<double>(ksteps) / c / wk / need;
+          const double kfactor = std::min(1.0, steps / 12.0);
+          const double row_bytes = (static_cast<double>(sum_n) / tiles) * bpc;
+          const double rowfactor = std::sqrt(std::min(1.0, row_bytes / 128.0));
+          double score = lane_eff * balance * (warps_per_sm / 16.0) * (0.5 + 0.5 * kfactor) * rowfactor;
+          score *= 1.0 - 0.015 * std::log2(static_cast<double>(c)) - 0.01 * (need - 1);
+          if (score > best_score) {
+            best_score = score;
+            best = p;
+            DistributeTiles(in, tiles, &best);
+          }
+          if (tiles == min_tiles && waves * slots / c <= min_tiles) continue;
+        }
       }
     }
   }
@@ -180,14 +208,18 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
     else if (key == "cluster") plan->cluster = val;
     else if (key == "ctas") ctas = val;
     else if (key == "gran") plan->gran = val;
+    else if (key == "direct") plan->direct = val;
     else return false;
   }
   auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
-  if (!pow2(plan->wn) || !pow2(plan->wk) || plan->wn * plan->wk > 8 || plan->ks < 1 || plan->ks > 8 ||
+  if (plan->direct != 0 && !DirectEligible(in)) return false;
+  plan->direct = plan->direct != 0 ? 1 : 0;
+  if (plan->direct == 0 && plan->gran < Granule(in.mode, in.row_align, false)) plan->gran = Granule(in.mode, in.row_align, false);
+  if ((plan->direct == 0 && !pow2(plan->wn)) || plan->wn < 1 || !pow2(plan->wk) || plan->wn * plan->wk > 16 || plan->wn > 8 || plan->ks < 1 || plan->ks > 8 ||
       plan->stages < 2 || plan->stages > 9 || plan->cluster < 1 || plan->cluster > 8 || !pow2(plan->cluster)) {
     return false;
   }
-  if (plan->gran % Granule(in.mode, in.row_align) != 0) return false;
+  if (plan->gran % Granule(in.mode, in.row_align, plan->direct != 0) != 0) return false;
   if (!ring_given) FitRing(in, in.max_rows, plan);
   const ModeGeom g = GeomOf(in.mode);
   int total = ctas > 0 ? std::max(1, ctas / plan->cluster) : 0;
@@ -205,8 +237,9 @@ std::string DescribePlan(const Plan& plan, const PlanInput& in) {
   int tiles = 0;
   for (int s = 0; s < in.nseg; ++s) tiles += plan.tiles[s];
   std::snprintf(buf, sizeof(buf),
-                "wn=%d,wk=%d,ks=%d,stages=%d,cluster=%d,gran=%d,tiles=%d,ctas=%d,threads=%d,smem=%zu", plan.wn,
-                plan.wk, plan.ks, plan.stages, plan.cluster, plan.gran, tiles, tiles * plan.cluster, plan.threads(),
+                "direct=%d,wn=%d,wk=%d,ks=%d,stages=%d,cluster=%d,gran=%d,tiles=%d,ctas=%d,threads=%d,smem=%zu",
+                plan.direct, plan.wn, plan.wk, plan.ks, plan.stages, plan.cluster, plan.gran, tiles,
+                tiles * plan.cluster, plan.threads(),
                 SmemBytes(plan, in.mode, in.max_rows, in.K));
   return buf;
 }

@@ -43,6 +43,7 @@ struct Plan {
   int cluster = 1;  // CTAs splitting K, reduced through distributed shared memory
   int tiles[kMaxSeg] = {0, 0, 0, 0};  // column tiles per segment
   int gran = 16;    // columns per granule of the balanced column partition
+  int direct = 1;   // 1: warps stream weights straight into registers; 0: cp.async shared-memory ring
   int threads() const { return 32 * wn * wk; }
   int rows_per_stage() const { return 16 * wk * ks; }
 };

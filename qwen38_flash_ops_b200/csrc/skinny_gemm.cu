@@ -1,19 +1,24 @@
 // SkinnyGemm for B200 (sm_100a): y[M, N] = x[M, K] @ W[K, N] for M <= 8 rows, streaming W once.
 //
-// Structure of one CTA (wn x wk warps):
-//   * it owns one column tile of one weight and one 1/cluster slice of K;
-//   * all threads feed a multi-stage shared-memory ring with cp.async (16-byte pieces where the
-//     rows allow it, 8- or 4-byte pieces otherwise), so the bytes in flight per SM are set by the
-//     ring depth and not by registers;
-//   * each warp consumes 16 weight rows x (64 or 128) columns per k-step: a thread reads four
-//     rows of its 8/16 columns from the ring, turns them into k-paired 16-bit operands
-//     (BF16: byte permute; FP8: byte permute + cvt.e4m3x2; NVFP4: nibble interleave +
-//     cvt.e2m1x2 + one packed multiply by the E4M3 block scale) and issues m16n8k16 MMAs with
-//     the weights as the 16-row operand and x (padded to 8 rows) as the 8-column operand.
-//     Every weight and every product is exact; accumulation is FP32;
-//   * partial sums are combined in a fixed order: across the wk warps through shared memory,
-//     then across the CTAs of the cluster through distributed shared memory, then scaled by the
-//     per-column w_scale, rounded once to BF16 and routed to the output that owns the column.
+// A CTA of wn x wk warps owns one column tile of one weight and one 1/cluster slice of K.  A warp
+// consumes 16 weight rows x (64 or 128) columns per k-step: a thread holds four rows of its 8/16
+// columns, turns them into k-paired 16-bit operands (BF16: byte permute; FP8: byte permute +
+// cvt.e4m3x2; NVFP4: nibble interleave + cvt.e2m1x2 + one packed multiply by the E4M3 block
+// scales) and issues m16n8k16 MMAs with the weights as the 16-row operand and x (padded to 8 rows)
+// as the 8-column operand.  Every weight and every product is exact; accumulation is FP32.
+//
+// Two kernels share that arithmetic and differ in how the weight bytes reach the registers:
+//   * SkinnyGemmDirectKernel (the fast path): every warp streams its own rows from HBM straight
+//     into registers with 64/128-bit non-allocating loads, kDepth k-steps ahead of the MMAs.  No
+//     barrier and no shared-memory traffic in the main loop; the bytes in flight per SM are
+//     warps x kDepth x 1-2 KiB.  Needs 16-byte aligned rows (8 for NVFP4) and whole thread chunks.
+//   * SkinnyGemmRingKernel (any 4-byte aligned layout, ragged column tails): all threads feed a
+//     multi-stage shared-memory ring with cp.async pieces of 16, 8 or 4 bytes with zero fill.
+//
+// Partial sums are combined in a fixed order: across the wk warps through shared memory, then
+// across the CTAs of the cluster through distributed shared memory, then scaled by the per-column
+// w_scale, rounded once to BF16 and routed to the output that owns the column.  With `lm` set the
+// epilogue also folds the BF16-rounded values into a per-row (max, index) key (fused LM head).
 //
 // The quantised modes run the MMA in FP16 (the only type cvt.e2m1x2 / cvt.e4m3x2 produce).  x is
 // BF16, so each CTA rescales its K slice of every x row by a power of two that puts the row
@@ -36,7 +41,7 @@ namespace {
 
 namespace cg = cooperative_groups;
 
-constexpr int kMaxThreads = 256;
+constexpr int kMaxThreads = 512;
 
 // ------------------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t SmemAddr(const void* p) {
@@ -77,6 +82,23 @@ __device__ __forceinline__ uint2 Lds64(uint32_t addr) {
 __device__ __forceinline__ uint32_t Lds8(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 Ldg128(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 Ldg64(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t Ldg8(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(v) : "l"(p));
   return v;
 }
 __device__ __forceinline__ uint32_t Prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -165,39 +187,46 @@ template <int MODE>
 struct Geom;
 template <>
 struct Geom<kBf16> {
-  static constexpr int kColsPerThread = 8, kBytesPerThread = 16, kMmas = 4;
+  static constexpr int kColsPerThread = 8, kBytesPerThread = 16, kMmas = 4, kDepth = 4;
 };
 template <>
 struct Geom<kFp8> {
-  static constexpr int kColsPerThread = 16, kBytesPerThread = 16, kMmas = 8;
+  static constexpr int kColsPerThread = 16, kBytesPerThread = 16, kMmas = 8, kDepth = 3;
 };
 template <>
 struct Geom<kNvfp4> {
-  static constexpr int kColsPerThread = 16, kBytesPerThread = 8, kMmas = 8;
+  static constexpr int kColsPerThread = 16, kBytesPerThread = 8, kMmas = 8, kDepth = 4;
 };
 
-// One k-step of one warp: 16 weight rows x the warp's columns.  `w_addr` is the shared-memory
-// address of this thread's bytes in row t of the step (rows t+4, t+8, t+12 follow at
-// 4 * row_bytes), `s_addr` the address of its NVFP4 scale byte in row t.
+// The raw bytes of one k-step of one thread: four consecutive weight rows (4t .. 4t+3 of the
+// step) of its columns, plus the four NVFP4 block-scale bytes.  The B fragment of the same
+// thread is x[4t .. 4t+3] of the step: the k index of an MMA is a free permutation.
+template <int MODE>
+struct Raw {
+  uint4 r[4];
+};
+template <>
+struct Raw<kNvfp4> {
+  uint2 r[4];
+  uint32_t s[4];
+};
+
+// One k-step of one warp from registers: dequantise to k-paired operands and run the MMAs.
 template <int MODE, bool SLOW>
-__device__ __forceinline__ void KStep(float (&acc)[Geom<MODE>::kMmas][4], uint32_t w_addr, uint32_t row4_bytes,
-                                      uint32_t s_addr, uint32_t srow4_bytes, uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void ComputeStep(float (&acc)[Geom<MODE>::kMmas][4], const Raw<MODE>& w, uint32_t b0,
+                                            uint32_t b1) {
   constexpr bool kBf16Mma = (MODE == kBf16) || SLOW;
   if constexpr (MODE == kBf16) {
-    const uint4 ra = Lds128(w_addr), rb = Lds128(w_addr + row4_bytes), rc = Lds128(w_addr + 2 * row4_bytes),
-                rd = Lds128(w_addr + 3 * row4_bytes);
-    const uint32_t a[4] = {ra.x, ra.y, ra.z, ra.w}, b[4] = {rb.x, rb.y, rb.z, rb.w};
-    const uint32_t c[4] = {rc.x, rc.y, rc.z, rc.w}, d[4] = {rd.x, rd.y, rd.z, rd.w};
+    const uint32_t a[4] = {w.r[0].x, w.r[0].y, w.r[0].z, w.r[0].w}, b[4] = {w.r[1].x, w.r[1].y, w.r[1].z, w.r[1].w};
+    const uint32_t c[4] = {w.r[2].x, w.r[2].y, w.r[2].z, w.r[2].w}, d[4] = {w.r[3].x, w.r[3].y, w.r[3].z, w.r[3].w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       Mma<true>(acc[i], Prmt(a[i], b[i], 0x5410u), Prmt(a[i], b[i], 0x7632u), Prmt(c[i], d[i], 0x5410u),
                 Prmt(c[i], d[i], 0x7632u), b0, b1);
     }
   } else if constexpr (MODE == kFp8) {
-    const uint4 ra = Lds128(w_addr), rb = Lds128(w_addr + row4_bytes), rc = Lds128(w_addr + 2 * row4_bytes),
-                rd = Lds128(w_addr + 3 * row4_bytes);
-    const uint32_t a[4] = {ra.x, ra.y, ra.z, ra.w}, b[4] = {rb.x, rb.y, rb.z, rb.w};
-    const uint32_t c[4] = {rc.x, rc.y, rc.z, rc.w}, d[4] = {rd.x, rd.y, rd.z, rd.w};
+    const uint32_t a[4] = {w.r[0].x, w.r[0].y, w.r[0].z, w.r[0].w}, b[4] = {w.r[1].x, w.r[1].y, w.r[1].z, w.r[1].w};
+    const uint32_t c[4] = {w.r[2].x, w.r[2].y, w.r[2].z, w.r[2].w}, d[4] = {w.r[3].x, w.r[3].y, w.r[3].z, w.r[3].w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       uint32_t p[4], q[4];
@@ -216,15 +245,12 @@ __device__ __forceinline__ void KStep(float (&acc)[Geom<MODE>::kMmas][4], uint32
       Mma<kBf16Mma>(acc[2 * i + 1], p[2], p[3], q[2], q[3], b0, b1);
     }
   } else {
-    const uint2 ra = Lds64(w_addr), rb = Lds64(w_addr + row4_bytes), rc = Lds64(w_addr + 2 * row4_bytes),
-                rd = Lds64(w_addr + 3 * row4_bytes);
-    const uint32_t sa = Lds8(s_addr), sb = Lds8(s_addr + srow4_bytes), sc = Lds8(s_addr + 2 * srow4_bytes),
-                   sd = Lds8(s_addr + 3 * srow4_bytes);
-    const uint32_t s_ab = CvtE4m3x2(sa | (sb << 8)), s_cd = CvtE4m3x2(sc | (sd << 8));
-    const uint32_t a[2] = {ra.x, ra.y}, b[2] = {rb.x, rb.y}, c[2] = {rc.x, rc.y}, d[2] = {rd.x, rd.y};
+    const uint32_t s_ab = CvtE4m3x2(Prmt(w.s[0], w.s[1], 0x0040u)), s_cd = CvtE4m3x2(Prmt(w.s[2], w.s[3], 0x0040u));
+    const uint32_t a[2] = {w.r[0].x, w.r[0].y}, b[2] = {w.r[1].x, w.r[1].y};
+    const uint32_t c[2] = {w.r[2].x, w.r[2].y}, d[2] = {w.r[3].x, w.r[3].y};
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      // byte q of `even`: (row A nibble, row B nibble) of column 8i + 2q; of `odd`: column 8i + 2q + 1
+      // byte q of `e_*`: (row A nibble, row B nibble) of column 8i + 2q; of `o_*`: column 8i + 2q + 1
       uint32_t e_ab[4], o_ab[4], e_cd[4], o_cd[4];
       CvtE2m1x8((a[i] & 0x0F0F0F0Fu) | ((b[i] << 4) & 0xF0F0F0F0u), e_ab);
       CvtE2m1x8(((a[i] >> 4) & 0x0F0F0F0Fu) | (b[i] & 0xF0F0F0F0u), o_ab);
@@ -246,15 +272,470 @@ __device__ __forceinline__ void KStep(float (&acc)[Geom<MODE>::kMmas][4], uint32
   }
 }
 
+// What a CTA works on: a column tile of one weight and a slice of K.
+struct Tile {
+  int seg, n0, n1, kbeg, kend, kslice, crank, C;
+};
+
+__device__ __forceinline__ Tile LocateTile(const GemmParams& p) {
+  Tile tl;
+  int s = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxSeg; ++i) s += (i < p.nseg && static_cast<int>(blockIdx.x) >= p.seg[i].tile_begin) ? 1 : 0;
+  tl.seg = s;
+  const Segment& sg = p.seg[s];
+  const int t = static_cast<int>(blockIdx.x) - sg.tile_begin;
+  tl.n0 = static_cast<int>(static_cast<long long>(t) * sg.granules / sg.tiles) * p.gran;
+  tl.n1 = min(sg.n, static_cast<int>(static_cast<long long>(t + 1) * sg.granules / sg.tiles) * p.gran);
+  tl.C = static_cast<int>(gridDim.y);
+  tl.crank = static_cast<int>(blockIdx.y);
+  const int ksteps_total = (p.K + 15) >> 4;
+  tl.kbeg = static_cast<int>(static_cast<long long>(tl.crank) * ksteps_total / tl.C) * 16;
+  tl.kend = min(p.K, static_cast<int>(static_cast<long long>(tl.crank + 1) * ksteps_total / tl.C) * 16);
+  tl.kslice = max(0, tl.kend - tl.kbeg);
+  return tl;
+}
+
+struct SharedScratch {
+  float inv_scale[kMaxRows];
+  float scale[kMaxRows];
+  uint32_t rmax[kMaxRows];  // largest BF16 magnitude bits of the row's K slice
+  uint32_t rmin[kMaxRows];  // smallest non-zero BF16 magnitude bits (0x7FFF if the slice is all zero)
+  float best_v[kMaxThreads / 32][kMaxRows];
+  long long best_i[kMaxThreads / 32][kMaxRows];
+  int last;
+};
+
+// max / min-nonzero of the two BF16 magnitudes packed in a word
+__device__ __forceinline__ void TrackWord(uint32_t w, uint32_t& mx, uint32_t& mn) {
+  const uint32_t lo = w & 0x7FFFu, hi = (w >> 16) & 0x7FFFu;
+  mx = max(mx, max(lo, hi));
+  mn = min(mn, min(lo != 0 ? lo : 0x7FFFu, hi != 0 ? hi : 0x7FFFu));
+}
+
+// two BF16 values times a power of two, as an FP16 pair (exact when the caller checked the range)
+__device__ __forceinline__ uint32_t ScaleToHalf2(uint32_t w, float sc) {
+  const float lo = __uint_as_float(w << 16) * sc, hi = __uint_as_float(w & 0xFFFF0000u) * sc;
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Copies the CTA's K slice of x into shared memory and, for the quantised modes, rescales every
+// row by a power of two and converts it to FP16.  WORDS = 4: 16-byte chunks (x 16-byte aligned,
+// K % 8 == 0); WORDS = 1: 4-byte pairs (K is even and slices start on multiples of 16, so a pair
+// never straddles a slice).  Returns true if the CTA must take the BF16 path.
+template <int MODE, int WORDS>
+__device__ __forceinline__ bool StageXImpl(const GemmParams& p, const Tile& tl, uint16_t* xs, SharedScratch& sh) {
+  constexpr int kElems = 2 * WORDS;
+  constexpr int kBatch = 4;
+  const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31;
+  const int M = p.M, xpitch = p.xpitch;
+  const int kpad = (tl.kslice + 15) & ~15;
+  const int chunks = kpad / kElems;
+  const int total = M * chunks;
+  uint32_t* xw = reinterpret_cast<uint32_t*>(xs);
+
+  // pass 1: global -> shared (raw BF16).  All loads of a batch are issued before the first is
+  // consumed, so a batch costs one L2 round trip.
+  for (int base0 = 0; base0 < total; base0 += nthreads * kBatch) {  // warp-uniform trip count
+    const int base = base0 + tid;
+    uint32_t v[kBatch][WORDS];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int idx = base + j * nthreads;
+#pragma unroll
+      for (int e = 0; e < WORDS; ++e) v[j][e] = 0;
+      if (idx < total) {
+        const int m = idx / chunks, kk = (idx - m * chunks) * kElems;
+        if (kk < tl.kslice) {
+          const uint16_t* src = p.x + static_cast<size_t>(m) * p.K + tl.kbeg + kk;
+          if constexpr (WORDS == 4) {
+            const uint4 q = __ldg(reinterpret_cast<const uint4*>(src));
+            v[j][0] = q.x, v[j][1] = q.y, v[j][2] = q.z, v[j][3] = q.w;
+          } else {
+            v[j][0] = __ldg(reinterpret_cast<const uint32_t*>(src));
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int idx = base + j * nthreads;
+      const bool live = idx < total;
+      const int m = live ? idx / chunks : 0;
+      if (live) {
+        const int kk = (idx - m * chunks) * kElems;
+        uint32_t* dst = xw + ((m * xpitch + kk) >> 1);
+        if constexpr (WORDS == 4) {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(v[j][0], v[j][1], v[j][2], v[j][3]);
+        } else {
+          *dst = v[j][0];
+        }
+      }
+      if constexpr (MODE != kBf16) {
+        uint32_t mx = 0, mn = 0x7FFFu;
+#pragma unroll
+        for (int e = 0; e < WORDS; ++e) TrackWord(v[j][e], mx, mn);
+        // lanes of a warp almost always work on the same row: one pair of atomics per warp
+        const int m0 = __shfl_sync(0xffffffffu, m, 0);
+        if (__all_sync(0xffffffffu, m == m0)) {
+          mx = __reduce_max_sync(0xffffffffu, mx);
+          mn = __reduce_min_sync(0xffffffffu, mn);
+          if (lane == 0) {
+            atomicMax(&sh.rmax[m0], mx);
+            atomicMin(&sh.rmin[m0], mn);
+          }
+        } else if (live) {
+          atomicMax(&sh.rmax[m], mx);
+          atomicMin(&sh.rmin[m], mn);
+        }
+      }
+    }
+  }
+  if constexpr (MODE == kBf16) {
+    __syncthreads();
+    return false;
+  } else {
+    __syncthreads();
+    // Power-of-two scale per row that puts the slice maximum in [2^14, 2^15).  Every non-zero
+    // element must land in the normal FP16 range: exponent no more than 28 below the maximum's.
+    bool ok = !p.force_slow;
+#pragma unroll
+    for (int m = 0; m < kMaxRows; ++m) {
+      if (m < M) {
+        const uint32_t a = sh.rmax[m];
+        const int e = static_cast<int>(a >> 7);  // BF16 exponent field of the row maximum
+        if (a != 0 && (e < 32 || e >= 255 || static_cast<int>(sh.rmin[m] >> 7) < e - 28)) ok = false;
+      }
+    }
+    const bool slow = !ok;
+    if (tid < kMaxRows) {
+      float sc = 1.f;
+      if (!slow && tid < M && sh.rmax[tid] != 0) sc = __uint_as_float((268u - (sh.rmax[tid] >> 7)) << 23);
+      sh.scale[tid] = sc;
+      sh.inv_scale[tid] = 1.f / sc;
+    }
+    __syncthreads();
+    if (!slow) {
+      // pass 2: in place, BF16 -> scaled FP16
+      for (int idx = tid; idx < total; idx += nthreads) {
+        const int m = idx / chunks, kk = (idx - m * chunks) * kElems;
+        const float sc = sh.scale[m];
+        uint32_t* px = xw + ((m * xpitch + kk) >> 1);
+        if constexpr (WORDS == 4) {
+          uint4 q = *reinterpret_cast<uint4*>(px);
+          q.x = ScaleToHalf2(q.x, sc);
+          q.y = ScaleToHalf2(q.y, sc);
+          q.z = ScaleToHalf2(q.z, sc);
+          q.w = ScaleToHalf2(q.w, sc);
+          *reinterpret_cast<uint4*>(px) = q;
+        } else {
+          *px = ScaleToHalf2(*px, sc);
+        }
+      }
+      __syncthreads();
+    }
+    return slow;
+  }
+}
+
+// Must be called by every thread of the CTA; sh.rmax / sh.rmin are initialised here.
 template <int MODE>
-__global__ void __launch_bounds__(kMaxThreads, 2) SkinnyGemmKernel(const GemmParams p) {
+__device__ __forceinline__ bool StageX(const GemmParams& p, const Tile& tl, uint16_t* xs, SharedScratch& sh) {
+  if (threadIdx.x < kMaxRows) {
+    sh.rmax[threadIdx.x] = 0;
+    sh.rmin[threadIdx.x] = 0x7FFFu;
+    sh.inv_scale[threadIdx.x] = 1.f;
+  }
+  __syncthreads();
+  const bool vec8 = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.K % 8 == 0);
+  if (vec8) return StageXImpl<MODE, 4>(p, tl, xs, sh);
+  return StageXImpl<MODE, 1>(p, tl, xs, sh);
+}
+
+// Reduction of the accumulators (wk warps, then the cluster), scaling, rounding, stores, and the
+// fused argmax.  `smem` is reused for the partial sums; every thread of the CTA must call this
+// after a __syncthreads() that ends all use of the shared memory by the main loop.
+template <int MODE>
+__device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, float (&acc)[Geom<MODE>::kMmas][4],
+                                         uint8_t* smem, SharedScratch& sh, bool warp_has_cols) {
   using G = Geom<MODE>;
+  constexpr int NM = G::kMmas;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int wn = warp % p.wn, wk = warp / p.wn;
+  const int M = p.M, C = tl.C, n0 = tl.n0, n1 = tl.n1;
+  const Segment& sg = p.seg[tl.seg];
+  const int cols_per_warp = 8 * G::kColsPerThread;
+  const int TNc = p.wn * cols_per_warp;
+  float* red = reinterpret_cast<float*>(smem);
+  float* part = red + static_cast<size_t>(p.wk) * M * TNc;
+  if (warp_has_cols) {
+#pragma unroll
+    for (int j = 0; j < NM; ++j) {
+      const int cl = wn * cols_per_warp + g * G::kColsPerThread + 2 * j;
+      const int m0 = 2 * t, m1 = 2 * t + 1;
+      if (m0 < M) *reinterpret_cast<float2*>(&red[(wk * M + m0) * TNc + cl]) = make_float2(acc[j][0], acc[j][2]);
+      if (m1 < M) *reinterpret_cast<float2*>(&red[(wk * M + m1) * TNc + cl]) = make_float2(acc[j][1], acc[j][3]);
+    }
+  } else {
+    for (int m = 0; m < M; ++m)
+      for (int c = lane; c < cols_per_warp; c += 32) red[(wk * M + m) * TNc + wn * cols_per_warp + c] = 0.f;
+  }
+  __syncthreads();
+
+  const int ncols = n1 - n0;  // valid columns of the tile (<= TNc)
+  float best_v[kMaxRows];
+  long long best_i[kMaxRows];
+#pragma unroll
+  for (int m = 0; m < kMaxRows; ++m) {
+    best_v[m] = 0.f;
+    best_i[m] = -1;
+  }
+  auto finalize = [&](int m, int c, float v) {
+    const int n = n0 + c;
+    if (sg.w_scale != nullptr) v *= sg.w_scale[n];
+    const __nv_bfloat16 b = __float2bfloat16(v);
+    if (!p.lm || p.out[sg.out_begin] != nullptr) {
+      int j = sg.out_begin;
+      for (int i = j + 1; i < sg.out_end; ++i) {
+        if (n >= p.col_begin[i]) j = i;
+      }
+      p.out[j][static_cast<size_t>(m) * p.width[j] + (n - p.col_begin[j])] = __bfloat16_as_ushort(b);
+    }
+    if (p.lm) {
+      const float f = __bfloat162float(b);
+#pragma unroll
+      for (int r = 0; r < kMaxRows; ++r) {
+        if (r == m && (best_i[r] < 0 || f > best_v[r] || (f != f && best_v[r] == best_v[r]))) {
+          best_v[r] = f;
+          best_i[r] = p.lm_col_offset + n;
+        }
+      }
+    }
+  };
+
+  if (C == 1) {
+    for (int m = 0; m < M; ++m) {
+      const float inv = sh.inv_scale[m];
+      for (int c = tid; c < ncols; c += nthreads) {
+        float sum = 0.f;
+        for (int w = 0; w < p.wk; ++w) sum += red[(w * M + m) * TNc + c];
+        finalize(m, c, sum * inv);
+      }
+    }
+  } else {
+    for (int m = 0; m < M; ++m) {
+      const float inv = sh.inv_scale[m];
+      for (int c = tid; c < TNc; c += nthreads) {
+        float sum = 0.f;
+        for (int w = 0; w < p.wk; ++w) sum += red[(w * M + m) * TNc + c];
+        part[m * TNc + c] = sum * inv;
+      }
+    }
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int cper = TNc / C;  // TNc is a multiple of 64 and C <= 8
+    const int cb = tl.crank * cper;
+    for (int m = 0; m < M; ++m) {
+      for (int cc = tid; cc < cper; cc += nthreads) {
+        const int c = cb + cc;
+        if (c >= ncols) break;
+        float sum = 0.f;
+        for (int r = 0; r < C; ++r) sum += cluster.map_shared_rank(part, r)[m * TNc + c];
+        finalize(m, c, sum);
+      }
+    }
+    cluster.sync();
+  }
+
+  if (p.lm) {
+    // CTA-level (max, index) per row, folded into the workspace keys with a 64-bit atomic max.
+    __syncthreads();
+#pragma unroll
+    for (int m = 0; m < kMaxRows; ++m) {
+      if (m < M) {
+        float v = best_i[m] < 0 ? -INFINITY : best_v[m];
+        long long i = best_i[m] < 0 ? LLONG_MAX : best_i[m];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, v, off);
+          const long long oi = __shfl_xor_sync(0xffffffffu, i, off);
+          if (Better(ov, oi, v, i)) {
+            v = ov;
+            i = oi;
+          }
+        }
+        if (lane == 0) {
+          sh.best_v[warp][m] = v;
+          sh.best_i[warp][m] = i;
+        }
+      }
+    }
+    __syncthreads();
+    if (tid < M) {
+      float v = sh.best_v[0][tid];
+      long long i = sh.best_i[0][tid];
+      for (int w = 1; w < (nthreads >> 5); ++w) {
+        if (Better(sh.best_v[w][tid], sh.best_i[w][tid], v, i)) {
+          v = sh.best_v[w][tid];
+          i = sh.best_i[w][tid];
+        }
+      }
+      if (i != LLONG_MAX) atomicMax(p.lm_keys + tid, PackKey(v, i));
+      __threadfence();
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned int total = gridDim.x * gridDim.y;
+      const unsigned int prev = atomicAdd(p.lm_count, 1u);
+      sh.last = (prev == total - 1) ? 1 : 0;
+      __threadfence();
+    }
+    __syncthreads();
+    if (sh.last) {
+      if (tid < M) {
+        const unsigned long long key = atomicExch(p.lm_keys + tid, 0ull);
+        const uint32_t ord = static_cast<uint32_t>(key >> 32);
+        const uint32_t bits = (ord == 0xFFFFFFFFu) ? 0x7FC00000u : ((ord & 0x80000000u) ? (ord & 0x7FFFFFFFu) : ~ord);
+        if (p.lm_idx != nullptr) p.lm_idx[tid] = static_cast<long long>(0xFFFFFFFFu - static_cast<uint32_t>(key));
+        if (p.lm_val != nullptr) p.lm_val[tid] = __uint_as_float(bits);
+        if (p.lm_key_out != nullptr) p.lm_key_out[tid] = key;
+      }
+      if (tid == 0) *p.lm_count = 0u;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ direct kernel
+template <int MODE>
+__global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const GemmParams p) {
+  using G = Geom<MODE>;
+  constexpr int NM = G::kMmas;
+  constexpr int D = G::kDepth;
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ float s_inv_scale[kMaxRows];
-  __shared__ uint32_t s_amax[kMaxThreads / 32][kMaxRows];
-  __shared__ float s_best_v[kMaxThreads / 32][kMaxRows];
-  __shared__ long long s_best_i[kMaxThreads / 32][kMaxRows];
-  __shared__ int s_last;
+  __shared__ SharedScratch sh;
+
+  if (p.trigger == 1) GridLaunchDependents();
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int wn = warp % p.wn, wk = warp / p.wn;
+  const Tile tl = LocateTile(p);
+  const Segment& sg = p.seg[tl.seg];
+  const long long pitch = sg.pitch;
+
+  // this thread's columns and this warp's k-steps (local step s is k-step wk + s * p.wk of the slice)
+  const int cols_per_warp = 8 * G::kColsPerThread;
+  const int colbase = tl.n0 + wn * cols_per_warp + g * G::kColsPerThread;
+  const bool warp_has_cols = tl.n0 + wn * cols_per_warp < tl.n1;
+  // threads past the tile's last column stream the tile's first chunk instead (their sums are never stored)
+  const int colload = colbase < tl.n1 ? colbase : tl.n0;
+  const int ksteps = (tl.kslice + 15) >> 4;
+  const int nsteps = ksteps > wk ? (ksteps - wk + p.wk - 1) / p.wk : 0;
+  // only the last k-step of the slice can be partial (K not a multiple of 16)
+  const bool tail_here = (tl.kslice & 15) != 0 && ((ksteps - 1) % p.wk) == wk;
+  const long long col_byte = (MODE == kBf16) ? static_cast<long long>(colload) * 2 : (MODE == kFp8) ? colload : colload / 2;
+  // a thread owns rows 4t .. 4t+3 of a k-step (the k index of an MMA is a free permutation)
+  const uint8_t* wq = sg.w + static_cast<long long>(tl.kbeg + wk * 16 + 4 * t) * pitch + col_byte;  // next step to load
+  const long long scale_delta = static_cast<long long>(sg.n >> 1) + (colload >> 4) - col_byte;
+  const long long step_stride = static_cast<long long>(p.wk) * 16 * pitch;
+  const long long pitch2 = 2 * pitch, pitch3 = 3 * pitch;
+
+  // loads local step s (steps are loaded in increasing order, so a running pointer suffices)
+  auto load_step = [&](Raw<MODE>& raw, int s) {
+    const uint8_t* q0 = wq;
+    wq += step_stride;
+    if (tail_here && s == nsteps - 1) {
+      const int r = tl.kbeg + (wk + s * p.wk) * 16 + 4 * t;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool ok = r + i < tl.kend;
+        if constexpr (MODE == kNvfp4) {
+          raw.r[i] = ok ? Ldg64(q0 + i * pitch) : make_uint2(0, 0);
+          raw.s[i] = ok ? Ldg8(q0 + i * pitch + scale_delta) : 0u;
+        } else {
+          raw.r[i] = ok ? Ldg128(q0 + i * pitch) : make_uint4(0, 0, 0, 0);
+        }
+      }
+      return;
+    }
+    const uint8_t* q1 = q0 + pitch;
+    const uint8_t* q2 = q0 + pitch2;
+    const uint8_t* q3 = q0 + pitch3;
+    if constexpr (MODE == kNvfp4) {
+      raw.r[0] = Ldg64(q0);
+      raw.r[1] = Ldg64(q1);
+      raw.r[2] = Ldg64(q2);
+      raw.r[3] = Ldg64(q3);
+      raw.s[0] = Ldg8(q0 + scale_delta);
+      raw.s[1] = Ldg8(q1 + scale_delta);
+      raw.s[2] = Ldg8(q2 + scale_delta);
+      raw.s[3] = Ldg8(q3 + scale_delta);
+    } else {
+      raw.r[0] = Ldg128(q0);
+      raw.r[1] = Ldg128(q1);
+      raw.r[2] = Ldg128(q2);
+      raw.r[3] = Ldg128(q3);
+    }
+  };
+
+  // weights do not depend on the predecessor kernel: get the first k-steps in flight, then wait
+  Raw<MODE> buf[D];
+#pragma unroll
+  for (int d = 0; d < D; ++d) {
+    if (warp_has_cols && d < nsteps) load_step(buf[d], d);
+  }
+  if (p.pdl_wait) GridDependencyWait();
+
+  uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
+  const bool slow = StageX<MODE>(p, tl, xs, sh);
+
+  float acc[NM][4];
+#pragma unroll
+  for (int j = 0; j < NM; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+
+  const uint32_t xs_addr = SmemAddr(xs) + static_cast<uint32_t>((g * p.xpitch + 4 * t) * 2);
+  const bool has_row = g < p.M;
+  if (warp_has_cols) {
+    for (int base = 0; base < nsteps; base += D) {
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        const int s = base + d;
+        if (s < nsteps) {
+          uint32_t b0 = 0, b1 = 0;
+          if (has_row) {
+            const uint2 xv = Lds64(xs_addr + static_cast<uint32_t>(wk + s * p.wk) * 32u);
+            b0 = xv.x;
+            b1 = xv.y;
+          }
+          if constexpr (MODE == kBf16) {
+            ComputeStep<MODE, false>(acc, buf[d], b0, b1);
+          } else {
+            if (slow) {
+              ComputeStep<MODE, true>(acc, buf[d], b0, b1);
+            } else {
+              ComputeStep<MODE, false>(acc, buf[d], b0, b1);
+            }
+          }
+          if (s + D < nsteps) load_step(buf[d], s + D);
+        }
+      }
+    }
+  }
+  if (p.trigger == 2) GridLaunchDependents();
+  __syncthreads();
+  Epilogue<MODE>(p, tl, acc, smem, sh, warp_has_cols);
+}
+
+// ------------------------------------------------------------------------------ ring kernel
+template <int MODE>
+__global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmRingKernel(const GemmParams p) {
+  using G = Geom<MODE>;
+  constexpr int NM = G::kMmas;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ SharedScratch sh;
 
   if (p.trigger == 1) GridLaunchDependents();
 
@@ -262,26 +743,10 @@ __global__ void __launch_bounds__(kMaxThreads, 2) SkinnyGemmKernel(const GemmPar
   const int nthreads = blockDim.x;
   const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int wn = warp % p.wn, wk = warp / p.wn;
-  const int M = p.M;
-
-  // ---- which tile of which weight
-  int s = 0;
-#pragma unroll
-  for (int i = 1; i < kMaxSeg; ++i) s += (i < p.nseg && static_cast<int>(blockIdx.x) >= p.seg[i].tile_begin) ? 1 : 0;
-  const Segment& sg = p.seg[s];
-  const int N = sg.n;
-  const int tl = static_cast<int>(blockIdx.x) - sg.tile_begin;
-  const int n0 = static_cast<int>(static_cast<long long>(tl) * sg.granules / sg.tiles) * p.gran;
-  const int n1 = min(N, static_cast<int>(static_cast<long long>(tl + 1) * sg.granules / sg.tiles) * p.gran);
+  const Tile tl = LocateTile(p);
+  const Segment& sg = p.seg[tl.seg];
+  const int N = sg.n, n0 = tl.n0, n1 = tl.n1, kbeg = tl.kbeg, kend = tl.kend, kslice = tl.kslice;
   const long long pitch = sg.pitch;
-
-  // ---- which slice of K
-  const int C = static_cast<int>(gridDim.y);
-  const int crank = static_cast<int>(blockIdx.y);
-  const int ksteps_total = (p.K + 15) >> 4;
-  const int kbeg = static_cast<int>(static_cast<long long>(crank) * ksteps_total / C) * 16;
-  const int kend = min(p.K, static_cast<int>(static_cast<long long>(crank + 1) * ksteps_total / C) * 16);
-  const int kslice = max(0, kend - kbeg);
   const int R = 16 * p.wk * p.ks;
   const int nst = (kslice + R - 1) / R;
 
@@ -323,7 +788,7 @@ __global__ void __launch_bounds__(kMaxThreads, 2) SkinnyGemmKernel(const GemmPar
         const int krow = row_base + row;
         if (krow >= kend) bytes = 0;
         const uint8_t* src = bytes > 0 ? wbase + static_cast<long long>(krow) * pitch + bo : sg.w;
-        const uint32_t dst = slot + row * TB + ((((bo >> 4) ^ ((row & 3) << 1 & swz_mask)) << 4) | (bo & 15));
+        const uint32_t dst = slot + row * TB + ((((bo >> 4) ^ (((row >> 2) & 3) << 1 & swz_mask)) << 4) | (bo & 15));
         if (vec == 16) {
           CpAsync16(dst, src, bytes);
         } else if (vec == 8) {
@@ -364,103 +829,9 @@ __global__ void __launch_bounds__(kMaxThreads, 2) SkinnyGemmKernel(const GemmPar
   }
   if (p.pdl_wait) GridDependencyWait();
 
-  const int kpad = (kslice + 15) & ~15;
   uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
-  const int xpitch = p.xpitch;
-  bool slow = false;
-  {
-    // Raw BF16 copy in the k-permuted order the B fragments read: position 4t+i of a 16-block
-    // holds row t+4i.  K is even and slices start on multiples of 16, so pairs never straddle.
-    uint32_t amax[kMaxRows];
-#pragma unroll
-    for (int m = 0; m < kMaxRows; ++m) amax[m] = 0;
-    const int npairs = kpad >> 1;
-#pragma unroll
-    for (int m = 0; m < kMaxRows; ++m) {
-      if (m < M) {
-        const uint32_t* xr = reinterpret_cast<const uint32_t*>(p.x + static_cast<size_t>(m) * p.K + kbeg);
-        for (int pp = tid; pp < npairs; pp += nthreads) {
-          const int kk = pp * 2;
-          const uint32_t v2 = kk < kslice ? __ldg(xr + pp) : 0u;
-          const uint32_t lo = v2 & 0xFFFFu, hi = v2 >> 16;
-          const int r16 = kk & 15;
-          const int base = m * xpitch + (kk & ~15);
-          xs[base + ((r16 & 3) << 2) + (r16 >> 2)] = static_cast<uint16_t>(lo);
-          xs[base + (((r16 + 1) & 3) << 2) + ((r16 + 1) >> 2)] = static_cast<uint16_t>(hi);
-          amax[m] = max(amax[m], max(lo & 0x7FFFu, hi & 0x7FFFu));
-        }
-      }
-    }
-    if constexpr (MODE == kBf16) {
-      if (tid < kMaxRows) s_inv_scale[tid] = 1.f;
-      __syncthreads();
-    } else {
-#pragma unroll
-      for (int m = 0; m < kMaxRows; ++m) {
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) amax[m] = max(amax[m], __shfl_xor_sync(0xffffffffu, amax[m], off));
-        if (lane == 0) s_amax[warp][m] = amax[m];
-      }
-      __syncthreads();
-      // Power-of-two scale per row that puts the slice maximum in [2^14, 2^15); then convert in place.
-      bool ok = !p.force_slow;
-      const int nwarps = nthreads >> 5;
-      float inv_scale[kMaxRows];
-#pragma unroll
-      for (int m = 0; m < kMaxRows; ++m) {
-        inv_scale[m] = 1.f;
-        if (m < M) {
-          uint32_t a = 0;
-          for (int w = 0; w < nwarps; ++w) a = max(a, s_amax[w][m]);
-          const int e = static_cast<int>(a >> 7);  // BF16 exponent field of the row maximum
-          float sc = 1.f;
-          if (a != 0) {
-            if (e < 32 || e >= 255) {
-              ok = false;
-            } else {
-              sc = __uint_as_float(static_cast<uint32_t>(268 - e) << 23);
-            }
-          }
-          const float inv = 1.f / sc;
-          inv_scale[m] = inv;
-          for (int kk = tid; kk < kpad; kk += nthreads) {
-            uint16_t* px = &xs[m * xpitch + kk];
-            const float xf = __uint_as_float(static_cast<uint32_t>(*px) << 16);
-            const float v = xf * sc;
-            const __half h = __float2half_rn(v);
-            ok = ok && (__half2float(h) == v) && (v == 0.f || fabsf(v) >= 6.103515625e-05f) && (v * inv == xf);
-            *px = __half_as_ushort(h);
-          }
-        }
-      }
-      slow = !__syncthreads_and(ok ? 1 : 0);
-      if (slow) {
-        // Not exactly representable: put the BF16 values back and use the BF16 MMA.
-#pragma unroll
-        for (int m = 0; m < kMaxRows; ++m) {
-          if (m < M) {
-            const uint32_t* xr = reinterpret_cast<const uint32_t*>(p.x + static_cast<size_t>(m) * p.K + kbeg);
-            for (int pp = tid; pp < npairs; pp += nthreads) {
-              const int kk = pp * 2;
-              const uint32_t v2 = kk < kslice ? __ldg(xr + pp) : 0u;
-              const int r16 = kk & 15;
-              const int base = m * xpitch + (kk & ~15);
-              xs[base + ((r16 & 3) << 2) + (r16 >> 2)] = static_cast<uint16_t>(v2 & 0xFFFFu);
-              xs[base + (((r16 + 1) & 3) << 2) + ((r16 + 1) >> 2)] = static_cast<uint16_t>(v2 >> 16);
-            }
-          }
-        }
-      }
-      if (tid == 0) {
-#pragma unroll
-        for (int m = 0; m < kMaxRows; ++m) s_inv_scale[m] = slow ? 1.f : inv_scale[m];
-      }
-      __syncthreads();
-    }
-  }
+  const bool slow = StageX<MODE>(p, tl, xs, sh);
 
-  // ---- consumer geometry
-  constexpr int NM = G::kMmas;
   float acc[NM][4];
 #pragma unroll
   for (int j = 0; j < NM; ++j)
@@ -472,14 +843,14 @@ __global__ void __launch_bounds__(kMaxThreads, 2) SkinnyGemmKernel(const GemmPar
   uint32_t w_off, s_off = 0;
   if constexpr (MODE == kNvfp4) {
     const uint32_t chunk = static_cast<uint32_t>(wn * 4 + (g >> 1));
-    w_off = t * TB + (((chunk ^ ((t << 1) & swz_mask)) << 4) | ((g & 1) << 3));
-    s_off = static_cast<uint32_t>(R * TB + t * SRB + sphase + wn * 8 + g);
+    w_off = 4 * t * TB + (((chunk ^ ((t << 1) & swz_mask)) << 4) | ((g & 1) << 3));
+    s_off = static_cast<uint32_t>(R * TB + 4 * t * SRB + sphase + wn * 8 + g);
   } else {
     const uint32_t chunk = static_cast<uint32_t>(wn * 8 + g);
-    w_off = t * TB + ((chunk ^ ((t << 1) & swz_mask)) << 4);
+    w_off = 4 * t * TB + ((chunk ^ ((t << 1) & swz_mask)) << 4);
   }
-  const uint32_t xs_addr = SmemAddr(xs) + static_cast<uint32_t>((g * xpitch + 4 * t) * 2);
-  const bool has_row = g < M;
+  const uint32_t xs_addr = SmemAddr(xs) + static_cast<uint32_t>((g * p.xpitch + 4 * t) * 2);
+  const bool has_row = g < p.M;
 
   for (int it = 0; it < nst; ++it) {
     CpAsyncWait(p.stages - 2);
@@ -500,14 +871,27 @@ __global__ void __launch_bounds__(kMaxThreads, 2) SkinnyGemmKernel(const GemmPar
           b1 = xv.y;
         }
         const uint32_t wa = slot + static_cast<uint32_t>(step_in_stage * 16) * TB + w_off;
-        const uint32_t sa = slot + static_cast<uint32_t>(step_in_stage * 16) * SRB + s_off;
+        Raw<MODE> raw;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if constexpr (MODE == kNvfp4) {
+            raw.r[i] = Lds64(wa + static_cast<uint32_t>(i) * TB);
+          } else {
+            raw.r[i] = Lds128(wa + static_cast<uint32_t>(i) * TB);
+          }
+        }
+        if constexpr (MODE == kNvfp4) {
+          const uint32_t sa = slot + static_cast<uint32_t>(step_in_stage * 16) * SRB + s_off;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) raw.s[i] = Lds8(sa + static_cast<uint32_t>(i) * SRB);
+        }
         if constexpr (MODE == kBf16) {
-          KStep<MODE, false>(acc, wa, 4u * TB, sa, 4u * SRB, b0, b1);
+          ComputeStep<MODE, false>(acc, raw, b0, b1);
         } else {
           if (slow) {
-            KStep<MODE, true>(acc, wa, 4u * TB, sa, 4u * SRB, b0, b1);
+            ComputeStep<MODE, true>(acc, raw, b0, b1);
           } else {
-            KStep<MODE, false>(acc, wa, 4u * TB, sa, 4u * SRB, b0, b1);
+            ComputeStep<MODE, false>(acc, raw, b0, b1);
           }
         }
       }
@@ -516,166 +900,26 @@ __global__ void __launch_bounds__(kMaxThreads, 2) SkinnyGemmKernel(const GemmPar
   CpAsyncWait(0);
   if (p.trigger == 2) GridLaunchDependents();
   __syncthreads();
-
-  // ---- reduction across the wk warps (fixed order), rows scaled back by 2^e
-  const int TNc = p.wn * cols_per_warp;
-  float* red = reinterpret_cast<float*>(smem);
-  float* part = red + static_cast<size_t>(p.wk) * M * TNc;
-  if (warp_has_cols) {
-#pragma unroll
-    for (int j = 0; j < NM; ++j) {
-      const int cl = wn * cols_per_warp + g * G::kColsPerThread + 2 * j;
-      const int m0 = 2 * t, m1 = 2 * t + 1;
-      if (m0 < M) *reinterpret_cast<float2*>(&red[(wk * M + m0) * TNc + cl]) = make_float2(acc[j][0], acc[j][2]);
-      if (m1 < M) *reinterpret_cast<float2*>(&red[(wk * M + m1) * TNc + cl]) = make_float2(acc[j][1], acc[j][3]);
-    }
-  } else {
-    // warps beyond the tile's last column contribute zeros
-    for (int m = 0; m < M; ++m)
-      for (int c = lane; c < cols_per_warp; c += 32) red[(wk * M + m) * TNc + wn * cols_per_warp + c] = 0.f;
-  }
-  __syncthreads();
-
-  const int ncols = n1 - n0;  // valid columns of the tile (<= TNc)
-  float best_v[kMaxRows];
-  long long best_i[kMaxRows];
-#pragma unroll
-  for (int m = 0; m < kMaxRows; ++m) {
-    best_v[m] = 0.f;
-    best_i[m] = -1;
-  }
-  auto finalize = [&](int m, int c, float v) {
-    const int n = n0 + c;
-    if (sg.w_scale != nullptr) v *= sg.w_scale[n];
-    const __nv_bfloat16 b = __float2bfloat16(v);
-    if (!p.lm || p.out[sg.out_begin] != nullptr) {
-      int j = sg.out_begin;
-      for (int i = j + 1; i < sg.out_end; ++i) {
-        if (n >= p.col_begin[i]) j = i;
-      }
-      p.out[j][static_cast<size_t>(m) * p.width[j] + (n - p.col_begin[j])] = __bfloat16_as_ushort(b);
-    }
-    if (p.lm) {
-      const float f = __bfloat162float(b);
-#pragma unroll
-      for (int r = 0; r < kMaxRows; ++r) {
-        if (r == m && (best_i[r] < 0 || f > best_v[r] || (f != f && best_v[r] == best_v[r]))) {
-          best_v[r] = f;
-          best_i[r] = p.lm_col_offset + n;
-        }
-      }
-    }
-  };
-
-  if (C == 1) {
-    for (int m = 0; m < M; ++m) {
-      const float inv = s_inv_scale[m];
-      for (int c = tid; c < ncols; c += nthreads) {
-        float sum = 0.f;
-        for (int w = 0; w < p.wk; ++w) sum += red[(w * M + m) * TNc + c];
-        finalize(m, c, sum * inv);
-      }
-    }
-  } else {
-    for (int m = 0; m < M; ++m) {
-      const float inv = s_inv_scale[m];
-      for (int c = tid; c < TNc; c += nthreads) {
-        float sum = 0.f;
-        for (int w = 0; w < p.wk; ++w) sum += red[(w * M + m) * TNc + c];
-        part[m * TNc + c] = sum * inv;
-      }
-    }
-    cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();
-    const int cper = TNc / C;  // TNc is a multiple of 64 and C <= 8
-    const int cb = crank * cper;
-    for (int m = 0; m < M; ++m) {
-      for (int cc = tid; cc < cper; cc += nthreads) {
-        const int c = cb + cc;
-        if (c >= ncols) break;
-        float sum = 0.f;
-        for (int r = 0; r < C; ++r) sum += cluster.map_shared_rank(part, r)[m * TNc + c];
-        finalize(m, c, sum);
-      }
-    }
-    cluster.sync();
-  }
-
-  if (p.lm) {
-    // CTA-level (max, index) per row, folded into the workspace keys with a 64-bit atomic max.
-    __syncthreads();
-#pragma unroll
-    for (int m = 0; m < kMaxRows; ++m) {
-      if (m < M) {
-        float v = best_i[m] < 0 ? -INFINITY : best_v[m];
-        long long i = best_i[m] < 0 ? LLONG_MAX : best_i[m];
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-          const float ov = __shfl_xor_sync(0xffffffffu, v, off);
-          const long long oi = __shfl_xor_sync(0xffffffffu, i, off);
-          if (Better(ov, oi, v, i)) {
-            v = ov;
-            i = oi;
-          }
-        }
-        if (lane == 0) {
-          s_best_v[warp][m] = v;
-          s_best_i[warp][m] = i;
-        }
-      }
-    }
-    __syncthreads();
-    if (tid < M) {
-      float v = s_best_v[0][tid];
-      long long i = s_best_i[0][tid];
-      for (int w = 1; w < (nthreads >> 5); ++w) {
-        if (Better(s_best_v[w][tid], s_best_i[w][tid], v, i)) {
-          v = s_best_v[w][tid];
-          i = s_best_i[w][tid];
-        }
-      }
-      if (i != LLONG_MAX) atomicMax(p.lm_keys + tid, PackKey(v, i));
-      __threadfence();
-    }
-    __syncthreads();
-    if (tid == 0) {
-      const unsigned int total = gridDim.x * gridDim.y;
-      const unsigned int prev = atomicAdd(p.lm_count, 1u);
-      s_last = (prev == total - 1) ? 1 : 0;
-      __threadfence();
-    }
-    __syncthreads();
-    if (s_last) {
-      if (tid < M) {
-        const unsigned long long key = atomicExch(p.lm_keys + tid, 0ull);
-        const uint32_t ord = static_cast<uint32_t>(key >> 32);
-        const uint32_t bits = (ord == 0xFFFFFFFFu) ? 0x7FC00000u : ((ord & 0x80000000u) ? (ord & 0x7FFFFFFFu) : ~ord);
-        if (p.lm_idx != nullptr) p.lm_idx[tid] = static_cast<long long>(0xFFFFFFFFu - static_cast<uint32_t>(key));
-        if (p.lm_val != nullptr) p.lm_val[tid] = __uint_as_float(bits);
-        if (p.lm_key_out != nullptr) p.lm_key_out[tid] = key;
-      }
-      if (tid == 0) *p.lm_count = 0u;
-    }
-  }
+  Epilogue<MODE>(p, tl, acc, smem, sh, warp_has_cols);
 }
 
 // Largest dynamic shared-memory request any of the kernels accepts: the opt-in limit of the
-// device minus the kernel's static shared memory.
+// device minus the kernels' static shared memory.
 int g_max_dynamic_smem = 0;
 
-template <int MODE>
-cudaError_t ConfigureKernel() {
+template <typename K>
+cudaError_t ConfigureKernel(K kernel) {
   int dev = 0, optin = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
   err = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   if (err != cudaSuccess) return err;
   cudaFuncAttributes fa;
-  err = cudaFuncGetAttributes(&fa, SkinnyGemmKernel<MODE>);
+  err = cudaFuncGetAttributes(&fa, kernel);
   if (err != cudaSuccess) return err;
   const int dyn = optin - static_cast<int>(fa.sharedSizeBytes);
   if (g_max_dynamic_smem == 0 || dyn < g_max_dynamic_smem) g_max_dynamic_smem = dyn;
-  return cudaFuncSetAttribute(SkinnyGemmKernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn);
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn);
 }
 
 template <int MODE>
@@ -702,7 +946,8 @@ cudaError_t LaunchMode(const GemmParams& p, const Plan& plan, size_t smem, cudaS
   }
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
-  return cudaLaunchKernelEx(&cfg, SkinnyGemmKernel<MODE>, p);
+  if (plan.direct) return cudaLaunchKernelEx(&cfg, SkinnyGemmDirectKernel<MODE>, p);
+  return cudaLaunchKernelEx(&cfg, SkinnyGemmRingKernel<MODE>, p);
 }
 
 }  // namespace
@@ -717,15 +962,18 @@ int DeviceSmCount() {
   return count;
 }
 
-// Raises the dynamic shared-memory limit of the three kernels once per process.  Called from the
+// Raises the dynamic shared-memory limit of the kernels once per process.  Called from the
 // *_create entry points, i.e. outside any stream capture.
 cudaError_t ConfigureSkinnyGemmKernels() {
   static std::once_flag once;
   static cudaError_t status = cudaSuccess;
   std::call_once(once, [] {
-    status = ConfigureKernel<kBf16>();
-    if (status == cudaSuccess) status = ConfigureKernel<kFp8>();
-    if (status == cudaSuccess) status = ConfigureKernel<kNvfp4>();
+    status = ConfigureKernel(SkinnyGemmDirectKernel<kBf16>);
+    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmDirectKernel<kFp8>);
+    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmDirectKernel<kNvfp4>);
+    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRingKernel<kBf16>);
+    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRingKernel<kFp8>);
+    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRingKernel<kNvfp4>);
   });
   return status;
 }
@@ -739,12 +987,13 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
   p.cluster = plan.cluster;
   p.gran = plan.gran;
   p.tile_row_bytes = plan.wn * geom.bytes_per_warp;
-  p.scale_row_bytes = mode == kNvfp4 ? plan.wn * 8 + 16 : 0;
+  p.scale_row_bytes = mode == kNvfp4 ? (plan.wn * 8 + 16 + 15) & ~15 : 0;
   const int R = plan.rows_per_stage();
   p.stage_bytes = (R * (p.tile_row_bytes + p.scale_row_bytes) + 127) & ~127;
   const int TNc = plan.wn * geom.cols_per_warp;
   const int red_bytes = (plan.wk + (plan.cluster > 1 ? 1 : 0)) * p.M * TNc * 4;
-  p.ring_bytes = (std::max(plan.stages * p.stage_bytes, red_bytes) + 127) & ~127;
+  const int ring = plan.direct ? 0 : plan.stages * p.stage_bytes;
+  p.ring_bytes = (std::max(ring, red_bytes) + 127) & ~127;
   const int ksteps = (p.K + 15) / 16;
   const int kslice_max = ((ksteps + plan.cluster - 1) / plan.cluster) * 16;
   p.xpitch = ((kslice_max + 63) & ~63) + 16;  // 32 bytes off a 128-byte multiple: rows land in distinct banks

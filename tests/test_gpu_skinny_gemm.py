@@ -76,9 +76,14 @@ def test_ragged_shapes(cuda, mode):
 
 
 @pytest.mark.parametrize("mode", [0, 1, 2])
-@pytest.mark.parametrize("plan", ["wn=1,wk=8,cluster=1", "wn=2,wk=4,cluster=2,ctas=6", "wn=4,wk=2,cluster=4,stages=3",
-                                  "wn=8,wk=1,cluster=8,ks=2,stages=5", "wn=2,wk=2,cluster=1,ks=3,stages=2",
-                                  "wn=4,wk=1,cluster=2,ctas=40"])
+@pytest.mark.parametrize("plan", [
+    # the register-streaming kernel
+    "direct=1,wn=1,wk=16,cluster=1", "direct=1,wn=2,wk=8,cluster=2,ctas=6", "direct=1,wn=4,wk=4,cluster=4",
+    "direct=1,wn=8,wk=2,cluster=8", "direct=1,wn=2,wk=2,cluster=1", "direct=1,wn=4,wk=1,cluster=2,ctas=40",
+    # the cp.async ring kernel
+    "direct=0,wn=1,wk=8,cluster=1", "direct=0,wn=2,wk=4,cluster=2,ctas=6", "direct=0,wn=4,wk=2,cluster=4,stages=3",
+    "direct=0,wn=8,wk=1,cluster=8,ks=2,stages=5", "direct=0,wn=2,wk=2,cluster=1,ks=3,stages=2",
+    "direct=0,wn=4,wk=1,cluster=2,ctas=40", "direct=0,wn=4,wk=4,cluster=1"])
 def test_every_plan_shape(cuda, mode, plan):
     rng = np.random.default_rng(sum(map(ord, plan)) + mode)
     run_case(rng, mode, 3, 2304, [[1280, 256], [512]], with_scale=True, plan=plan)

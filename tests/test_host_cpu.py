@@ -93,7 +93,7 @@ def test_plan_invariants(dtype, k, n, align):
     cpw = {_lib.QFG_BFLOAT16: 64, _lib.QFG_FLOAT8E4M3FN: 128, _lib.QFG_UINT8: 128}[dtype]
     for sms in (148, 132, 1):
         p = _lib.plan_describe(dtype, k, n, align, sms)
-        assert p["wn"] * p["wk"] * 32 == p["threads"] <= 256
+        assert p["wn"] * p["wk"] * 32 == p["threads"] <= 512
         assert p["cluster"] in (1, 2, 4, 8) and 2 <= p["stages"] <= 9
         assert p["smem"] <= 227 * 1024
         assert sum(p["seg_tiles"]) == p["tiles"] and p["ctas"] == p["tiles"] * p["cluster"]
@@ -103,14 +103,21 @@ def test_plan_invariants(dtype, k, n, align):
             widest = -(-granules // tiles) * p["gran"]
             assert widest <= p["wn"] * cpw, "a tile must fit the CTA's columns"
         if sms == 148 and sum(n) * k > 2 ** 24:
-            assert p["ctas"] >= 148, "a large shape must cover every SM"
+            assert p["ctas"] >= 0.9 * 148, "a large shape must cover (nearly) every SM"
 
 
 def test_plan_override_and_errors():
-    p = _lib.plan_describe(_lib.QFG_UINT8, 5120, [17408], 16, 148, "wn=4,wk=2,cluster=2,ctas=296,stages=5,ks=2")
-    assert (p["wn"], p["wk"], p["cluster"], p["stages"], p["ks"], p["ctas"]) == (4, 2, 2, 5, 2, 296)
+    p = _lib.plan_describe(_lib.QFG_UINT8, 5120, [17408], 16, 148, "direct=0,wn=4,wk=2,cluster=2,ctas=296,stages=5,ks=2")
+    assert (p["direct"], p["wn"], p["wk"], p["cluster"], p["stages"], p["ks"], p["ctas"]) == (0, 4, 2, 2, 5, 2, 296)
+    p = _lib.plan_describe(_lib.QFG_UINT8, 5120, [17408], 16, 148, "wn=4,wk=4,cluster=2,ctas=148")
+    assert (p["direct"], p["threads"], p["ctas"]) == (1, 512, 148)
+    # shapes the register-streaming kernel cannot take fall back to the ring kernel
+    assert _lib.plan_describe(_lib.QFG_BFLOAT16, 256, [132], 8)["direct"] == 0
+    assert _lib.plan_describe(_lib.QFG_UINT8, 256, [192], 4)["direct"] == 0
     with pytest.raises(_lib.QfgError):
-        _lib.plan_describe(_lib.QFG_UINT8, 5120, [17408], 16, 148, "wn=3")
+        _lib.plan_describe(_lib.QFG_UINT8, 256, [192], 4, 148, "direct=1")
+    with pytest.raises(_lib.QfgError):
+        _lib.plan_describe(_lib.QFG_UINT8, 5120, [17408], 16, 148, "wk=3")
     with pytest.raises(_lib.QfgError):
         _lib.plan_describe(_lib.QFG_UINT8, 5120, [17408], 16, 148, "bogus=1")
     with pytest.raises(_lib.QfgError):
