@@ -10,6 +10,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <stdexcept>
 #include <string>
@@ -72,6 +73,13 @@ struct qfg_skinny_gemm {
   int pdl_wait = 0;
   int force_slow = 0;
   std::string plan_spec;
+  // plans already computed for this node, keyed by the shape of the call
+  mutable std::mutex plan_mu;
+  mutable std::map<std::string, qfg::Plan> plans;
+  qfg_skinny_gemm() = default;
+  qfg_skinny_gemm(const qfg_skinny_gemm& o)
+      : seg_outs(o.seg_outs), widths(o.widths), trigger(o.trigger), d_w_scale(o.d_w_scale), w_scale_len(o.w_scale_len),
+        pdl_wait(o.pdl_wait), force_slow(o.force_slow), plan_spec(o.plan_spec) {}
 };
 
 struct qfg_dequant {
@@ -97,7 +105,7 @@ struct Prepared {
 // Shape / type checks and segment tables of one call (fused_gemm.cu:512-572).  `outs` may be
 // null when only the plan is wanted.
 Prepared Prepare(const qfg_skinny_gemm& op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weights,
-                 int n_weights, void* const* outs, int n_outs, bool need_outs) {
+                 int n_weights, void* const* outs, int n_outs, bool need_outs, int64_t single_width = 0) {
   const int nseg = static_cast<int>(op.seg_outs.size());
   if (n_weights != nseg) throw InvalidArgument("SkinnyGemm: input count");
   if (m < 1) throw InvalidArgument("SkinnyGemm: M must be >= 1");
@@ -125,12 +133,14 @@ Prepared Prepare(const qfg_skinny_gemm& op, const void* x, int64_t m, int64_t k,
     sg.out_begin = o;
     long long begin = 0;
     for (int i = 0; i < op.seg_outs[s]; ++i, ++o) {
-      if (op.widths[o] < 1) throw InvalidArgument("SkinnyGemm: widths must be positive");
+      // the fused LM head passes the shard width per call instead of as an attribute
+      const int64_t width = single_width > 0 ? single_width : op.widths[o];
+      if (width < 1 || width > INT_MAX) throw InvalidArgument("SkinnyGemm: widths must be positive");
       p.out[o] = need_outs ? static_cast<uint16_t*>(outs[o]) : nullptr;
       if (need_outs && outs[o] == nullptr) throw InvalidArgument("SkinnyGemm: null output");
       p.col_begin[o] = static_cast<int>(begin);
-      p.width[o] = op.widths[o];
-      begin += op.widths[o];
+      p.width[o] = static_cast<int>(width);
+      begin += width;
     }
     sg.out_end = o;
     if (begin > INT_MAX) throw InvalidArgument("SkinnyGemm: N too large");
@@ -184,11 +194,29 @@ Prepared Prepare(const qfg_skinny_gemm& op, const void* x, int64_t m, int64_t k,
   pr.plan_in.mode = pr.mode;
   pr.plan_in.row_align = row_align;
   pr.plan_in.sm_count = qfg::DeviceSmCount();
+  pr.plan_in.max_clusters = need_outs ? &qfg::QueryMaxActiveClusters : nullptr;
   return pr;
 }
 
+qfg::Plan ComputePlan(const qfg_skinny_gemm& op, const qfg::PlanInput& in);
+
 qfg::Plan PlanFor(const qfg_skinny_gemm& op, qfg::PlanInput in, int rows) {
   in.max_rows = rows;
+  std::string key = std::to_string(in.K) + "/" + std::to_string(in.mode) + "/" + std::to_string(in.row_align) + "/" +
+                    std::to_string(rows) + "/" + (in.max_clusters != nullptr ? "d" : "h");
+  for (int s = 0; s < in.nseg; ++s) key += "/" + std::to_string(in.n[s]);
+  {
+    std::lock_guard<std::mutex> lock(op.plan_mu);
+    auto it = op.plans.find(key + "|" + op.plan_spec);
+    if (it != op.plans.end()) return it->second;
+  }
+  qfg::Plan plan = ComputePlan(op, in);
+  std::lock_guard<std::mutex> lock(op.plan_mu);
+  op.plans[key + "|" + op.plan_spec] = plan;
+  return plan;
+}
+
+qfg::Plan ComputePlan(const qfg_skinny_gemm& op, const qfg::PlanInput& in) {
   qfg::Plan plan = qfg::ChoosePlan(in);
   std::string spec = op.plan_spec;
   if (spec.empty()) {
@@ -492,16 +520,16 @@ int qfg_lmhead_compute(const qfg_lmhead* op, const void* x, int64_t m, int64_t k
     if (n < 1 || n > INT_MAX || col_offset < 0 || col_offset + n > 0xFFFFFFFELL)
       throw InvalidArgument("LmHead: bad vocabulary range");
     if (m < 1 || m > qfg::kMaxRows) throw InvalidArgument("LmHead: 1 <= rows <= 8");
-    qfg_skinny_gemm call = op->gemm;  // same attributes, this call's width
-    call.widths[0] = static_cast<int>(n);
+    const qfg_skinny_gemm& call = op->gemm;
     void* outs[1] = {logits};
-    Prepared pr = Prepare(call, x, m, k, weight, 1, outs, 1, false);
+    Prepared pr = Prepare(call, x, m, k, weight, 1, outs, 1, false, n);
     if (x == nullptr || reinterpret_cast<uintptr_t>(x) % 4 != 0 || weight->data == nullptr)
       throw InvalidArgument("LmHead: null or misaligned input");
     const int a = Alignment(weight->data, pr.params.seg[0].pitch);
     if (a == 0) throw InvalidArgument("LmHead: weight rows must be 4-byte aligned");
     pr.params.seg[0].vec = pr.params.seg[0].svec = a;
     pr.plan_in.row_align = a;
+    pr.plan_in.max_clusters = &qfg::QueryMaxActiveClusters;
     pr.params.out[0] = static_cast<uint16_t*>(logits);
     pr.params.lm = 1;
     pr.params.lm_keys = static_cast<unsigned long long*>(workspace);
@@ -511,7 +539,6 @@ int qfg_lmhead_compute(const qfg_lmhead* op, const void* x, int64_t m, int64_t k
     pr.params.lm_key_out = reinterpret_cast<unsigned long long*>(key);
     pr.params.lm_col_offset = col_offset;
     Run(call, pr, m, static_cast<cudaStream_t>(stream), "LmHead");
-    call.d_w_scale = nullptr;
     return QFG_OK;
   } catch (const InvalidArgument& e) {
     return Fail(QFG_INVALID_ARGUMENT, e.what());

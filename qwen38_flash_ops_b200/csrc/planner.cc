@@ -157,15 +157,24 @@ Plan ChoosePlan(const PlanInput& in) {
         const size_t smem = SmemBytes(p, in.mode, kMaxRows, in.K);
         if (smem > 200 * 1024 && c < 8) continue;
         const int per_sm = std::max(1, std::min(16 / (wn * wk), static_cast<int>((220 * 1024) / std::max<size_t>(smem, 1))));
-        const int slots = per_sm * in.sm_count;
+        // clusters that can be resident at once: GPC boundaries cost a cluster launch some SMs
+        int cluster_slots;
+        if (in.max_clusters != nullptr) {
+          cluster_slots = in.max_clusters(in.mode, p.direct, wn * wk * 32, smem, c);
+        } else {
+          cluster_slots = c == 1 ? per_sm * in.sm_count : static_cast<int>(per_sm * in.sm_count * 0.89) / c;
+        }
+        if (cluster_slots < 1) continue;
+        const int slots = cluster_slots * c;
         const int max_cols = wn * g.cols_per_warp;
         const int min_tiles = MinTiles(in, max_cols, gran);
         for (int waves = 1; waves <= 4; ++waves) {
-          int tiles = std::max(min_tiles, waves * slots / c);
+          int tiles = std::max(min_tiles, waves * cluster_slots);
           tiles = static_cast<int>(std::min<long long>(tiles, std::max<long long>(granules, 1)));
           const int ctas = tiles * c;
-          const int need = (ctas + slots - 1) / slots;
-          const double balance = static_cast<double>(ctas) / (static_cast<double>(need) * slots);
+          const int need = (tiles + cluster_slots - 1) / cluster_slots;
+          const double balance = static_cast<double>(tiles) / (static_cast<double>(need) * cluster_slots) *
+                                 std::min(1.0, static_cast<double>(slots) / (per_sm * in.sm_count));
           const double widest = std::ceil(static_cast<double>(granules) / tiles) * gran;
           const double lane_eff = std::min(1.0, (static_cast<double>(sum_n) / tiles) / max_cols) *
                                   ((static_cast<double>(sum_n) / tiles) / std::max(widest, 1.0));
@@ -181,7 +190,7 @@ Plan ChoosePlan(const PlanInput& in) {
             best = p;
             DistributeTiles(in, tiles, &best);
           }
-          if (tiles == min_tiles && waves * slots / c <= min_tiles) continue;
+          if (tiles == min_tiles && waves * cluster_slots <= min_tiles) break;
         }
       }
     }
@@ -194,7 +203,7 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
   if (spec.empty()) return true;
   std::stringstream ss(spec);
   std::string item;
-  int ctas = -1;
+  int ctas = -1, waves = -1;
   bool ring_given = false;
   while (std::getline(ss, item, ',')) {
     const size_t eq = item.find('=');
@@ -207,6 +216,7 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
     else if (key == "stages") { plan->stages = val; ring_given = true; }
     else if (key == "cluster") plan->cluster = val;
     else if (key == "ctas") ctas = val;
+    else if (key == "waves") waves = val;
     else if (key == "gran") plan->gran = val;
     else if (key == "direct") plan->direct = val;
     else return false;
@@ -223,6 +233,18 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
   if (!ring_given) FitRing(in, in.max_rows, plan);
   const ModeGeom g = GeomOf(in.mode);
   int total = ctas > 0 ? std::max(1, ctas / plan->cluster) : 0;
+  if (waves > 0) {
+    // as many tiles as `waves` full waves of co-resident clusters hold
+    const size_t smem = SmemBytes(*plan, in.mode, kMaxRows, in.K);
+    const int per_sm = std::max(1, std::min(16 / (plan->wn * plan->wk), static_cast<int>((220 * 1024) / std::max<size_t>(smem, 1))));
+    int cluster_slots;
+    if (in.max_clusters != nullptr) {
+      cluster_slots = in.max_clusters(in.mode, plan->direct, plan->threads(), smem, plan->cluster);
+    } else {
+      cluster_slots = plan->cluster == 1 ? per_sm * in.sm_count : static_cast<int>(per_sm * in.sm_count * 0.89) / plan->cluster;
+    }
+    total = std::max(1, waves * cluster_slots);
+  }
   const int min_tiles = MinTiles(in, plan->wn * g.cols_per_warp, plan->gran);
   if (total == 0) {
     total = 0;

@@ -101,6 +101,9 @@ struct PlanInput {
   int row_align = 16;  // min over segments of the alignment (16 / 8 / 4) of base and pitch
   int sm_count = 148;
   int max_rows = kMaxRows;
+  // Co-resident clusters (CTAs for cluster == 1) of a launch shape on the current device, or null
+  // when planning without a device (then a B200-like packing loss is assumed for clusters).
+  int (*max_clusters)(int mode, int direct, int threads, size_t smem, int cluster) = nullptr;
 };
 Plan ChoosePlan(const PlanInput& in);
 // Applies "key=value,..." overrides (wn, wk, ks, stages, cluster, ctas, gran); returns false on a bad key.
@@ -114,6 +117,7 @@ std::string DescribePlan(const Plan& plan, const PlanInput& in);
 cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStream_t stream);
 int DeviceSmCount();
 cudaError_t ConfigureSkinnyGemmKernels();
+int QueryMaxActiveClusters(int mode, int direct, int threads, size_t smem, int cluster);
 
 // argmax_rows.cu
 cudaError_t LaunchArgmaxRows(int dtype, const void* x, int64_t rows, int64_t vocab, int64_t* idx, float* val,

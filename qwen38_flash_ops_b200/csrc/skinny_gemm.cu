@@ -32,7 +32,9 @@
 
 #include <algorithm>
 #include <climits>
+#include <map>
 #include <mutex>
+#include <tuple>
 
 #include "qfg_internal.h"
 
@@ -628,8 +630,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const G
   const int cols_per_warp = 8 * G::kColsPerThread;
   const int colbase = tl.n0 + wn * cols_per_warp + g * G::kColsPerThread;
   const bool warp_has_cols = tl.n0 + wn * cols_per_warp < tl.n1;
-  // threads past the tile's last column stream the tile's first chunk instead (their sums are never stored)
-  const int colload = colbase < tl.n1 ? colbase : tl.n0;
+  // threads past the tile's last column load nothing; their pointer is parked on the tile's first chunk
+  const bool cvalid = colbase < tl.n1;
+  const int colload = cvalid ? colbase : tl.n0;
   const int ksteps = (tl.kslice + 15) >> 4;
   const int nsteps = ksteps > wk ? (ksteps - wk + p.wk - 1) / p.wk : 0;
   // only the last k-step of the slice can be partial (K not a multiple of 16)
@@ -649,7 +652,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const G
       const int r = tl.kbeg + (wk + s * p.wk) * 16 + 4 * t;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const bool ok = r + i < tl.kend;
+        const bool ok = cvalid && r + i < tl.kend;
         if constexpr (MODE == kNvfp4) {
           raw.r[i] = ok ? Ldg64(q0 + i * pitch) : make_uint2(0, 0);
           raw.s[i] = ok ? Ldg8(q0 + i * pitch + scale_delta) : 0u;
@@ -662,6 +665,18 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const G
     const uint8_t* q1 = q0 + pitch;
     const uint8_t* q2 = q0 + pitch2;
     const uint8_t* q3 = q0 + pitch3;
+    if (!cvalid) {  // columns past the tile: nothing to stream, the sums are never stored
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if constexpr (MODE == kNvfp4) {
+          raw.r[i] = make_uint2(0, 0);
+          raw.s[i] = 0u;
+        } else {
+          raw.r[i] = make_uint4(0, 0, 0, 0);
+        }
+      }
+      return;
+    }
     if constexpr (MODE == kNvfp4) {
       raw.r[0] = Ldg64(q0);
       raw.r[1] = Ldg64(q1);
@@ -960,6 +975,49 @@ int DeviceSmCount() {
     return n;
   }();
   return count;
+}
+
+// Co-resident clusters (CTAs for cluster == 1) of one launch shape on the current device; cached.
+int QueryMaxActiveClusters(int mode, int direct, int threads, size_t smem, int cluster) {
+  static std::mutex mu;
+  static std::map<std::tuple<int, int, int, size_t, int>, int> cache;
+  const size_t smem_key = (smem + 4095) & ~static_cast<size_t>(4095);
+  const auto key = std::make_tuple(mode, direct, threads, smem_key, cluster);
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  const void* fn = nullptr;
+  switch (mode) {
+    case kBf16: fn = direct ? (const void*)SkinnyGemmDirectKernel<kBf16> : (const void*)SkinnyGemmRingKernel<kBf16>; break;
+    case kFp8: fn = direct ? (const void*)SkinnyGemmDirectKernel<kFp8> : (const void*)SkinnyGemmRingKernel<kFp8>; break;
+    default: fn = direct ? (const void*)SkinnyGemmDirectKernel<kNvfp4> : (const void*)SkinnyGemmRingKernel<kNvfp4>; break;
+  }
+  int result = 0;
+  if (g_max_dynamic_smem > 0 && smem_key > static_cast<size_t>(g_max_dynamic_smem)) {
+    result = 0;
+  } else if (cluster <= 1) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, threads, smem_key) == cudaSuccess) {
+      result = per_sm * DeviceSmCount();
+    }
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, static_cast<unsigned>(cluster), 1);
+    cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+    cfg.dynamicSmemBytes = smem_key;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = static_cast<unsigned>(cluster);
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) == cudaSuccess) result = n;
+  }
+  cudaGetLastError();
+  cache[key] = result;
+  return result;
 }
 
 // Raises the dynamic shared-memory limit of the kernels once per process.  Called from the

