@@ -54,6 +54,16 @@ int MinTiles(const PlanInput& in, int max_cols, int gran) {
 // increasing order), so unlike the rest of the plan they may depend on the row count.
 void FitRing(const PlanInput& in, int rows, Plan* p) {
   const ModeGeom g = GeomOf(in.mode);
+  if (p->direct) {
+    // warp-private rings: as deep as the CTA's share of shared memory allows, at most 8 k-steps
+    const int warps = p->wn * p->wk;
+    const int per_sm = std::max(1, 20 / warps);
+    const size_t budget = static_cast<size_t>(220 * 1024) / per_sm;
+    p->ks = 1;
+    p->stages = 8;
+    while (p->stages > 2 && SmemBytes(*p, in.mode, rows, in.K) > budget) --p->stages;
+    return;
+  }
   const int tb = p->wn * g.bytes_per_warp + (in.mode == kNvfp4 ? (p->wn * 8 + 16 + 15) & ~15 : 0);
   // stages of about 8 KiB, ring of about 64 KiB
   p->ks = std::min(4, std::max(1, 8192 / (16 * p->wk * tb)));
@@ -71,7 +81,9 @@ size_t SmemBytes(const Plan& plan, int mode, int rows, int K) {
   const int stage = (plan.rows_per_stage() * (tb + srb) + 127) & ~127;
   const int tnc = plan.wn * g.cols_per_warp;
   const int red = (plan.wk + (plan.cluster > 1 ? 1 : 0)) * rows * tnc * 4;
-  const int ring = (std::max(plan.direct ? 0 : plan.stages * stage, red) + 127) & ~127;
+  const int direct_slot = 4 * 32 * g.bytes_per_thread + (mode == kNvfp4 ? 256 : 0);
+  const int ring_raw = plan.direct ? plan.wn * plan.wk * plan.stages * direct_slot : plan.stages * stage;
+  const int ring = (std::max(ring_raw, red) + 127) & ~127;
   const int ksteps = (K + 15) / 16;
   const int kslice = ((ksteps + plan.cluster - 1) / plan.cluster) * 16;
   const int xpitch = ((kslice + 63) & ~63) + 16;
@@ -135,16 +147,18 @@ Plan ChoosePlan(const PlanInput& in) {
   long long granules = 0;
   for (int s = 0; s < in.nseg; ++s) granules += (in.n[s] + gran - 1) / gran;
   const int ksteps = (in.K + 15) / 16;
-  const int max_warps = direct ? 16 : 8;
+  const int max_warps = direct ? 20 : 8;
+  const int max_wn = direct ? 10 : 8;
 
   Plan best;
   double best_score = -1.0;
   for (int c = 1; c <= 8; c *= 2) {
     if (c > 1 && in.K / c < 256) continue;
-    for (int wn = 1; wn <= 8; ++wn) {
+    for (int wn = 1; wn <= max_wn; ++wn) {
       if (!direct && (wn & (wn - 1)) != 0) continue;                 // the ring's swizzle wants 2^n warps
       if (!direct && in.mode == kNvfp4 && wn < 2 && sum_n >= 256) continue;
-      for (int wk = 1; wn * wk <= max_warps; wk *= 2) {
+      for (int wk = 1; wn * wk <= max_warps; ++wk) {
+        if (!direct && (wk & (wk - 1)) != 0) continue;
         Plan p;
         p.wn = wn;
         p.wk = wk;
@@ -156,7 +170,7 @@ Plan ChoosePlan(const PlanInput& in) {
         // eight x rows must fit beside the partial sums, whatever the row count of a call
         const size_t smem = SmemBytes(p, in.mode, kMaxRows, in.K);
         if (smem > 200 * 1024 && c < 8) continue;
-        const int per_sm = std::max(1, std::min(16 / (wn * wk), static_cast<int>((220 * 1024) / std::max<size_t>(smem, 1))));
+        const int per_sm = std::max(1, std::min(max_warps / (wn * wk), static_cast<int>((220 * 1024) / std::max<size_t>(smem, 1))));
         // clusters that can be resident at once: GPC boundaries cost a cluster launch some SMs
         int cluster_slots;
         if (in.max_clusters != nullptr) {
@@ -178,7 +192,7 @@ Plan ChoosePlan(const PlanInput& in) {
           const double widest = std::ceil(static_cast<double>(granules) / tiles) * gran;
           const double lane_eff = std::min(1.0, (static_cast<double>(sum_n) / tiles) / max_cols) *
                                   ((static_cast<double>(sum_n) / tiles) / std::max(widest, 1.0));
-          const double warps_per_sm = std::min(16.0, static_cast<double>(per_sm * wn * wk));
+          const double warps_per_sm = std::min(16.0, static_cast<double>(per_sm * wn * wk));  // 16 warps saturate an SM
           const double steps = static_cast<double>(ksteps) / c / wk / need;
           const double kfactor = std::min(1.0, steps / 12.0);
           const double row_bytes = (static_cast<double>(sum_n) / tiles) * bpc;
@@ -225,8 +239,9 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
   if (plan->direct != 0 && !DirectEligible(in)) return false;
   plan->direct = plan->direct != 0 ? 1 : 0;
   if (plan->direct == 0 && plan->gran < Granule(in.mode, in.row_align, false)) plan->gran = Granule(in.mode, in.row_align, false);
-  if ((plan->direct == 0 && !pow2(plan->wn)) || plan->wn < 1 || !pow2(plan->wk) || plan->wn * plan->wk > 16 || plan->wn > 8 || plan->ks < 1 || plan->ks > 8 ||
-      plan->stages < 2 || plan->stages > 9 || plan->cluster < 1 || plan->cluster > 8 || !pow2(plan->cluster)) {
+  if ((plan->direct == 0 && (!pow2(plan->wn) || !pow2(plan->wk) || plan->wn * plan->wk > 8)) || plan->wn < 1 || plan->wk < 1 ||
+      plan->wn * plan->wk > 20 || plan->wn > 10 || plan->ks < 1 || plan->ks > 8 ||
+      plan->stages < 2 || plan->stages > 8 || plan->cluster < 1 || plan->cluster > 8 || !pow2(plan->cluster)) {
     return false;
   }
   if (plan->gran % Granule(in.mode, in.row_align, plan->direct != 0) != 0) return false;
@@ -236,7 +251,7 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
   if (waves > 0) {
     // as many tiles as `waves` full waves of co-resident clusters hold
     const size_t smem = SmemBytes(*plan, in.mode, kMaxRows, in.K);
-    const int per_sm = std::max(1, std::min(16 / (plan->wn * plan->wk), static_cast<int>((220 * 1024) / std::max<size_t>(smem, 1))));
+    const int per_sm = std::max(1, std::min(20 / (plan->wn * plan->wk), static_cast<int>((220 * 1024) / std::max<size_t>(smem, 1))));
     int cluster_slots;
     if (in.max_clusters != nullptr) {
       cluster_slots = in.max_clusters(in.mode, plan->direct, plan->threads(), smem, plan->cluster);

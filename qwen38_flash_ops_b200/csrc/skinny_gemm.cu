@@ -8,10 +8,12 @@
 // as the 8-column operand.  Every weight and every product is exact; accumulation is FP32.
 //
 // Two kernels share that arithmetic and differ in how the weight bytes reach the registers:
-//   * SkinnyGemmDirectKernel (the fast path): every warp streams its own rows from HBM straight
-//     into registers with 64/128-bit non-allocating loads, kDepth k-steps ahead of the MMAs.  No
-//     barrier and no shared-memory traffic in the main loop; the bytes in flight per SM are
-//     warps x kDepth x 1-2 KiB.  Needs 16-byte aligned rows (8 for NVFP4) and whole thread chunks.
+//   * SkinnyGemmDirectKernel (the fast path): every warp streams its own rows from HBM into a
+//     warp-private shared-memory ring with lane-private cp.async copies, `depth` k-steps ahead of
+//     the MMAs.  No CTA barrier in the K loop; the bytes in flight per SM are warps x depth x
+//     1-2 KiB, bounded by shared memory rather than registers (a B200 needs well over 100 KiB in
+//     flight per SM to stream at HBM speed).  Needs 16-byte aligned rows (8 for NVFP4) and whole
+//     thread chunks.
 //   * SkinnyGemmRingKernel (any 4-byte aligned layout, ragged column tails): all threads feed a
 //     multi-stage shared-memory ring with cp.async pieces of 16, 8 or 4 bytes with zero fill.
 //
@@ -43,7 +45,8 @@ namespace {
 
 namespace cg = cooperative_groups;
 
-constexpr int kMaxThreads = 512;
+constexpr int kMaxThreads = 640;   // direct kernel: up to 20 warps (at most 102 registers per thread)
+constexpr int kRingThreads = 256;  // ring kernel: up to 8 warps
 
 // ------------------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t SmemAddr(const void* p) {
@@ -189,15 +192,15 @@ template <int MODE>
 struct Geom;
 template <>
 struct Geom<kBf16> {
-  static constexpr int kColsPerThread = 8, kBytesPerThread = 16, kMmas = 4, kDepth = 4;
+  static constexpr int kColsPerThread = 8, kBytesPerThread = 16, kMmas = 4;
 };
 template <>
 struct Geom<kFp8> {
-  static constexpr int kColsPerThread = 16, kBytesPerThread = 16, kMmas = 8, kDepth = 3;
+  static constexpr int kColsPerThread = 16, kBytesPerThread = 16, kMmas = 8;
 };
 template <>
 struct Geom<kNvfp4> {
-  static constexpr int kColsPerThread = 16, kBytesPerThread = 8, kMmas = 8, kDepth = 4;
+  static constexpr int kColsPerThread = 16, kBytesPerThread = 8, kMmas = 8;
 };
 
 // The raw bytes of one k-step of one thread: four consecutive weight rows (4t .. 4t+3 of the
@@ -610,11 +613,19 @@ __device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, fl
 }
 
 // ------------------------------------------------------------------------------ direct kernel
+// Every warp streams its own weight rows: each lane cp.async-copies the bytes it will itself
+// consume (four rows of its 8/16 columns per k-step) into a warp-private shared-memory ring,
+// `depth` k-steps ahead of the MMAs.  There is no CTA barrier in the K loop, and the bytes in
+// flight per SM (warps x depth x 1-2 KiB) are bounded by shared memory, not by registers.
+// Ring slot of one warp: [4 rows][32 lanes][8 or 16 bytes] + (NVFP4) [16 rows][16 bytes] of
+// block scales: the two aligned 8-byte words per row that hold the warp's eight scale bytes.
 template <int MODE>
 __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const GemmParams p) {
   using G = Geom<MODE>;
   constexpr int NM = G::kMmas;
-  constexpr int D = G::kDepth;
+  constexpr int CB = G::kBytesPerThread;
+  constexpr int kNibBytes = 4 * 32 * CB;
+  constexpr int kSlotBytes = kNibBytes + (MODE == kNvfp4 ? 256 : 0);
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ SharedScratch sh;
 
@@ -625,80 +636,72 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const G
   const Tile tl = LocateTile(p);
   const Segment& sg = p.seg[tl.seg];
   const long long pitch = sg.pitch;
+  const int D = p.stages;
 
   // this thread's columns and this warp's k-steps (local step s is k-step wk + s * p.wk of the slice)
   const int cols_per_warp = 8 * G::kColsPerThread;
-  const int colbase = tl.n0 + wn * cols_per_warp + g * G::kColsPerThread;
-  const bool warp_has_cols = tl.n0 + wn * cols_per_warp < tl.n1;
-  // threads past the tile's last column load nothing; their pointer is parked on the tile's first chunk
+  const int colwarp = tl.n0 + wn * cols_per_warp;
+  const int colbase = colwarp + g * G::kColsPerThread;
+  const bool warp_has_cols = colwarp < tl.n1;
   const bool cvalid = colbase < tl.n1;
-  const int colload = cvalid ? colbase : tl.n0;
   const int ksteps = (tl.kslice + 15) >> 4;
-  const int nsteps = ksteps > wk ? (ksteps - wk + p.wk - 1) / p.wk : 0;
-  // only the last k-step of the slice can be partial (K not a multiple of 16)
-  const bool tail_here = (tl.kslice & 15) != 0 && ((ksteps - 1) % p.wk) == wk;
-  const long long col_byte = (MODE == kBf16) ? static_cast<long long>(colload) * 2 : (MODE == kFp8) ? colload : colload / 2;
+  const int nsteps = (warp_has_cols && ksteps > wk) ? (ksteps - wk + p.wk - 1) / p.wk : 0;
+  // only the last k-step of the slice can be partial (K not a multiple of 16); the last k-step of
+  // the whole weight is also where the scale words must not run past the end of the tensor
+  const bool last_here = ((ksteps - 1) % p.wk) == wk;
+  const long long col_byte = (MODE == kBf16) ? static_cast<long long>(colbase) * 2 : (MODE == kFp8) ? colbase : colbase / 2;
   // a thread owns rows 4t .. 4t+3 of a k-step (the k index of an MMA is a free permutation)
-  const uint8_t* wq = sg.w + static_cast<long long>(tl.kbeg + wk * 16 + 4 * t) * pitch + col_byte;  // next step to load
-  const long long scale_delta = static_cast<long long>(sg.n >> 1) + (colload >> 4) - col_byte;
+  const uint8_t* wq = sg.w + static_cast<long long>(tl.kbeg + wk * 16 + 4 * t) * pitch + col_byte;  // next step to copy
   const long long step_stride = static_cast<long long>(p.wk) * 16 * pitch;
-  const long long pitch2 = 2 * pitch, pitch3 = 3 * pitch;
+  // NVFP4 block scales of the warp's 128 columns: 8 bytes per row at `soff`, fetched as the aligned words around them
+  const long long soff = static_cast<long long>(sg.n >> 1) + (colwarp >> 4);
+  const int sphase = static_cast<int>(soff & 7);
+  const bool scale_lane = (MODE == kNvfp4) && (g == 0 || (g == 1 && sphase != 0));
+  const uint8_t* sq = sg.w + static_cast<long long>(tl.kbeg + wk * 16 + 4 * t) * pitch + (soff & ~7LL) + g * 8;
 
-  // loads local step s (steps are loaded in increasing order, so a running pointer suffices)
-  auto load_step = [&](Raw<MODE>& raw, int s) {
+  const uint32_t ring = SmemAddr(smem) + static_cast<uint32_t>(warp) * static_cast<uint32_t>(D) * kSlotBytes;
+  const uint32_t lane_off = static_cast<uint32_t>(lane) * CB;
+
+  // copies local step s into its ring slot (steps are issued in increasing order: running pointers)
+  auto issue_step = [&](int s) {
+    const uint32_t slot = ring + static_cast<uint32_t>(s % D) * kSlotBytes;
     const uint8_t* q0 = wq;
+    const uint8_t* s0 = sq;
     wq += step_stride;
-    if (tail_here && s == nsteps - 1) {
-      const int r = tl.kbeg + (wk + s * p.wk) * 16 + 4 * t;
+    sq += step_stride;
+    const bool last = last_here && s == nsteps - 1;
+    const int r = tl.kbeg + (wk + s * p.wk) * 16 + 4 * t;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const bool ok = cvalid && r + i < tl.kend;
-        if constexpr (MODE == kNvfp4) {
-          raw.r[i] = ok ? Ldg64(q0 + i * pitch) : make_uint2(0, 0);
-          raw.s[i] = ok ? Ldg8(q0 + i * pitch + scale_delta) : 0u;
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t dst = slot + static_cast<uint32_t>(i) * (32 * CB) + lane_off;
+      const bool row_ok = !last || r + i < tl.kend;
+      if (cvalid) {
+        if constexpr (CB == 16) {
+          CpAsync16(dst, row_ok ? q0 + i * pitch : sg.w, row_ok ? 16 : 0);
         } else {
-          raw.r[i] = ok ? Ldg128(q0 + i * pitch) : make_uint4(0, 0, 0, 0);
+          CpAsync8(dst, row_ok ? q0 + i * pitch : sg.w, row_ok ? 8 : 0);
         }
       }
-      return;
-    }
-    const uint8_t* q1 = q0 + pitch;
-    const uint8_t* q2 = q0 + pitch2;
-    const uint8_t* q3 = q0 + pitch3;
-    if (!cvalid) {  // columns past the tile: nothing to stream, the sums are never stored
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        if constexpr (MODE == kNvfp4) {
-          raw.r[i] = make_uint2(0, 0);
-          raw.s[i] = 0u;
-        } else {
-          raw.r[i] = make_uint4(0, 0, 0, 0);
+      if constexpr (MODE == kNvfp4) {
+        if (scale_lane) {
+          const uint32_t sdst = slot + kNibBytes + static_cast<uint32_t>(4 * t + i) * 16 + static_cast<uint32_t>(g) * 8;
+          int bytes = 8;
+          const uint8_t* src = s0 + i * pitch;
+          if (last) {
+            const long long room = sg.total_bytes - (src - sg.w);
+            bytes = !row_ok ? 0 : room >= 8 ? 8 : room > 0 ? static_cast<int>(room) : 0;
+            if (bytes == 0) src = sg.w;
+          }
+          CpAsync8(sdst, src, bytes);
         }
       }
-      return;
-    }
-    if constexpr (MODE == kNvfp4) {
-      raw.r[0] = Ldg64(q0);
-      raw.r[1] = Ldg64(q1);
-      raw.r[2] = Ldg64(q2);
-      raw.r[3] = Ldg64(q3);
-      raw.s[0] = Ldg8(q0 + scale_delta);
-      raw.s[1] = Ldg8(q1 + scale_delta);
-      raw.s[2] = Ldg8(q2 + scale_delta);
-      raw.s[3] = Ldg8(q3 + scale_delta);
-    } else {
-      raw.r[0] = Ldg128(q0);
-      raw.r[1] = Ldg128(q1);
-      raw.r[2] = Ldg128(q2);
-      raw.r[3] = Ldg128(q3);
     }
   };
 
   // weights do not depend on the predecessor kernel: get the first k-steps in flight, then wait
-  Raw<MODE> buf[D];
-#pragma unroll
-  for (int d = 0; d < D; ++d) {
-    if (warp_has_cols && d < nsteps) load_step(buf[d], d);
+  for (int d = 0; d < D - 1; ++d) {
+    if (d < nsteps) issue_step(d);
+    CpAsyncCommit();
   }
   if (p.pdl_wait) GridDependencyWait();
 
@@ -713,32 +716,58 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const G
 
   const uint32_t xs_addr = SmemAddr(xs) + static_cast<uint32_t>((g * p.xpitch + 4 * t) * 2);
   const bool has_row = g < p.M;
-  if (warp_has_cols) {
-    for (int base = 0; base < nsteps; base += D) {
+  for (int s = 0; s < nsteps; ++s) {
+    // the slot consumed one step ago is free again: refill it with step s + D - 1
+    __syncwarp();
+    if (s + D - 1 < nsteps) issue_step(s + D - 1);
+    CpAsyncCommit();
+    CpAsyncWait(D - 1);
+    __syncwarp();
+    const uint32_t slot = ring + static_cast<uint32_t>(s % D) * kSlotBytes;
+    Raw<MODE> raw;
 #pragma unroll
-      for (int d = 0; d < D; ++d) {
-        const int s = base + d;
-        if (s < nsteps) {
-          uint32_t b0 = 0, b1 = 0;
-          if (has_row) {
-            const uint2 xv = Lds64(xs_addr + static_cast<uint32_t>(wk + s * p.wk) * 32u);
-            b0 = xv.x;
-            b1 = xv.y;
-          }
-          if constexpr (MODE == kBf16) {
-            ComputeStep<MODE, false>(acc, buf[d], b0, b1);
-          } else {
-            if (slow) {
-              ComputeStep<MODE, true>(acc, buf[d], b0, b1);
-            } else {
-              ComputeStep<MODE, false>(acc, buf[d], b0, b1);
-            }
-          }
-          if (s + D < nsteps) load_step(buf[d], s + D);
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (CB == 16) {
+        raw.r[i] = Lds128(slot + static_cast<uint32_t>(i) * (32 * CB) + lane_off);
+      } else {
+        raw.r[i] = Lds64(slot + static_cast<uint32_t>(i) * (32 * CB) + lane_off);
+      }
+    }
+    if constexpr (MODE == kNvfp4) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        raw.s[i] = Lds8(slot + kNibBytes + static_cast<uint32_t>(4 * t + i) * 16 + static_cast<uint32_t>(sphase + g));
+    }
+    if (!cvalid) {  // columns past the tile: their ring bytes were never written
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if constexpr (CB == 16) {
+          raw.r[i] = make_uint4(0, 0, 0, 0);
+        } else {
+          raw.r[i] = make_uint2(0, 0);
         }
       }
     }
+    uint32_t b0 = 0, b1 = 0;
+    if (has_row) {
+      const uint2 xv = Lds64(xs_addr + static_cast<uint32_t>(wk + s * p.wk) * 32u);
+      b0 = xv.x;
+      b1 = xv.y;
+    }
+    if (p.debug & 2) {  // measurement aid: consume the bytes without dequantising
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[0][i] += __uint_as_float((raw.r[i].x ^ raw.r[i].y) & 0x3FFFFFFFu);
+    } else if constexpr (MODE == kBf16) {
+      ComputeStep<MODE, false>(acc, raw, b0, b1);
+    } else {
+      if (slow) {
+        ComputeStep<MODE, true>(acc, raw, b0, b1);
+      } else {
+        ComputeStep<MODE, false>(acc, raw, b0, b1);
+      }
+    }
   }
+  CpAsyncWait(0);
   if (p.trigger == 2) GridLaunchDependents();
   __syncthreads();
   Epilogue<MODE>(p, tl, acc, smem, sh, warp_has_cols);
@@ -746,7 +775,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const G
 
 // ------------------------------------------------------------------------------ ring kernel
 template <int MODE>
-__global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmRingKernel(const GemmParams p) {
+__global__ void __launch_bounds__(kRingThreads, 2) SkinnyGemmRingKernel(const GemmParams p) {
   using G = Geom<MODE>;
   constexpr int NM = G::kMmas;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -1050,7 +1079,8 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
   p.stage_bytes = (R * (p.tile_row_bytes + p.scale_row_bytes) + 127) & ~127;
   const int TNc = plan.wn * geom.cols_per_warp;
   const int red_bytes = (plan.wk + (plan.cluster > 1 ? 1 : 0)) * p.M * TNc * 4;
-  const int ring = plan.direct ? 0 : plan.stages * p.stage_bytes;
+  const int direct_slot = 4 * 32 * geom.bytes_per_thread + (mode == kNvfp4 ? 256 : 0);
+  const int ring = plan.direct ? plan.wn * plan.wk * plan.stages * direct_slot : plan.stages * p.stage_bytes;
   p.ring_bytes = (std::max(ring, red_bytes) + 127) & ~127;
   const int ksteps = (p.K + 15) / 16;
   const int kslice_max = ((ksteps + plan.cluster - 1) / plan.cluster) * 16;

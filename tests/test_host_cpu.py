@@ -93,8 +93,8 @@ def test_plan_invariants(dtype, k, n, align):
     cpw = {_lib.QFG_BFLOAT16: 64, _lib.QFG_FLOAT8E4M3FN: 128, _lib.QFG_UINT8: 128}[dtype]
     for sms in (148, 132, 16):
         p = _lib.plan_describe(dtype, k, n, align, sms)
-        assert p["wn"] * p["wk"] * 32 == p["threads"] <= 512
-        assert p["cluster"] in (1, 2, 4, 8) and 2 <= p["stages"] <= 9
+        assert p["wn"] * p["wk"] * 32 == p["threads"] <= 640
+        assert p["cluster"] in (1, 2, 4, 8) and 2 <= p["stages"] <= 8
         assert p["smem"] <= 227 * 1024
         assert sum(p["seg_tiles"]) == p["tiles"] and p["ctas"] == p["tiles"] * p["cluster"]
         for width, tiles in zip(n, p["seg_tiles"]):
@@ -117,7 +117,7 @@ def test_plan_override_and_errors():
     with pytest.raises(_lib.QfgError):
         _lib.plan_describe(_lib.QFG_UINT8, 256, [192], 4, 148, "direct=1")
     with pytest.raises(_lib.QfgError):
-        _lib.plan_describe(_lib.QFG_UINT8, 5120, [17408], 16, 148, "wk=3")
+        _lib.plan_describe(_lib.QFG_UINT8, 5120, [17408], 16, 148, "wn=11")
     with pytest.raises(_lib.QfgError):
         _lib.plan_describe(_lib.QFG_UINT8, 5120, [17408], 16, 148, "bogus=1")
     with pytest.raises(_lib.QfgError):
