@@ -179,8 +179,11 @@ Prepared Prepare(const qfg_skinny_gemm& op, const void* x, int64_t m, int64_t k,
     sg.total_bytes = sg.pitch * k;
     if (need_outs) {
       if (w.data == nullptr) throw InvalidArgument("SkinnyGemm: null weight");
-      const int a = Alignment(w.data, sg.pitch);
+      int a = Alignment(w.data, sg.pitch);
       if (a == 0) throw InvalidArgument("SkinnyGemm: weight rows must be 4-byte aligned");
+      // the streaming kernel copies aligned 16-byte pieces: it needs a 16-byte aligned base even
+      // where the pitch is only a multiple of 8
+      if (a == 8 && reinterpret_cast<uintptr_t>(w.data) % 16 != 0) a = 4;
       row_align = std::min(row_align, a);
     } else {
       row_align = std::min(row_align, Alignment(nullptr, sg.pitch) == 0 ? 4 : Alignment(nullptr, sg.pitch));
@@ -294,6 +297,51 @@ int SetGemmOption(qfg_skinny_gemm* op, const char* key, const char* value) {
 }
 
 }  // namespace
+
+namespace qfg {
+
+int SetLastError(int code, const char* message) { return Fail(code, message); }
+
+// The fused LM head on a caller-chosen scratch area (see qfg_lmhead_compute).
+int LmheadComputeWithWorkspace(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
+                       int64_t n, int64_t col_offset, void* workspace, int64_t* idx, float* val, uint64_t* key,
+                       void* logits, void* stream) {
+  if (op == nullptr || weight == nullptr) return Fail(QFG_FAIL, "LmHead: null argument");
+  try {
+    if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 8 != 0)
+      throw InvalidArgument("LmHead: workspace must be an 8-byte aligned device pointer");
+    if (n < 1 || n > INT_MAX || col_offset < 0 || col_offset + n > 0xFFFFFFFELL)
+      throw InvalidArgument("LmHead: bad vocabulary range");
+    if (m < 1 || m > qfg::kMaxRows) throw InvalidArgument("LmHead: 1 <= rows <= 8");
+    const qfg_skinny_gemm& call = op->gemm;
+    void* outs[1] = {logits};
+    Prepared pr = Prepare(call, x, m, k, weight, 1, outs, 1, false, n);
+    if (x == nullptr || reinterpret_cast<uintptr_t>(x) % 4 != 0 || weight->data == nullptr)
+      throw InvalidArgument("LmHead: null or misaligned input");
+    int a = Alignment(weight->data, pr.params.seg[0].pitch);
+    if (a == 0) throw InvalidArgument("LmHead: weight rows must be 4-byte aligned");
+    if (a == 8 && reinterpret_cast<uintptr_t>(weight->data) % 16 != 0) a = 4;
+    pr.params.seg[0].vec = pr.params.seg[0].svec = a;
+    pr.plan_in.row_align = a;
+    pr.plan_in.max_clusters = &qfg::QueryMaxActiveClusters;
+    pr.params.out[0] = static_cast<uint16_t*>(logits);
+    pr.params.lm = 1;
+    pr.params.lm_keys = static_cast<unsigned long long*>(workspace);
+    pr.params.lm_count = reinterpret_cast<unsigned int*>(static_cast<unsigned long long*>(workspace) + qfg::kMaxRows);
+    pr.params.lm_idx = reinterpret_cast<long long*>(idx);
+    pr.params.lm_val = val;
+    pr.params.lm_key_out = reinterpret_cast<unsigned long long*>(key);
+    pr.params.lm_col_offset = col_offset;
+    Run(call, pr, m, static_cast<cudaStream_t>(stream), "LmHead");
+    return QFG_OK;
+  } catch (const InvalidArgument& e) {
+    return Fail(QFG_INVALID_ARGUMENT, e.what());
+  } catch (const std::exception& e) {
+    return Fail(QFG_FAIL, e.what());
+  }
+}
+
+}  // namespace qfg
 
 extern "C" {
 
@@ -516,38 +564,7 @@ int qfg_lmhead_create(const float* w_scale, size_t n_w_scale, int trigger, qfg_l
 int qfg_lmhead_compute(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
                        int64_t n, int64_t col_offset, void* workspace, int64_t* idx, float* val, uint64_t* key,
                        void* logits, void* stream) {
-  if (op == nullptr || weight == nullptr) return Fail(QFG_FAIL, "LmHead: null argument");
-  try {
-    if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 8 != 0)
-      throw InvalidArgument("LmHead: workspace must be an 8-byte aligned device pointer");
-    if (n < 1 || n > INT_MAX || col_offset < 0 || col_offset + n > 0xFFFFFFFELL)
-      throw InvalidArgument("LmHead: bad vocabulary range");
-    if (m < 1 || m > qfg::kMaxRows) throw InvalidArgument("LmHead: 1 <= rows <= 8");
-    const qfg_skinny_gemm& call = op->gemm;
-    void* outs[1] = {logits};
-    Prepared pr = Prepare(call, x, m, k, weight, 1, outs, 1, false, n);
-    if (x == nullptr || reinterpret_cast<uintptr_t>(x) % 4 != 0 || weight->data == nullptr)
-      throw InvalidArgument("LmHead: null or misaligned input");
-    const int a = Alignment(weight->data, pr.params.seg[0].pitch);
-    if (a == 0) throw InvalidArgument("LmHead: weight rows must be 4-byte aligned");
-    pr.params.seg[0].vec = pr.params.seg[0].svec = a;
-    pr.plan_in.row_align = a;
-    pr.plan_in.max_clusters = &qfg::QueryMaxActiveClusters;
-    pr.params.out[0] = static_cast<uint16_t*>(logits);
-    pr.params.lm = 1;
-    pr.params.lm_keys = static_cast<unsigned long long*>(workspace);
-    pr.params.lm_count = reinterpret_cast<unsigned int*>(static_cast<unsigned long long*>(workspace) + qfg::kMaxRows);
-    pr.params.lm_idx = reinterpret_cast<long long*>(idx);
-    pr.params.lm_val = val;
-    pr.params.lm_key_out = reinterpret_cast<unsigned long long*>(key);
-    pr.params.lm_col_offset = col_offset;
-    Run(call, pr, m, static_cast<cudaStream_t>(stream), "LmHead");
-    return QFG_OK;
-  } catch (const InvalidArgument& e) {
-    return Fail(QFG_INVALID_ARGUMENT, e.what());
-  } catch (const std::exception& e) {
-    return Fail(QFG_FAIL, e.what());
-  }
+  return qfg::LmheadComputeWithWorkspace(op, x, m, k, weight, n, col_offset, workspace, idx, val, key, logits, stream);
 }
 
 int qfg_lmhead_set_option(qfg_lmhead* op, const char* key, const char* value) {

@@ -60,8 +60,12 @@ void FitRing(const PlanInput& in, int rows, Plan* p) {
     const int per_sm = std::max(1, 20 / warps);
     const size_t budget = static_cast<size_t>(220 * 1024) / per_sm;
     p->ks = 1;
-    p->stages = 8;
-    while (p->stages > 2 && SmemBytes(*p, in.mode, rows, in.K) > budget) --p->stages;
+    // the kernel is compiled for ring depths 8, 6, 4 and 3
+    static const int kDepths[] = {8, 6, 4, 3};
+    for (int d : kDepths) {
+      p->stages = d;
+      if (SmemBytes(*p, in.mode, rows, in.K) <= budget) break;
+    }
     return;
   }
   const int tb = p->wn * g.bytes_per_warp + (in.mode == kNvfp4 ? (p->wn * 8 + 16 + 15) & ~15 : 0);
@@ -81,7 +85,7 @@ size_t SmemBytes(const Plan& plan, int mode, int rows, int K) {
   const int stage = (plan.rows_per_stage() * (tb + srb) + 127) & ~127;
   const int tnc = plan.wn * g.cols_per_warp;
   const int red = (plan.wk + (plan.cluster > 1 ? 1 : 0)) * rows * tnc * 4;
-  const int direct_slot = 4 * 32 * g.bytes_per_thread + (mode == kNvfp4 ? 256 : 0);
+  const int direct_slot = mode == kNvfp4 ? 16 * 80 + 16 * 32 : 4 * 32 * g.bytes_per_thread;
   const int ring_raw = plan.direct ? plan.wn * plan.wk * plan.stages * direct_slot : plan.stages * stage;
   const int ring = (std::max(ring_raw, red) + 127) & ~127;
   const int ksteps = (K + 15) / 16;
@@ -237,6 +241,7 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
   }
   auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
   if (plan->direct != 0 && !DirectEligible(in)) return false;
+  if (plan->direct != 0 && ring_given && plan->stages != 3 && plan->stages != 4 && plan->stages != 6 && plan->stages != 8) return false;
   plan->direct = plan->direct != 0 ? 1 : 0;
   if (plan->direct == 0 && plan->gran < Granule(in.mode, in.row_align, false)) plan->gran = Granule(in.mode, in.row_align, false);
   if ((plan->direct == 0 && (!pow2(plan->wn) || !pow2(plan->wk) || plan->wn * plan->wk > 8)) || plan->wn < 1 || plan->wk < 1 ||

@@ -126,6 +126,12 @@ cudaError_t LaunchArgmaxRows(int dtype, const void* x, int64_t rows, int64_t voc
 cudaError_t LaunchLmheadCombine(const uint64_t* keys, int ranks, int64_t m, int64_t* idx, float* val,
                                 cudaStream_t stream);
 
+// capi.cc
+int LmheadComputeWithWorkspace(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
+                               int64_t n, int64_t col_offset, void* workspace, int64_t* idx, float* val, uint64_t* key,
+                               void* logits, void* stream);
+int SetLastError(int code, const char* message);
+
 // dequant_bf16.cu
 struct DequantParams {
   const uint8_t* w = nullptr;

@@ -613,21 +613,33 @@ __device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, fl
 }
 
 // ------------------------------------------------------------------------------ direct kernel
-// Every warp streams its own weight rows: each lane cp.async-copies the bytes it will itself
-// consume (four rows of its 8/16 columns per k-step) into a warp-private shared-memory ring,
-// `depth` k-steps ahead of the MMAs.  There is no CTA barrier in the K loop, and the bytes in
-// flight per SM (warps x depth x 1-2 KiB) are bounded by shared memory, not by registers.
-// Ring slot of one warp: [4 rows][32 lanes][8 or 16 bytes] + (NVFP4) [16 rows][16 bytes] of
-// block scales: the two aligned 8-byte words per row that hold the warp's eight scale bytes.
-template <int MODE>
+// Every warp streams its own weight rows into a warp-private shared-memory ring with 16-byte
+// cp.async.cg copies (L1 bypass), DEPTH k-steps ahead of the MMAs.  There is no CTA barrier in
+// the K loop, and the bytes in flight per SM (warps x DEPTH x 1.8-2 KiB) are bounded by shared
+// memory, not by registers.  Measured on B200: this copy pattern streams at over 6 TB/s with 16
+// warps per SM, where 8-byte copies through L1 or register loads at the same occupancy stay
+// below 4 TB/s.
+//
+// Ring slot of one warp.  BF16 / FP8: [4 rows][32 lanes][16 bytes], every lane copies the bytes it
+// consumes.  NVFP4: 16 rows of the warp's 64 nibble bytes at a pitch of 80 bytes, copied as
+// aligned 16-byte pieces (a chunk that starts 8 bytes off a 16-byte boundary - odd rows of a
+// weight whose packed pitch is 8 mod 16, like the 151936-column LM head, or a tile whose first
+// column is 16 mod 32 - takes five pieces and is read back at an offset of 8), followed by
+// 16 rows x 32 bytes holding the one or two aligned 16-byte pieces around the warp's eight
+// block-scale bytes.  Every lane owns at most four pieces; their source pointers advance by one
+// k-step stride per step.
+template <int MODE, int DEPTH>
 __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const GemmParams p) {
   using G = Geom<MODE>;
   constexpr int NM = G::kMmas;
   constexpr int CB = G::kBytesPerThread;
-  constexpr int kNibBytes = 4 * 32 * CB;
-  constexpr int kSlotBytes = kNibBytes + (MODE == kNvfp4 ? 256 : 0);
+  constexpr int kNibPitch = 80;  // NVFP4: shared-memory bytes per weight row of a warp
+  constexpr int kSclPitch = 32;
+  constexpr int kNibBytes = MODE == kNvfp4 ? 16 * kNibPitch : 4 * 32 * CB;
+  constexpr int kSlotBytes = kNibBytes + (MODE == kNvfp4 ? 16 * kSclPitch : 0);
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ SharedScratch sh;
+  __shared__ __align__(16) uint32_t s_zero[4];
 
   if (p.trigger == 1) GridLaunchDependents();
   const int tid = threadIdx.x;
@@ -636,7 +648,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const G
   const Tile tl = LocateTile(p);
   const Segment& sg = p.seg[tl.seg];
   const long long pitch = sg.pitch;
-  const int D = p.stages;
+  if (tid < 4) s_zero[tid] = 0;
 
   // this thread's columns and this warp's k-steps (local step s is k-step wk + s * p.wk of the slice)
   const int cols_per_warp = 8 * G::kColsPerThread;
@@ -646,61 +658,100 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const G
   const bool cvalid = colbase < tl.n1;
   const int ksteps = (tl.kslice + 15) >> 4;
   const int nsteps = (warp_has_cols && ksteps > wk) ? (ksteps - wk + p.wk - 1) / p.wk : 0;
-  // only the last k-step of the slice can be partial (K not a multiple of 16); the last k-step of
-  // the whole weight is also where the scale words must not run past the end of the tensor
-  const bool last_here = ((ksteps - 1) % p.wk) == wk;
-  const long long col_byte = (MODE == kBf16) ? static_cast<long long>(colbase) * 2 : (MODE == kFp8) ? colbase : colbase / 2;
-  // a thread owns rows 4t .. 4t+3 of a k-step (the k index of an MMA is a free permutation)
-  const uint8_t* wq = sg.w + static_cast<long long>(tl.kbeg + wk * 16 + 4 * t) * pitch + col_byte;  // next step to copy
+  // The last k-step of the slice is copied by a careful path: rows past K (K not a multiple of
+  // 16) must read as zero and aligned pieces must not run past the end of the tensor.
+  const int careful_step = (((ksteps - 1) % p.wk) == wk) ? nsteps - 1 : -1;
+  const int row0 = tl.kbeg + wk * 16;  // first weight row of this warp's local step 0 (a multiple of 16)
   const long long step_stride = static_cast<long long>(p.wk) * 16 * pitch;
-  // NVFP4 block scales of the warp's 128 columns: 8 bytes per row at `soff`, fetched as the aligned words around them
-  const long long soff = static_cast<long long>(sg.n >> 1) + (colwarp >> 4);
-  const int sphase = static_cast<int>(soff & 7);
-  const bool scale_lane = (MODE == kNvfp4) && (g == 0 || (g == 1 && sphase != 0));
-  const uint8_t* sq = sg.w + static_cast<long long>(tl.kbeg + wk * 16 + 4 * t) * pitch + (soff & ~7LL) + g * 8;
+  const uint32_t ring = SmemAddr(smem) + static_cast<uint32_t>(warp) * (DEPTH * kSlotBytes);
 
-  const uint32_t ring = SmemAddr(smem) + static_cast<uint32_t>(warp) * static_cast<uint32_t>(D) * kSlotBytes;
-  const uint32_t lane_off = static_cast<uint32_t>(lane) * CB;
-
-  // copies local step s into its ring slot (steps are issued in increasing order: running pointers)
-  auto issue_step = [&](int s) {
-    const uint32_t slot = ring + static_cast<uint32_t>(s % D) * kSlotBytes;
-    const uint8_t* q0 = wq;
-    const uint8_t* s0 = sq;
-    wq += step_stride;
-    sq += step_stride;
-    const bool last = last_here && s == nsteps - 1;
-    const int r = tl.kbeg + (wk + s * p.wk) * 16 + 4 * t;
+  // ---- copy plan of this lane: up to four 16-byte pieces per k-step
+  const uint8_t* src[4];
+  uint32_t dst[4];
+  int prow[4];  // row of the step the piece belongs to
+  uint32_t pmask = 0;
+  uint32_t w_rd[4], s_rd[4];
+  if constexpr (MODE == kNvfp4) {
+    const long long col_byte = colwarp / 2;
+    const uint8_t* chunk0 = sg.w + static_cast<long long>(row0) * pitch + col_byte;
+    const int mis = static_cast<int>(pitch & 8);        // odd rows start 8 bytes off a 16-byte boundary
+    const int cshift = static_cast<int>(col_byte & 8);  // so does a chunk whose first column is 16 mod 32
+    const long long sabs = static_cast<long long>(sg.n >> 1) + (colwarp >> 4);
+    const int soff_even = static_cast<int>(sabs & 15), soff_odd = static_cast<int>((sabs + mis) & 15);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int slot = lane + 32 * j;
+      if (slot < 80) {  // nibble piece c of row r
+        const int r = slot / 5, c = slot - 5 * r;
+        const int shift = (((r & 1) ? mis : 0) + cshift) & 15;  // 0 or 8
+        if (c < 4 || shift != 0) pmask |= 1u << j;
+        prow[j] = r;
+        src[j] = chunk0 + static_cast<long long>(r) * pitch + (c * 16 - shift);
+        dst[j] = static_cast<uint32_t>(r * kNibPitch + c * 16);
+      } else {  // scale piece c of row r: the aligned 16 bytes around (or after) the eight scale bytes
+        const int sl = slot - 80;
+        const int r = sl >> 1, c = sl & 1;
+        const int o = (r & 1) ? soff_odd : soff_even;
+        if (sl < 32 && (c == 0 || o > 8)) pmask |= 1u << j;
+        prow[j] = r & 15;
+        src[j] = sg.w + static_cast<long long>(row0 + (r & 15)) * pitch + sabs - o + c * 16;
+        dst[j] = static_cast<uint32_t>(kNibBytes + (r & 15) * kSclPitch + c * 16);
+      }
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint32_t dst = slot + static_cast<uint32_t>(i) * (32 * CB) + lane_off;
-      const bool row_ok = !last || r + i < tl.kend;
-      if (cvalid) {
-        if constexpr (CB == 16) {
-          CpAsync16(dst, row_ok ? q0 + i * pitch : sg.w, row_ok ? 16 : 0);
-        } else {
-          CpAsync8(dst, row_ok ? q0 + i * pitch : sg.w, row_ok ? 8 : 0);
-        }
+      w_rd[i] = static_cast<uint32_t>((4 * t + i) * kNibPitch + ((((i & 1) ? mis : 0) + cshift) & 15) + g * 8);
+      s_rd[i] = static_cast<uint32_t>(kNibBytes + (4 * t + i) * kSclPitch + ((i & 1) ? soff_odd : soff_even) + g);
+    }
+  } else {
+    const long long col_byte = (MODE == kBf16) ? static_cast<long long>(colbase) * 2 : colbase;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      prow[i] = 4 * t + i;
+      src[i] = sg.w + static_cast<long long>(row0 + 4 * t + i) * pitch + col_byte;
+      dst[i] = static_cast<uint32_t>(i * (32 * CB) + lane * CB);
+      w_rd[i] = dst[i];
+      s_rd[i] = 0;
+    }
+    if (cvalid) pmask = 0xF;
+  }
+  // lanes past the tile's last column read zeros instead of the ring
+  const uint32_t zaddr = SmemAddr(s_zero);
+  const uint32_t vm = cvalid ? 0xFFFFFFFFu : 0u;
+  if (!cvalid) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      w_rd[i] = zaddr;
+      s_rd[i] = zaddr;
+    }
+  }
+
+  // copies local step s into ring slot `slot_addr` and advances the source pointers
+  auto issue_step = [&](int s, uint32_t slot_addr) {
+    if (s != careful_step) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (pmask & (1u << j)) CpAsync16(slot_addr + dst[j], src[j], 16);
+        src[j] += step_stride;
       }
-      if constexpr (MODE == kNvfp4) {
-        if (scale_lane) {
-          const uint32_t sdst = slot + kNibBytes + static_cast<uint32_t>(4 * t + i) * 16 + static_cast<uint32_t>(g) * 8;
-          int bytes = 8;
-          const uint8_t* src = s0 + i * pitch;
-          if (last) {
-            const long long room = sg.total_bytes - (src - sg.w);
-            bytes = !row_ok ? 0 : room >= 8 ? 8 : room > 0 ? static_cast<int>(room) : 0;
-            if (bytes == 0) src = sg.w;
-          }
-          CpAsync8(sdst, src, bytes);
+    } else {
+      const int r0 = row0 + s * p.wk * 16;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (pmask & (1u << j)) {
+          const long long room = sg.total_bytes - (src[j] - sg.w);
+          const int bytes = (r0 + prow[j] >= tl.kend) ? 0 : room >= 16 ? 16 : room > 0 ? static_cast<int>(room) : 0;
+          CpAsync16(slot_addr + dst[j], bytes > 0 ? src[j] : sg.w, bytes);
         }
+        src[j] += step_stride;
       }
     }
   };
 
   // weights do not depend on the predecessor kernel: get the first k-steps in flight, then wait
-  for (int d = 0; d < D - 1; ++d) {
-    if (d < nsteps) issue_step(d);
+#pragma unroll
+  for (int d = 0; d < DEPTH - 1; ++d) {
+    if (d < nsteps) issue_step(d, ring + d * kSlotBytes);
     CpAsyncCommit();
   }
   if (p.pdl_wait) GridDependencyWait();
@@ -714,50 +765,42 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const G
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
 
-  const uint32_t xs_addr = SmemAddr(xs) + static_cast<uint32_t>((g * p.xpitch + 4 * t) * 2);
+  uint32_t x_rd = SmemAddr(xs) + static_cast<uint32_t>((g * p.xpitch + 4 * t + wk * 16) * 2);
+  const uint32_t x_step = static_cast<uint32_t>(p.wk) * 32u;
   const bool has_row = g < p.M;
+  uint32_t rd_slot = ring;                                   // slot of step s
+  uint32_t wr_slot = ring + (DEPTH - 1) * kSlotBytes;        // slot of step s + DEPTH - 1
+  const uint32_t ring_end = ring + DEPTH * kSlotBytes;
   for (int s = 0; s < nsteps; ++s) {
-    // the slot consumed one step ago is free again: refill it with step s + D - 1
+    // the slot consumed one step ago is free again: refill it with step s + DEPTH - 1
     __syncwarp();
-    if (s + D - 1 < nsteps) issue_step(s + D - 1);
+    if (s + DEPTH - 1 < nsteps) issue_step(s + DEPTH - 1, wr_slot);
     CpAsyncCommit();
-    CpAsyncWait(D - 1);
+    asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
     __syncwarp();
-    const uint32_t slot = ring + static_cast<uint32_t>(s % D) * kSlotBytes;
+    const uint32_t base = rd_slot & vm;
     Raw<MODE> raw;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      if constexpr (CB == 16) {
-        raw.r[i] = Lds128(slot + static_cast<uint32_t>(i) * (32 * CB) + lane_off);
+      if constexpr (MODE == kNvfp4) {
+        raw.r[i] = Lds64(base + w_rd[i]);
+        raw.s[i] = Lds8(base + s_rd[i]);
       } else {
-        raw.r[i] = Lds64(slot + static_cast<uint32_t>(i) * (32 * CB) + lane_off);
-      }
-    }
-    if constexpr (MODE == kNvfp4) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        raw.s[i] = Lds8(slot + kNibBytes + static_cast<uint32_t>(4 * t + i) * 16 + static_cast<uint32_t>(sphase + g));
-    }
-    if (!cvalid) {  // columns past the tile: their ring bytes were never written
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        if constexpr (CB == 16) {
-          raw.r[i] = make_uint4(0, 0, 0, 0);
-        } else {
-          raw.r[i] = make_uint2(0, 0);
-        }
+        raw.r[i] = Lds128(base + w_rd[i]);
       }
     }
     uint32_t b0 = 0, b1 = 0;
     if (has_row) {
-      const uint2 xv = Lds64(xs_addr + static_cast<uint32_t>(wk + s * p.wk) * 32u);
+      const uint2 xv = Lds64(x_rd);
       b0 = xv.x;
       b1 = xv.y;
     }
-    if (p.debug & 2) {  // measurement aid: consume the bytes without dequantising
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[0][i] += __uint_as_float((raw.r[i].x ^ raw.r[i].y) & 0x3FFFFFFFu);
-    } else if constexpr (MODE == kBf16) {
+    x_rd += x_step;
+    rd_slot += kSlotBytes;
+    if (rd_slot == ring_end) rd_slot = ring;
+    wr_slot += kSlotBytes;
+    if (wr_slot == ring_end) wr_slot = ring;
+    if constexpr (MODE == kBf16) {
       ComputeStep<MODE, false>(acc, raw, b0, b1);
     } else {
       if (slow) {
@@ -767,7 +810,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const G
       }
     }
   }
-  CpAsyncWait(0);
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   if (p.trigger == 2) GridLaunchDependents();
   __syncthreads();
   Epilogue<MODE>(p, tl, acc, smem, sh, warp_has_cols);
@@ -967,6 +1010,15 @@ cudaError_t ConfigureKernel(K kernel) {
 }
 
 template <int MODE>
+cudaError_t ConfigureDirect() {
+  cudaError_t err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 3>);
+  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 4>);
+  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 6>);
+  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 8>);
+  return err;
+}
+
+template <int MODE>
 cudaError_t LaunchMode(const GemmParams& p, const Plan& plan, size_t smem, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(p.seg[p.nseg - 1].tile_begin + p.seg[p.nseg - 1].tiles),
@@ -990,7 +1042,15 @@ cudaError_t LaunchMode(const GemmParams& p, const Plan& plan, size_t smem, cudaS
   }
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
-  if (plan.direct) return cudaLaunchKernelEx(&cfg, SkinnyGemmDirectKernel<MODE>, p);
+  if (plan.direct) {
+    switch (plan.stages) {
+      case 3: return cudaLaunchKernelEx(&cfg, SkinnyGemmDirectKernel<MODE, 3>, p);
+      case 4: return cudaLaunchKernelEx(&cfg, SkinnyGemmDirectKernel<MODE, 4>, p);
+      case 6: return cudaLaunchKernelEx(&cfg, SkinnyGemmDirectKernel<MODE, 6>, p);
+      case 8: return cudaLaunchKernelEx(&cfg, SkinnyGemmDirectKernel<MODE, 8>, p);
+      default: return cudaErrorInvalidValue;
+    }
+  }
   return cudaLaunchKernelEx(&cfg, SkinnyGemmRingKernel<MODE>, p);
 }
 
@@ -1017,9 +1077,9 @@ int QueryMaxActiveClusters(int mode, int direct, int threads, size_t smem, int c
   if (it != cache.end()) return it->second;
   const void* fn = nullptr;
   switch (mode) {
-    case kBf16: fn = direct ? (const void*)SkinnyGemmDirectKernel<kBf16> : (const void*)SkinnyGemmRingKernel<kBf16>; break;
-    case kFp8: fn = direct ? (const void*)SkinnyGemmDirectKernel<kFp8> : (const void*)SkinnyGemmRingKernel<kFp8>; break;
-    default: fn = direct ? (const void*)SkinnyGemmDirectKernel<kNvfp4> : (const void*)SkinnyGemmRingKernel<kNvfp4>; break;
+    case kBf16: fn = direct ? (const void*)SkinnyGemmDirectKernel<kBf16, 4> : (const void*)SkinnyGemmRingKernel<kBf16>; break;
+    case kFp8: fn = direct ? (const void*)SkinnyGemmDirectKernel<kFp8, 4> : (const void*)SkinnyGemmRingKernel<kFp8>; break;
+    default: fn = direct ? (const void*)SkinnyGemmDirectKernel<kNvfp4, 4> : (const void*)SkinnyGemmRingKernel<kNvfp4>; break;
   }
   int result = 0;
   if (g_max_dynamic_smem > 0 && smem_key > static_cast<size_t>(g_max_dynamic_smem)) {
@@ -1055,9 +1115,9 @@ cudaError_t ConfigureSkinnyGemmKernels() {
   static std::once_flag once;
   static cudaError_t status = cudaSuccess;
   std::call_once(once, [] {
-    status = ConfigureKernel(SkinnyGemmDirectKernel<kBf16>);
-    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmDirectKernel<kFp8>);
-    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmDirectKernel<kNvfp4>);
+    status = ConfigureDirect<kBf16>();
+    if (status == cudaSuccess) status = ConfigureDirect<kFp8>();
+    if (status == cudaSuccess) status = ConfigureDirect<kNvfp4>();
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRingKernel<kBf16>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRingKernel<kFp8>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRingKernel<kNvfp4>);
@@ -1079,7 +1139,7 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
   p.stage_bytes = (R * (p.tile_row_bytes + p.scale_row_bytes) + 127) & ~127;
   const int TNc = plan.wn * geom.cols_per_warp;
   const int red_bytes = (plan.wk + (plan.cluster > 1 ? 1 : 0)) * p.M * TNc * 4;
-  const int direct_slot = 4 * 32 * geom.bytes_per_thread + (mode == kNvfp4 ? 256 : 0);
+  const int direct_slot = mode == kNvfp4 ? 16 * 80 + 16 * 32 : 4 * 32 * geom.bytes_per_thread;
   const int ring = plan.direct ? plan.wn * plan.wk * plan.stages * direct_slot : plan.stages * p.stage_bytes;
   p.ring_bytes = (std::max(ring, red_bytes) + 127) & ~127;
   const int ksteps = (p.K + 15) / 16;
