@@ -163,6 +163,18 @@ QFG_API int qfg_lmhead_create(const float* w_scale, size_t n_w_scale, int trigge
 QFG_API int qfg_lmhead_compute(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
                        int64_t n, int64_t col_offset, void* workspace, int64_t* idx, float* val,
                        uint64_t* key, void* logits, void* stream);
+/* qfg_lmhead_compute for callers that cannot provide device memory of their own: hosts that
+ * forbid allocation once serving has started, or hooks that are handed nothing but their inputs
+ * and outputs.  No counterpart in the reference (its ops never need scratch memory).  The keys
+ * and the counter live in a 256-byte array built into the library, so: at most
+ * qfg_lmhead_static_max_rows() (8) rows per call, larger m is refused with QFG_INVALID_ARGUMENT;
+ * all calls on a GPU share the array, so calls that overlap on that GPU race (one stream is
+ * safe); the first call on each GPU looks the array up and clears it synchronously and should
+ * therefore precede any stream capture.  Nothing is allocated or freed by any call. */
+QFG_API size_t qfg_lmhead_static_max_rows(void);
+QFG_API int qfg_lmhead_compute_static(const qfg_lmhead* op, const void* x, int64_t m, int64_t k,
+                                      const qfg_tensor2d* weight, int64_t n, int64_t col_offset, int64_t* idx,
+                                      float* val, uint64_t* key, void* logits, void* stream);
 QFG_API int qfg_lmhead_set_option(qfg_lmhead* op, const char* key, const char* value);
 QFG_API void qfg_lmhead_destroy(qfg_lmhead* op);
 

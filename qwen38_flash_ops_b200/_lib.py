@@ -22,7 +22,8 @@ EXPORTS = (
     "qfg_skinny_gemm_describe", "qfg_plan_describe", "qfg_skinny_gemm_destroy",
     "qfg_argmax_rows",
     "qfg_dequant_create", "qfg_dequant_compute", "qfg_dequant_destroy",
-    "qfg_lmhead_workspace_bytes", "qfg_lmhead_create", "qfg_lmhead_compute", "qfg_lmhead_set_option",
+    "qfg_lmhead_workspace_bytes", "qfg_lmhead_create", "qfg_lmhead_compute", "qfg_lmhead_static_max_rows",
+    "qfg_lmhead_compute_static", "qfg_lmhead_set_option",
     "qfg_lmhead_destroy", "qfg_lmhead_combine",
 )
 
@@ -71,6 +72,9 @@ def load() -> ctypes.CDLL:
     lib.qfg_lmhead_create.argtypes = [POINTER(c_float), c_size_t, c_int, POINTER(c_void_p)]
     lib.qfg_lmhead_compute.argtypes = [c_void_p, c_void_p, c_int64, c_int64, POINTER(Tensor2D), c_int64, c_int64,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.qfg_lmhead_static_max_rows.restype = c_size_t
+    lib.qfg_lmhead_compute_static.argtypes = [c_void_p, c_void_p, c_int64, c_int64, POINTER(Tensor2D), c_int64, c_int64,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.qfg_lmhead_set_option.argtypes = [c_void_p, c_char_p, c_char_p]
     lib.qfg_lmhead_destroy.argtypes = [c_void_p]
     lib.qfg_lmhead_destroy.restype = None

@@ -198,6 +198,22 @@ class LmHeadArgmax:
                                            lg.data_ptr() if logits else None, _stream_ptr()))
         return (idx, val, key, lg) if logits else (idx, val, key)
 
+    def call_static(self, x: torch.Tensor, w: torch.Tensor, n: int, col_offset: int = 0, out=None):
+        """The same computation through qfg_lmhead_compute_static: the scratch is the library's
+        built-in array, nothing is taken from this instance's workspace.  `out` must be given by
+        callers that may not allocate; at most 8 rows; calls must not overlap on one GPU."""
+        _require_cuda(x, "x")
+        k = x.shape[-1]
+        m = x.numel() // k
+        t = _tensor2d(w)
+        if out is None:
+            out = (torch.empty(m, dtype=torch.int64, device=x.device), torch.empty(m, dtype=torch.float32, device=x.device),
+                   torch.empty(m, dtype=torch.int64, device=x.device))
+        idx, val, key = out
+        check(self._lib.qfg_lmhead_compute_static(self._h, x.data_ptr(), m, k, ctypes.byref(t), int(n), int(col_offset),
+                                                  idx.data_ptr(), val.data_ptr(), key.data_ptr(), None, _stream_ptr()))
+        return idx, val, key
+
     def __del__(self):
         h = getattr(self, "_h", None)
         if h:
