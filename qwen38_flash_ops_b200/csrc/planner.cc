@@ -19,17 +19,19 @@ namespace {
 
 double BytesPerCol(int mode) { return mode == kBf16 ? 2.0 : mode == kFp8 ? 1.0 : 0.5; }
 
-int Granule(int mode, int row_align, bool direct) {
-  const ModeGeom g = GeomOf(mode);
-  if (direct) return g.cols_per_thread;  // a thread's chunk is one aligned 8/16-byte load
+int Granule(int mode, int row_align, bool direct, int wide = 1) {
+  const ModeGeom g = GeomOf(mode, direct ? wide : 1);
+  if (direct) return g.cols_per_thread;  // tiles are whole thread chunks
   const int cols_per_vec = static_cast<int>(row_align / BytesPerCol(mode));
   return std::max(g.cols_per_thread, cols_per_vec);
 }
 
 // The register-streaming kernel needs whole thread chunks and rows aligned to its load width.
-bool DirectEligible(const PlanInput& in) {
-  const ModeGeom g = GeomOf(in.mode);
-  if (in.row_align < g.bytes_per_thread) return false;
+bool DirectEligible(const PlanInput& in, int wide = 1) {
+  const ModeGeom g = GeomOf(in.mode, wide);
+  // BF16 / FP8 lanes copy their own 16 bytes; NVFP4 rows are copied as aligned 16-byte pieces
+  // around chunks that may start 8 bytes off
+  if (in.row_align < (in.mode == kNvfp4 ? 8 : 16)) return false;
   for (int s = 0; s < in.nseg; ++s) {
     if (in.n[s] % g.cols_per_thread != 0) return false;
   }
@@ -57,7 +59,7 @@ void FitRing(const PlanInput& in, int rows, Plan* p) {
   if (p->direct) {
     // warp-private rings: as deep as the CTA's share of shared memory allows, at most 8 k-steps
     const int warps = p->wn * p->wk;
-    const int per_sm = std::max(1, 20 / warps);
+    const int per_sm = std::max(1, (p->wide == 2 ? 16 : 20) / warps);
     const size_t budget = static_cast<size_t>(220 * 1024) / per_sm;
     p->ks = 1;
     // the kernel is compiled for ring depths 8, 6, 4 and 3
@@ -79,13 +81,13 @@ void FitRing(const PlanInput& in, int rows, Plan* p) {
 }
 
 size_t SmemBytes(const Plan& plan, int mode, int rows, int K) {
-  const ModeGeom g = GeomOf(mode);
+  const ModeGeom g = GeomOf(mode, plan.direct ? plan.wide : 1);
   const int tb = plan.wn * g.bytes_per_warp;
   const int srb = mode == kNvfp4 ? (plan.wn * 8 + 16 + 15) & ~15 : 0;
   const int stage = (plan.rows_per_stage() * (tb + srb) + 127) & ~127;
   const int tnc = plan.wn * g.cols_per_warp;
   const int red = (plan.wk + (plan.cluster > 1 ? 1 : 0)) * rows * tnc * 4;
-  const int direct_slot = mode == kNvfp4 ? 16 * 80 + 16 * 32 : 4 * 32 * g.bytes_per_thread;
+  const int direct_slot = DirectSlotBytes(mode, plan.wide);
   const int ring_raw = plan.direct ? plan.wn * plan.wk * plan.stages * direct_slot : plan.stages * stage;
   const int ring = (std::max(ring_raw, red) + 127) & ~127;
   const int ksteps = (K + 15) / 16;
@@ -95,7 +97,7 @@ size_t SmemBytes(const Plan& plan, int mode, int rows, int K) {
 }
 
 void DistributeTiles(const PlanInput& in, int total_tiles, Plan* plan) {
-  const ModeGeom g = GeomOf(in.mode);
+  const ModeGeom g = GeomOf(in.mode, plan->direct ? plan->wide : 1);
   const int max_cols = plan->wn * g.cols_per_warp;
   long long sum_n = 0;
   int min_t[kMaxSeg], given = 0;
@@ -141,21 +143,47 @@ void DistributeTiles(const PlanInput& in, int total_tiles, Plan* plan) {
 //   balance          - CTAs versus the resident CTA slots of whole waves (16 warps per SM);
 //   pipeline length  - k-steps per warp, so that fill and drain of the load pipeline amortise;
 //   row width        - contiguous bytes a CTA reads per weight row.
+// Launch shapes measured best on B200 (148 SMs) for the decode GEMMs of the model this library
+// serves; the counterpart of the reference's H200 table (src/fused_gemm/fused_gemm.cu:132-156).
+// Every other shape, and these shapes on a different SM count, go through the scoring rule below.
+struct TunedShape {
+  int mode, K, nseg;
+  int n[kMaxSeg];
+  const char* spec;
+};
+const TunedShape kTunedB200[] = {
+    {kBf16, 5120, 1, {5120, 0, 0, 0}, "direct=1,wn=1,wk=6,cluster=4,waves=1"},
+    {kFp8, 5120, 3, {8192, 1024, 1024, 0}, "direct=1,wn=1,wk=6,cluster=4,waves=1"},
+    {kNvfp4, 5120, 2, {17408, 17408, 0, 0}, "direct=1,wide=2,wn=1,wk=8,cluster=2,waves=1"},
+    {kNvfp4, 17408, 1, {5120, 0, 0, 0}, "direct=1,wide=1,wn=5,wk=4,cluster=8,waves=1"},
+    {kNvfp4, 5120, 1, {151936, 0, 0, 0}, "direct=1,wide=1,wn=9,wk=2,cluster=1,waves=1"},
+};
+
 Plan ChoosePlan(const PlanInput& in) {
-  const ModeGeom g = GeomOf(in.mode);
+  if (in.sm_count == 148 && DirectEligible(in)) {
+    for (const TunedShape& t : kTunedB200) {
+      bool same = t.mode == in.mode && t.K == in.K && t.nseg == in.nseg;
+      for (int s = 0; same && s < in.nseg; ++s) same = t.n[s] == in.n[s];
+      Plan tuned;
+      if (same && ApplyPlanOverrides(t.spec, in, &tuned)) return tuned;
+    }
+  }
   const double bpc = BytesPerCol(in.mode);
   long long sum_n = 0;
   for (int s = 0; s < in.nseg; ++s) sum_n += in.n[s];
   const bool direct = DirectEligible(in);
-  const int gran = Granule(in.mode, in.row_align, direct);
-  long long granules = 0;
-  for (int s = 0; s < in.nseg; ++s) granules += (in.n[s] + gran - 1) / gran;
   const int ksteps = (in.K + 15) / 16;
-  const int max_warps = direct ? 20 : 8;
-  const int max_wn = direct ? 10 : 8;
 
   Plan best;
   double best_score = -1.0;
+  for (int wide = 1; wide <= 2; ++wide) {
+  if (wide == 2 && (in.mode != kNvfp4 || !DirectEligible(in, 2))) break;
+  const ModeGeom g = GeomOf(in.mode, direct ? wide : 1);
+  const int gran = Granule(in.mode, in.row_align, direct, wide);
+  long long granules = 0;
+  for (int s = 0; s < in.nseg; ++s) granules += (in.n[s] + gran - 1) / gran;
+  const int max_warps = direct ? (wide == 2 ? 16 : 20) : 8;
+  const int max_wn = direct ? 10 : 8;
   for (int c = 1; c <= 8; c *= 2) {
     if (c > 1 && in.K / c < 256) continue;
     for (int wn = 1; wn <= max_wn; ++wn) {
@@ -169,6 +197,7 @@ Plan ChoosePlan(const PlanInput& in) {
         p.cluster = c;
         p.gran = gran;
         p.direct = direct ? 1 : 0;
+        p.wide = wide;
         p.ks = 1;
         p.stages = 3;
         // eight x rows must fit beside the partial sums, whatever the row count of a call
@@ -178,7 +207,7 @@ Plan ChoosePlan(const PlanInput& in) {
         // clusters that can be resident at once: GPC boundaries cost a cluster launch some SMs
         int cluster_slots;
         if (in.max_clusters != nullptr) {
-          cluster_slots = in.max_clusters(in.mode, p.direct, wn * wk * 32, smem, c);
+          cluster_slots = in.max_clusters(in.mode, p.direct * p.wide, wn * wk * 32, smem, c);
         } else {
           cluster_slots = c == 1 ? per_sm * in.sm_count : static_cast<int>(per_sm * in.sm_count * 0.89) / c;
         }
@@ -196,12 +225,15 @@ Plan ChoosePlan(const PlanInput& in) {
           const double widest = std::ceil(static_cast<double>(granules) / tiles) * gran;
           const double lane_eff = std::min(1.0, (static_cast<double>(sum_n) / tiles) / max_cols) *
                                   ((static_cast<double>(sum_n) / tiles) / std::max(widest, 1.0));
-          const double warps_per_sm = std::min(16.0, static_cast<double>(per_sm * wn * wk));  // 16 warps saturate an SM
+          // 16 warps saturate an SM; a wide warp keeps twice the bytes in flight
+          const double warps_per_sm = std::min(16.0, static_cast<double>(per_sm * wn * wk * wide));
           const double steps = static_cast<double>(ksteps) / c / wk / need;
           const double kfactor = std::min(1.0, steps / 12.0);
           const double row_bytes = (static_cast<double>(sum_n) / tiles) * bpc;
           const double rowfactor = std::sqrt(std::min(1.0, row_bytes / 128.0));
           double score = lane_eff * balance * (warps_per_sm / 16.0) * (0.5 + 0.5 * kfactor) * rowfactor;
+          // wider threads fetch fewer partly used sectors and spend fewer instructions per weight
+          if (wide == 2) score *= 0.9;  // measured: the wide warp pays off only where tiles are narrow and K is split
           score *= 1.0 - 0.015 * std::log2(static_cast<double>(c)) - 0.01 * (need - 1);
           if (score > best_score) {
             best_score = score;
@@ -213,6 +245,7 @@ Plan ChoosePlan(const PlanInput& in) {
       }
     }
   }
+  }
   FitRing(in, in.max_rows, &best);
   return best;
 }
@@ -222,14 +255,14 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
   std::stringstream ss(spec);
   std::string item;
   int ctas = -1, waves = -1;
-  bool ring_given = false;
+  bool ring_given = false, wide_given = false, shape_given = false;
   while (std::getline(ss, item, ',')) {
     const size_t eq = item.find('=');
     if (eq == std::string::npos) return false;
     const std::string key = item.substr(0, eq);
     const int val = std::atoi(item.substr(eq + 1).c_str());
-    if (key == "wn") plan->wn = val;
-    else if (key == "wk") plan->wk = val;
+    if (key == "wn") { plan->wn = val; shape_given = true; }
+    else if (key == "wk") { plan->wk = val; shape_given = true; }
     else if (key == "ks") { plan->ks = val; ring_given = true; }
     else if (key == "stages") { plan->stages = val; ring_given = true; }
     else if (key == "cluster") plan->cluster = val;
@@ -237,29 +270,36 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
     else if (key == "waves") waves = val;
     else if (key == "gran") plan->gran = val;
     else if (key == "direct") plan->direct = val;
+    else if (key == "wide") { plan->wide = val; wide_given = true; }
     else return false;
   }
   auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
-  if (plan->direct != 0 && !DirectEligible(in)) return false;
+  if (shape_given && !wide_given) plan->wide = 1;  // a warp shape without a width means the 128-column warp
+  if (plan->wide != 1 && plan->wide != 2) return false;
+  if (plan->direct == 0 || in.mode != kNvfp4) plan->wide = 1;
+  if (plan->direct != 0 && !DirectEligible(in, plan->wide)) return false;
   if (plan->direct != 0 && ring_given && plan->stages != 3 && plan->stages != 4 && plan->stages != 6 && plan->stages != 8) return false;
   plan->direct = plan->direct != 0 ? 1 : 0;
   if (plan->direct == 0 && plan->gran < Granule(in.mode, in.row_align, false)) plan->gran = Granule(in.mode, in.row_align, false);
   if ((plan->direct == 0 && (!pow2(plan->wn) || !pow2(plan->wk) || plan->wn * plan->wk > 8)) || plan->wn < 1 || plan->wk < 1 ||
-      plan->wn * plan->wk > 20 || plan->wn > 10 || plan->ks < 1 || plan->ks > 8 ||
+      plan->wn * plan->wk > (plan->wide == 2 ? 16 : 20) || plan->wn > 10 || plan->ks < 1 || plan->ks > 8 ||
       plan->stages < 2 || plan->stages > 8 || plan->cluster < 1 || plan->cluster > 8 || !pow2(plan->cluster)) {
     return false;
   }
-  if (plan->gran % Granule(in.mode, in.row_align, plan->direct != 0) != 0) return false;
+  if (plan->gran % Granule(in.mode, in.row_align, plan->direct != 0, plan->wide) != 0) plan->gran = Granule(in.mode, in.row_align, plan->direct != 0, plan->wide);
   if (!ring_given) FitRing(in, in.max_rows, plan);
-  const ModeGeom g = GeomOf(in.mode);
+  const ModeGeom g = GeomOf(in.mode, plan->direct ? plan->wide : 1);
   int total = ctas > 0 ? std::max(1, ctas / plan->cluster) : 0;
   if (waves > 0) {
     // as many tiles as `waves` full waves of co-resident clusters hold
-    const size_t smem = SmemBytes(*plan, in.mode, kMaxRows, in.K);
+    // tiles must not depend on the rows of the call: size the launch as for a full row block
+    Plan full = *plan;
+    if (!ring_given) FitRing(in, kMaxRows, &full);
+    const size_t smem = SmemBytes(full, in.mode, kMaxRows, in.K);
     const int per_sm = std::max(1, std::min(20 / (plan->wn * plan->wk), static_cast<int>((220 * 1024) / std::max<size_t>(smem, 1))));
     int cluster_slots;
     if (in.max_clusters != nullptr) {
-      cluster_slots = in.max_clusters(in.mode, plan->direct, plan->threads(), smem, plan->cluster);
+      cluster_slots = in.max_clusters(in.mode, plan->direct * plan->wide, plan->threads(), smem, plan->cluster);
     } else {
       cluster_slots = plan->cluster == 1 ? per_sm * in.sm_count : static_cast<int>(per_sm * in.sm_count * 0.89) / plan->cluster;
     }
@@ -279,8 +319,8 @@ std::string DescribePlan(const Plan& plan, const PlanInput& in) {
   int tiles = 0;
   for (int s = 0; s < in.nseg; ++s) tiles += plan.tiles[s];
   std::snprintf(buf, sizeof(buf),
-                "direct=%d,wn=%d,wk=%d,ks=%d,stages=%d,cluster=%d,gran=%d,tiles=%d,ctas=%d,threads=%d,smem=%zu",
-                plan.direct, plan.wn, plan.wk, plan.ks, plan.stages, plan.cluster, plan.gran, tiles,
+                "direct=%d,wide=%d,wn=%d,wk=%d,ks=%d,stages=%d,cluster=%d,gran=%d,tiles=%d,ctas=%d,threads=%d,smem=%zu",
+                plan.direct, plan.wide, plan.wn, plan.wk, plan.ks, plan.stages, plan.cluster, plan.gran, tiles,
                 tiles * plan.cluster, plan.threads(),
                 SmemBytes(plan, in.mode, in.max_rows, in.K));
   return buf;

@@ -25,12 +25,20 @@ struct ModeGeom {
   int cols_per_warp;     // 8 thread groups side by side
   int bytes_per_warp;    // per weight row
 };
-inline ModeGeom GeomOf(int mode) {
+// `wide` = 2: the NVFP4 direct kernel's variant whose warps cover 256 columns (a thread owns two
+// 16-column groups 128 columns apart).
+inline ModeGeom GeomOf(int mode, int wide = 1) {
   switch (mode) {
     case kBf16: return {8, 16, 64, 128};
     case kFp8: return {16, 16, 128, 128};
-    default: return {16, 8, 128, 64};
+    default: return wide == 2 ? ModeGeom{16, 8, 256, 128} : ModeGeom{16, 8, 128, 64};
   }
+}
+// Bytes of one warp's ring slot (one k-step) in the direct kernel.
+inline int DirectSlotBytes(int mode, int wide) {
+  if (mode != kNvfp4) return 4 * 32 * 16;
+  const int w = wide == 2 ? 2 : 1;
+  return 16 * (64 * w + 16) + 32 + 16 * 32 + 96;
 }
 
 // Launch geometry.  It depends on (K, segment widths, weight type) only - never on the
@@ -43,7 +51,8 @@ struct Plan {
   int cluster = 1;  // CTAs splitting K, reduced through distributed shared memory
   int tiles[kMaxSeg] = {0, 0, 0, 0};  // column tiles per segment
   int gran = 16;    // columns per granule of the balanced column partition
-  int direct = 1;   // 1: warps stream weights straight into registers; 0: cp.async shared-memory ring
+  int direct = 1;   // 1: warp-private cp.async rings, no CTA barrier in the K loop; 0: CTA-wide ring
+  int wide = 1;     // NVFP4 direct kernel: 16-column groups per thread (1 or 2)
   int threads() const { return 32 * wn * wk; }
   int rows_per_stage() const { return 16 * wk * ks; }
 };

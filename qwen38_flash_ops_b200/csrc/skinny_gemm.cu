@@ -45,7 +45,8 @@ namespace {
 
 namespace cg = cooperative_groups;
 
-constexpr int kMaxThreads = 640;   // direct kernel: up to 20 warps (at most 102 registers per thread)
+constexpr int kMaxThreads = 640;      // direct kernel: up to 20 warps (at most 102 registers per thread)
+constexpr int kMaxThreadsWide = 512;  // its 32-columns-per-thread NVFP4 variant: up to 16 warps (128 registers)
 constexpr int kRingThreads = 256;  // ring kernel: up to 8 warps
 
 // ------------------------------------------------------------------------------ PTX helpers
@@ -188,37 +189,42 @@ __device__ __forceinline__ unsigned long long PackKey(float v, long long idx) {
   return (static_cast<unsigned long long>(ord) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(idx));
 }
 
-template <int MODE>
+// W: 16-column groups a thread of the NVFP4 direct kernel owns.  With W = 2 a warp covers 256
+// columns and thread group g owns groups g and g + 8 of them, i.e. two 8-byte runs 64 bytes
+// apart in every row: fewer partly used sectors and less loop overhead per weight, and the
+// 8-byte shared-memory reads stay aligned on rows that start 8 bytes off a 16-byte boundary.
+template <int MODE, int W = 1>
 struct Geom;
 template <>
-struct Geom<kBf16> {
+struct Geom<kBf16, 1> {
   static constexpr int kColsPerThread = 8, kBytesPerThread = 16, kMmas = 4;
 };
 template <>
-struct Geom<kFp8> {
+struct Geom<kFp8, 1> {
   static constexpr int kColsPerThread = 16, kBytesPerThread = 16, kMmas = 8;
 };
-template <>
-struct Geom<kNvfp4> {
-  static constexpr int kColsPerThread = 16, kBytesPerThread = 8, kMmas = 8;
+template <int W>
+struct Geom<kNvfp4, W> {
+  static constexpr int kColsPerThread = 16, kBytesPerThread = 8, kMmas = 8 * W;
 };
 
 // The raw bytes of one k-step of one thread: four consecutive weight rows (4t .. 4t+3 of the
-// step) of its columns, plus the four NVFP4 block-scale bytes.  The B fragment of the same
-// thread is x[4t .. 4t+3] of the step: the k index of an MMA is a free permutation.
-template <int MODE>
+// step) of its columns, plus the NVFP4 block-scale bytes of those rows (one byte per 16-column
+// group).  The B fragment of the same thread is x[4t .. 4t+3] of the step: the k index of an MMA
+// is a free permutation.
+template <int MODE, int W = 1>
 struct Raw {
   uint4 r[4];
 };
-template <>
-struct Raw<kNvfp4> {
-  uint2 r[4];
-  uint32_t s[4];
+template <int W>
+struct Raw<kNvfp4, W> {
+  uint2 r[W][4];
+  uint32_t s[W][4];
 };
 
 // One k-step of one warp from registers: dequantise to k-paired operands and run the MMAs.
-template <int MODE, bool SLOW>
-__device__ __forceinline__ void ComputeStep(float (&acc)[Geom<MODE>::kMmas][4], const Raw<MODE>& w, uint32_t b0,
+template <int MODE, bool SLOW, int W = 1>
+__device__ __forceinline__ void ComputeStep(float (&acc)[Geom<MODE, W>::kMmas][4], const Raw<MODE, W>& w, uint32_t b0,
                                             uint32_t b1) {
   constexpr bool kBf16Mma = (MODE == kBf16) || SLOW;
   if constexpr (MODE == kBf16) {
@@ -250,28 +256,32 @@ __device__ __forceinline__ void ComputeStep(float (&acc)[Geom<MODE>::kMmas][4], 
       Mma<kBf16Mma>(acc[2 * i + 1], p[2], p[3], q[2], q[3], b0, b1);
     }
   } else {
-    const uint32_t s_ab = CvtE4m3x2(Prmt(w.s[0], w.s[1], 0x0040u)), s_cd = CvtE4m3x2(Prmt(w.s[2], w.s[3], 0x0040u));
-    const uint32_t a[2] = {w.r[0].x, w.r[0].y}, b[2] = {w.r[1].x, w.r[1].y};
-    const uint32_t c[2] = {w.r[2].x, w.r[2].y}, d[2] = {w.r[3].x, w.r[3].y};
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      // byte q of `e_*`: (row A nibble, row B nibble) of column 8i + 2q; of `o_*`: column 8i + 2q + 1
-      uint32_t e_ab[4], o_ab[4], e_cd[4], o_cd[4];
-      CvtE2m1x8((a[i] & 0x0F0F0F0Fu) | ((b[i] << 4) & 0xF0F0F0F0u), e_ab);
-      CvtE2m1x8(((a[i] >> 4) & 0x0F0F0F0Fu) | (b[i] & 0xF0F0F0F0u), o_ab);
-      CvtE2m1x8((c[i] & 0x0F0F0F0Fu) | ((d[i] << 4) & 0xF0F0F0F0u), e_cd);
-      CvtE2m1x8(((c[i] >> 4) & 0x0F0F0F0Fu) | (d[i] & 0xF0F0F0F0u), o_cd);
+    for (int h = 0; h < W; ++h) {
+      const uint32_t s_ab = CvtE4m3x2(Prmt(w.s[h][0], w.s[h][1], 0x0040u));
+      const uint32_t s_cd = CvtE4m3x2(Prmt(w.s[h][2], w.s[h][3], 0x0040u));
+      const uint32_t a[2] = {w.r[h][0].x, w.r[h][0].y}, b[2] = {w.r[h][1].x, w.r[h][1].y};
+      const uint32_t c[2] = {w.r[h][2].x, w.r[h][2].y}, d[2] = {w.r[h][3].x, w.r[h][3].y};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint32_t a0 = Hmul2(e_ab[q], s_ab), a1 = Hmul2(o_ab[q], s_ab);
-        uint32_t a2 = Hmul2(e_cd[q], s_cd), a3 = Hmul2(o_cd[q], s_cd);
-        if constexpr (SLOW) {
-          a0 = HalfPairToBf16Pair(a0);
-          a1 = HalfPairToBf16Pair(a1);
-          a2 = HalfPairToBf16Pair(a2);
-          a3 = HalfPairToBf16Pair(a3);
+      for (int i = 0; i < 2; ++i) {
+        // byte q of `e_*`: (row A nibble, row B nibble) of column 8i + 2q; of `o_*`: column 8i + 2q + 1
+        uint32_t e_ab[4], o_ab[4], e_cd[4], o_cd[4];
+        CvtE2m1x8((a[i] & 0x0F0F0F0Fu) | ((b[i] << 4) & 0xF0F0F0F0u), e_ab);
+        CvtE2m1x8(((a[i] >> 4) & 0x0F0F0F0Fu) | (b[i] & 0xF0F0F0F0u), o_ab);
+        CvtE2m1x8((c[i] & 0x0F0F0F0Fu) | ((d[i] << 4) & 0xF0F0F0F0u), e_cd);
+        CvtE2m1x8(((c[i] >> 4) & 0x0F0F0F0Fu) | (d[i] & 0xF0F0F0F0u), o_cd);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t a0 = Hmul2(e_ab[q], s_ab), a1 = Hmul2(o_ab[q], s_ab);
+          uint32_t a2 = Hmul2(e_cd[q], s_cd), a3 = Hmul2(o_cd[q], s_cd);
+          if constexpr (SLOW) {
+            a0 = HalfPairToBf16Pair(a0);
+            a1 = HalfPairToBf16Pair(a1);
+            a2 = HalfPairToBf16Pair(a2);
+            a3 = HalfPairToBf16Pair(a3);
+          }
+          Mma<kBf16Mma>(acc[8 * h + 4 * i + q], a0, a1, a2, a3, b0, b1);
         }
-        Mma<kBf16Mma>(acc[4 * i + q], a0, a1, a2, a3, b0, b1);
       }
     }
   }
@@ -461,24 +471,26 @@ __device__ __forceinline__ bool StageX(const GemmParams& p, const Tile& tl, uint
 // Reduction of the accumulators (wk warps, then the cluster), scaling, rounding, stores, and the
 // fused argmax.  `smem` is reused for the partial sums; every thread of the CTA must call this
 // after a __syncthreads() that ends all use of the shared memory by the main loop.
-template <int MODE>
-__device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, float (&acc)[Geom<MODE>::kMmas][4],
+template <int MODE, int W = 1>
+__device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, float (&acc)[Geom<MODE, W>::kMmas][4],
                                          uint8_t* smem, SharedScratch& sh, bool warp_has_cols) {
-  using G = Geom<MODE>;
+  using G = Geom<MODE, W>;
   constexpr int NM = G::kMmas;
   const int tid = threadIdx.x, nthreads = blockDim.x;
   const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int wn = warp % p.wn, wk = warp / p.wn;
   const int M = p.M, C = tl.C, n0 = tl.n0, n1 = tl.n1;
   const Segment& sg = p.seg[tl.seg];
-  const int cols_per_warp = 8 * G::kColsPerThread;
+  const int cols_per_warp = 8 * G::kColsPerThread * W;
   const int TNc = p.wn * cols_per_warp;
   float* red = reinterpret_cast<float*>(smem);
   float* part = red + static_cast<size_t>(p.wk) * M * TNc;
   if (warp_has_cols) {
 #pragma unroll
     for (int j = 0; j < NM; ++j) {
-      const int cl = wn * cols_per_warp + g * G::kColsPerThread + 2 * j;
+      // MMA j covers columns 2 (j % 8), +1 of the thread's (j / 8)-th column group (128 columns apart)
+      const int per_group = G::kMmas / W;
+      const int cl = wn * cols_per_warp + (j / per_group) * 8 * G::kColsPerThread + g * G::kColsPerThread + 2 * (j % per_group);
       const int m0 = 2 * t, m1 = 2 * t + 1;
       if (m0 < M) *reinterpret_cast<float2*>(&red[(wk * M + m0) * TNc + cl]) = make_float2(acc[j][0], acc[j][2]);
       if (m1 < M) *reinterpret_cast<float2*>(&red[(wk * M + m1) * TNc + cl]) = make_float2(acc[j][1], acc[j][3]);
@@ -615,31 +627,58 @@ __device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, fl
 // ------------------------------------------------------------------------------ direct kernel
 // Every warp streams its own weight rows into a warp-private shared-memory ring with 16-byte
 // cp.async.cg copies (L1 bypass), DEPTH k-steps ahead of the MMAs.  There is no CTA barrier in
-// the K loop, and the bytes in flight per SM (warps x DEPTH x 1.8-2 KiB) are bounded by shared
+// the K loop, and the bytes in flight per SM (warps x DEPTH x 2-3 KiB) are bounded by shared
 // memory, not by registers.  Measured on B200: this copy pattern streams at over 6 TB/s with 16
 // warps per SM, where 8-byte copies through L1 or register loads at the same occupancy stay
 // below 4 TB/s.
 //
-// Ring slot of one warp.  BF16 / FP8: [4 rows][32 lanes][16 bytes], every lane copies the bytes it
-// consumes.  NVFP4: 16 rows of the warp's 64 nibble bytes at a pitch of 80 bytes, copied as
-// aligned 16-byte pieces (a chunk that starts 8 bytes off a 16-byte boundary - odd rows of a
-// weight whose packed pitch is 8 mod 16, like the 151936-column LM head, or a tile whose first
-// column is 16 mod 32 - takes five pieces and is read back at an offset of 8), followed by
-// 16 rows x 32 bytes holding the one or two aligned 16-byte pieces around the warp's eight
-// block-scale bytes.  Every lane owns at most four pieces; their source pointers advance by one
-// k-step stride per step.
-template <int MODE, int DEPTH>
-__global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const GemmParams p) {
-  using G = Geom<MODE>;
+// Ring slot of one warp.
+//   BF16 / FP8: [4 rows][32 lanes][16 bytes]; every lane copies exactly the bytes it consumes.
+//   NVFP4: the warp's 64 W nibble bytes of each of the 16 rows, copied as aligned 16-byte pieces
+//     (a chunk that starts 8 bytes off a 16-byte boundary - odd rows of a weight whose packed
+//     pitch is 8 mod 16, like the 151936-column LM head, or a tile whose first column is 16 mod
+//     32 - takes one piece more and is read back at an offset of 8), then the one or two aligned
+//     pieces around the warp's 8 W block-scale bytes of each row.  Rows 8..15 of the nibble area
+//     and every fourth row of the scale area are displaced by 32 bytes, which puts the four row
+//     groups a warp-wide shared-memory load touches into distinct banks.
+// A lane owns up to kPieces pieces; their sources are one 64-bit base, advanced by a k-step
+// stride per step, plus a 32-bit offset each.
+template <typename T>
+__device__ __forceinline__ void Pin(T& v) {
+  asm volatile("" : "+r"(v));  // keeps a loop invariant in its register instead of being recomputed
+}
+__device__ __forceinline__ void CpAsync16If(uint32_t pred, uint32_t dst, const uint8_t* base, uint32_t off) {
+  asm volatile(
+      "{ .reg .pred p; .reg .u64 a;\n"
+      " setp.ne.b32 p, %0, 0;\n"
+      " mad.wide.u32 a, %3, 1, %2;\n"
+      " @p cp.async.cg.shared.global [%1], [a], 16;\n}" ::"r"(pred), "r"(dst), "l"(base), "r"(off)
+      : "memory");
+}
+
+template <int MODE, int W>
+struct DirectSlot {
+  using G = Geom<MODE, W>;
+  static constexpr int kNibPitch = 64 * W + 16;                 // NVFP4: bytes per nibble row of a warp
+  static constexpr int kNibBytes = MODE == kNvfp4 ? 16 * kNibPitch + 32 : 4 * 32 * G::kBytesPerThread;
+  static constexpr int kSclPitch = 32;
+  static constexpr int kSclBytes = MODE == kNvfp4 ? 16 * kSclPitch + 96 : 0;
+  static constexpr int kBytes = kNibBytes + kSclBytes;
+  static constexpr int kPiecesPerRow = 4 * W + 3;               // NVFP4: 4W+1 nibble pieces, 2 scale pieces
+  static constexpr int kPieces = MODE == kNvfp4 ? (16 * kPiecesPerRow + 31) / 32 : 4;
+  __device__ static constexpr int NibRow(int r) { return r * kNibPitch + ((r >> 3) & 1) * 32; }
+  __device__ static constexpr int SclRow(int r) { return kNibBytes + r * kSclPitch + (r >> 2) * 32; }
+};
+
+template <int MODE, int DEPTH, int W>
+__global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) SkinnyGemmDirectKernel(const GemmParams p) {
+  using G = Geom<MODE, W>;
+  using S = DirectSlot<MODE, W>;
   constexpr int NM = G::kMmas;
   constexpr int CB = G::kBytesPerThread;
-  constexpr int kNibPitch = 80;  // NVFP4: shared-memory bytes per weight row of a warp
-  constexpr int kSclPitch = 32;
-  constexpr int kNibBytes = MODE == kNvfp4 ? 16 * kNibPitch : 4 * 32 * CB;
-  constexpr int kSlotBytes = kNibBytes + (MODE == kNvfp4 ? 16 * kSclPitch : 0);
+  constexpr int NP = S::kPieces;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ SharedScratch sh;
-  __shared__ __align__(16) uint32_t s_zero[4];
 
   if (p.trigger == 1) GridLaunchDependents();
   const int tid = threadIdx.x;
@@ -648,10 +687,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const G
   const Tile tl = LocateTile(p);
   const Segment& sg = p.seg[tl.seg];
   const long long pitch = sg.pitch;
-  if (tid < 4) s_zero[tid] = 0;
 
   // this thread's columns and this warp's k-steps (local step s is k-step wk + s * p.wk of the slice)
-  const int cols_per_warp = 8 * G::kColsPerThread;
+  const int cols_per_warp = 8 * G::kColsPerThread * W;
   const int colwarp = tl.n0 + wn * cols_per_warp;
   const int colbase = colwarp + g * G::kColsPerThread;
   const bool warp_has_cols = colwarp < tl.n1;
@@ -663,95 +701,103 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const G
   const int careful_step = (((ksteps - 1) % p.wk) == wk) ? nsteps - 1 : -1;
   const int row0 = tl.kbeg + wk * 16;  // first weight row of this warp's local step 0 (a multiple of 16)
   const long long step_stride = static_cast<long long>(p.wk) * 16 * pitch;
-  const uint32_t ring = SmemAddr(smem) + static_cast<uint32_t>(warp) * (DEPTH * kSlotBytes);
+  const uint32_t ring = SmemAddr(smem) + static_cast<uint32_t>(warp) * (DEPTH * S::kBytes);
 
-  // ---- copy plan of this lane: up to four 16-byte pieces per k-step
-  const uint8_t* src[4];
-  uint32_t dst[4];
-  int prow[4];  // row of the step the piece belongs to
-  uint32_t pmask = 0;
-  uint32_t w_rd[4], s_rd[4];
+  // ---- copy plan of this lane: source offset from `gbase`, destination offset in the slot
+  const long long warp_col_byte = MODE == kBf16 ? static_cast<long long>(colwarp) * 2 : MODE == kFp8 ? colwarp : colwarp / 2;
+  const uint8_t* gbase = sg.w + static_cast<long long>(row0) * pitch + warp_col_byte - 16;
+  uint32_t off[NP], dst[NP], pmask = 0;
+  uint32_t rd_w[2], rd_s[2];  // read offsets of the even and the odd rows of this lane
   if constexpr (MODE == kNvfp4) {
-    const long long col_byte = colwarp / 2;
-    const uint8_t* chunk0 = sg.w + static_cast<long long>(row0) * pitch + col_byte;
-    const int mis = static_cast<int>(pitch & 8);        // odd rows start 8 bytes off a 16-byte boundary
-    const int cshift = static_cast<int>(col_byte & 8);  // so does a chunk whose first column is 16 mod 32
-    const long long sabs = static_cast<long long>(sg.n >> 1) + (colwarp >> 4);
-    const int soff_even = static_cast<int>(sabs & 15), soff_odd = static_cast<int>((sabs + mis) & 15);
+    const int mis = static_cast<int>(pitch & 8);              // odd rows start 8 bytes off a 16-byte boundary
+    const int cshift = static_cast<int>(warp_col_byte & 8);   // so does a chunk whose first column is 16 mod 32
+    const long long sabs = static_cast<long long>(sg.n >> 1) + (colwarp >> 4);  // scale bytes within the row
+    const int so_even = static_cast<int>(sabs & 15), so_odd = static_cast<int>((sabs + mis) & 15);
+    const int sh_even = cshift, sh_odd = (mis + cshift) & 15;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < NP; ++j) {
       const int slot = lane + 32 * j;
-      if (slot < 80) {  // nibble piece c of row r
-        const int r = slot / 5, c = slot - 5 * r;
-        const int shift = (((r & 1) ? mis : 0) + cshift) & 15;  // 0 or 8
-        if (c < 4 || shift != 0) pmask |= 1u << j;
-        prow[j] = r;
-        src[j] = chunk0 + static_cast<long long>(r) * pitch + (c * 16 - shift);
-        dst[j] = static_cast<uint32_t>(r * kNibPitch + c * 16);
-      } else {  // scale piece c of row r: the aligned 16 bytes around (or after) the eight scale bytes
-        const int sl = slot - 80;
-        const int r = sl >> 1, c = sl & 1;
-        const int o = (r & 1) ? soff_odd : soff_even;
-        if (sl < 32 && (c == 0 || o > 8)) pmask |= 1u << j;
-        prow[j] = r & 15;
-        src[j] = sg.w + static_cast<long long>(row0 + (r & 15)) * pitch + sabs - o + c * 16;
-        dst[j] = static_cast<uint32_t>(kNibBytes + (r & 15) * kSclPitch + c * 16);
+      const int r = slot / S::kPiecesPerRow, c = slot - r * S::kPiecesPerRow;
+      off[j] = 0;
+      dst[j] = 0;
+      if (r < 16) {
+        if (c < 4 * W + 1) {  // nibble piece c of row r
+          const int shift = (r & 1) ? sh_odd : sh_even;
+          if (c < 4 * W || shift != 0) pmask |= 1u << j;
+          off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (c * 16 - shift) + 16);
+          dst[j] = static_cast<uint32_t>(S::NibRow(r) + c * 16);
+        } else {  // the aligned 16 bytes that hold (c2 = 0) or follow (c2 = 1) the first scale byte
+          const int c2 = c - (4 * W + 1);
+          const int o = (r & 1) ? so_odd : so_even;
+          if (c2 == 0 || o + 8 * W > 16) pmask |= 1u << j;
+          off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (sabs - o + c2 * 16 - warp_col_byte) + 16);
+          dst[j] = static_cast<uint32_t>(S::SclRow(r) + c2 * 16);
+        }
       }
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      w_rd[i] = static_cast<uint32_t>((4 * t + i) * kNibPitch + ((((i & 1) ? mis : 0) + cshift) & 15) + g * 8);
-      s_rd[i] = static_cast<uint32_t>(kNibBytes + (4 * t + i) * kSclPitch + ((i & 1) ? soff_odd : soff_even) + g);
-    }
+    const int rbase = S::NibRow(4 * t) + g * CB, sbase = S::SclRow(4 * t) + g;
+    rd_w[0] = static_cast<uint32_t>(rbase + sh_even);
+    rd_w[1] = static_cast<uint32_t>(rbase + sh_odd);
+    rd_s[0] = static_cast<uint32_t>(sbase + so_even);
+    rd_s[1] = static_cast<uint32_t>(sbase + so_odd);
   } else {
-    const long long col_byte = (MODE == kBf16) ? static_cast<long long>(colbase) * 2 : colbase;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      prow[i] = 4 * t + i;
-      src[i] = sg.w + static_cast<long long>(row0 + 4 * t + i) * pitch + col_byte;
+      off[i] = static_cast<uint32_t>(static_cast<long long>(4 * t + i) * pitch + g * CB + 16);
       dst[i] = static_cast<uint32_t>(i * (32 * CB) + lane * CB);
-      w_rd[i] = dst[i];
-      s_rd[i] = 0;
     }
     if (cvalid) pmask = 0xF;
-  }
-  // lanes past the tile's last column read zeros instead of the ring
-  const uint32_t zaddr = SmemAddr(s_zero);
-  const uint32_t vm = cvalid ? 0xFFFFFFFFu : 0u;
-  if (!cvalid) {
+    rd_w[0] = rd_w[1] = static_cast<uint32_t>(lane * CB);
+    rd_s[0] = rd_s[1] = 0;
+    if (!cvalid && warp_has_cols) {
+      // lanes past the tile's last column copy nothing: their share of the ring reads as zero
+      for (int d = 0; d < DEPTH; ++d)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      w_rd[i] = zaddr;
-      s_rd[i] = zaddr;
+        for (int i = 0; i < 4; ++i)
+          asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(ring + d * S::kBytes + dst[i]), "r"(0) : "memory");
     }
   }
+#pragma unroll
+  for (int j = 0; j < NP; ++j) {
+    Pin(off[j]);
+    Pin(dst[j]);
+  }
+  Pin(pmask);
+  Pin(rd_w[0]);
+  Pin(rd_w[1]);
+  Pin(rd_s[0]);
+  Pin(rd_s[1]);
 
-  // copies local step s into ring slot `slot_addr` and advances the source pointers
+  // copies local step s into the slot at `slot_addr`
   auto issue_step = [&](int s, uint32_t slot_addr) {
     if (s != careful_step) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (pmask & (1u << j)) CpAsync16(slot_addr + dst[j], src[j], 16);
-        src[j] += step_stride;
-      }
+      for (int j = 0; j < NP; ++j) CpAsync16If(pmask & (1u << j), slot_addr + dst[j], gbase, off[j]);
     } else {
       const int r0 = row0 + s * p.wk * 16;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < NP; ++j) {
         if (pmask & (1u << j)) {
-          const long long room = sg.total_bytes - (src[j] - sg.w);
-          const int bytes = (r0 + prow[j] >= tl.kend) ? 0 : room >= 16 ? 16 : room > 0 ? static_cast<int>(room) : 0;
-          CpAsync16(slot_addr + dst[j], bytes > 0 ? src[j] : sg.w, bytes);
+          int r;  // row of the step this piece belongs to
+          if constexpr (MODE == kNvfp4) {
+            r = (lane + 32 * j) / S::kPiecesPerRow;
+          } else {
+            r = 4 * t + j;
+          }
+          const uint8_t* src = gbase + off[j];
+          const long long room = sg.total_bytes - (src - sg.w);
+          const int bytes = (r0 + r >= tl.kend) ? 0 : room >= 16 ? 16 : room > 0 ? static_cast<int>(room) : 0;
+          CpAsync16(slot_addr + dst[j], bytes > 0 ? src : sg.w, bytes);
         }
-        src[j] += step_stride;
       }
     }
+    gbase += step_stride;
   };
 
   // weights do not depend on the predecessor kernel: get the first k-steps in flight, then wait
 #pragma unroll
   for (int d = 0; d < DEPTH - 1; ++d) {
-    if (d < nsteps) issue_step(d, ring + d * kSlotBytes);
+    if (d < nsteps) issue_step(d, ring + d * S::kBytes);
     CpAsyncCommit();
   }
   if (p.pdl_wait) GridDependencyWait();
@@ -765,55 +811,53 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const G
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
 
-  uint32_t x_rd = SmemAddr(xs) + static_cast<uint32_t>((g * p.xpitch + 4 * t + wk * 16) * 2);
-  const uint32_t x_step = static_cast<uint32_t>(p.wk) * 32u;
-  const bool has_row = g < p.M;
-  uint32_t rd_slot = ring;                                   // slot of step s
-  uint32_t wr_slot = ring + (DEPTH - 1) * kSlotBytes;        // slot of step s + DEPTH - 1
-  const uint32_t ring_end = ring + DEPTH * kSlotBytes;
+  // lanes whose x row does not exist read row 0; their accumulators are never stored
+  uint32_t x_rd = SmemAddr(xs) + static_cast<uint32_t>(((g < p.M ? g : 0) * p.xpitch + 4 * t + wk * 16) * 2);
+  uint32_t x_step = static_cast<uint32_t>(p.wk) * 32u;
+  Pin(x_step);
+  const uint32_t ring_end = ring + DEPTH * S::kBytes;
+  uint32_t rd_slot = ring;                               // slot of step s
+  uint32_t wr_slot = ring + (DEPTH - 1) * S::kBytes;     // slot of step s - 1, refilled with step s + DEPTH - 1
   for (int s = 0; s < nsteps; ++s) {
-    // the slot consumed one step ago is free again: refill it with step s + DEPTH - 1
     __syncwarp();
     if (s + DEPTH - 1 < nsteps) issue_step(s + DEPTH - 1, wr_slot);
     CpAsyncCommit();
     asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
     __syncwarp();
-    const uint32_t base = rd_slot & vm;
-    Raw<MODE> raw;
+    Raw<MODE, W> raw;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       if constexpr (MODE == kNvfp4) {
-        raw.r[i] = Lds64(base + w_rd[i]);
-        raw.s[i] = Lds8(base + s_rd[i]);
+        const uint32_t wa = rd_slot + rd_w[i & 1] + i * S::kNibPitch;
+        const uint32_t sa = rd_slot + rd_s[i & 1] + i * S::kSclPitch;
+#pragma unroll
+        for (int h = 0; h < W; ++h) {
+          raw.r[h][i] = Lds64(wa + h * 64);
+          raw.s[h][i] = Lds8(sa + h * 8);
+        }
       } else {
-        raw.r[i] = Lds128(base + w_rd[i]);
+        raw.r[i] = Lds128(rd_slot + rd_w[0] + i * (32 * CB));
       }
     }
-    uint32_t b0 = 0, b1 = 0;
-    if (has_row) {
-      const uint2 xv = Lds64(x_rd);
-      b0 = xv.x;
-      b1 = xv.y;
-    }
+    const uint2 xv = Lds64(x_rd);
     x_rd += x_step;
-    rd_slot += kSlotBytes;
+    wr_slot = rd_slot;
+    rd_slot += S::kBytes;
     if (rd_slot == ring_end) rd_slot = ring;
-    wr_slot += kSlotBytes;
-    if (wr_slot == ring_end) wr_slot = ring;
     if constexpr (MODE == kBf16) {
-      ComputeStep<MODE, false>(acc, raw, b0, b1);
+      ComputeStep<MODE, false, W>(acc, raw, xv.x, xv.y);
     } else {
       if (slow) {
-        ComputeStep<MODE, true>(acc, raw, b0, b1);
+        ComputeStep<MODE, true, W>(acc, raw, xv.x, xv.y);
       } else {
-        ComputeStep<MODE, false>(acc, raw, b0, b1);
+        ComputeStep<MODE, false, W>(acc, raw, xv.x, xv.y);
       }
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   if (p.trigger == 2) GridLaunchDependents();
   __syncthreads();
-  Epilogue<MODE>(p, tl, acc, smem, sh, warp_has_cols);
+  Epilogue<MODE, W>(p, tl, acc, smem, sh, warp_has_cols);
 }
 
 // ------------------------------------------------------------------------------ ring kernel
@@ -962,7 +1006,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) SkinnyGemmRingKernel(const Ge
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           if constexpr (MODE == kNvfp4) {
-            raw.r[i] = Lds64(wa + static_cast<uint32_t>(i) * TB);
+            raw.r[0][i] = Lds64(wa + static_cast<uint32_t>(i) * TB);
           } else {
             raw.r[i] = Lds128(wa + static_cast<uint32_t>(i) * TB);
           }
@@ -970,7 +1014,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) SkinnyGemmRingKernel(const Ge
         if constexpr (MODE == kNvfp4) {
           const uint32_t sa = slot + static_cast<uint32_t>(step_in_stage * 16) * SRB + s_off;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) raw.s[i] = Lds8(sa + static_cast<uint32_t>(i) * SRB);
+          for (int i = 0; i < 4; ++i) raw.s[0][i] = Lds8(sa + static_cast<uint32_t>(i) * SRB);
         }
         if constexpr (MODE == kBf16) {
           ComputeStep<MODE, false>(acc, raw, b0, b1);
@@ -1009,13 +1053,25 @@ cudaError_t ConfigureKernel(K kernel) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn);
 }
 
-template <int MODE>
+template <int MODE, int W>
 cudaError_t ConfigureDirect() {
-  cudaError_t err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 3>);
-  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 4>);
-  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 6>);
-  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 8>);
+  cudaError_t err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 3, W>);
+  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 4, W>);
+  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 6, W>);
+  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 8, W>);
   return err;
+}
+
+// the direct kernel is compiled for ring depths 3, 4, 6 and 8
+template <int MODE, int W>
+cudaError_t LaunchDirect(const cudaLaunchConfig_t* cfg, int depth, const GemmParams& p) {
+  switch (depth) {
+    case 3: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 3, W>, p);
+    case 4: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 4, W>, p);
+    case 6: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 6, W>, p);
+    case 8: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 8, W>, p);
+    default: return cudaErrorInvalidValue;
+  }
 }
 
 template <int MODE>
@@ -1043,13 +1099,10 @@ cudaError_t LaunchMode(const GemmParams& p, const Plan& plan, size_t smem, cudaS
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
   if (plan.direct) {
-    switch (plan.stages) {
-      case 3: return cudaLaunchKernelEx(&cfg, SkinnyGemmDirectKernel<MODE, 3>, p);
-      case 4: return cudaLaunchKernelEx(&cfg, SkinnyGemmDirectKernel<MODE, 4>, p);
-      case 6: return cudaLaunchKernelEx(&cfg, SkinnyGemmDirectKernel<MODE, 6>, p);
-      case 8: return cudaLaunchKernelEx(&cfg, SkinnyGemmDirectKernel<MODE, 8>, p);
-      default: return cudaErrorInvalidValue;
+    if constexpr (MODE == kNvfp4) {
+      if (plan.wide == 2) return LaunchDirect<MODE, 2>(&cfg, plan.stages, p);
     }
+    return LaunchDirect<MODE, 1>(&cfg, plan.stages, p);
   }
   return cudaLaunchKernelEx(&cfg, SkinnyGemmRingKernel<MODE>, p);
 }
@@ -1077,9 +1130,13 @@ int QueryMaxActiveClusters(int mode, int direct, int threads, size_t smem, int c
   if (it != cache.end()) return it->second;
   const void* fn = nullptr;
   switch (mode) {
-    case kBf16: fn = direct ? (const void*)SkinnyGemmDirectKernel<kBf16, 4> : (const void*)SkinnyGemmRingKernel<kBf16>; break;
-    case kFp8: fn = direct ? (const void*)SkinnyGemmDirectKernel<kFp8, 4> : (const void*)SkinnyGemmRingKernel<kFp8>; break;
-    default: fn = direct ? (const void*)SkinnyGemmDirectKernel<kNvfp4, 4> : (const void*)SkinnyGemmRingKernel<kNvfp4>; break;
+    case kBf16: fn = direct ? (const void*)SkinnyGemmDirectKernel<kBf16, 4, 1> : (const void*)SkinnyGemmRingKernel<kBf16>; break;
+    case kFp8: fn = direct ? (const void*)SkinnyGemmDirectKernel<kFp8, 4, 1> : (const void*)SkinnyGemmRingKernel<kFp8>; break;
+    default:
+      fn = direct == 2   ? (const void*)SkinnyGemmDirectKernel<kNvfp4, 4, 2>
+           : direct == 1 ? (const void*)SkinnyGemmDirectKernel<kNvfp4, 4, 1>
+                         : (const void*)SkinnyGemmRingKernel<kNvfp4>;
+      break;
   }
   int result = 0;
   if (g_max_dynamic_smem > 0 && smem_key > static_cast<size_t>(g_max_dynamic_smem)) {
@@ -1115,9 +1172,10 @@ cudaError_t ConfigureSkinnyGemmKernels() {
   static std::once_flag once;
   static cudaError_t status = cudaSuccess;
   std::call_once(once, [] {
-    status = ConfigureDirect<kBf16>();
-    if (status == cudaSuccess) status = ConfigureDirect<kFp8>();
-    if (status == cudaSuccess) status = ConfigureDirect<kNvfp4>();
+    status = ConfigureDirect<kBf16, 1>();
+    if (status == cudaSuccess) status = ConfigureDirect<kFp8, 1>();
+    if (status == cudaSuccess) status = ConfigureDirect<kNvfp4, 1>();
+    if (status == cudaSuccess) status = ConfigureDirect<kNvfp4, 2>();
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRingKernel<kBf16>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRingKernel<kFp8>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRingKernel<kNvfp4>);
@@ -1126,7 +1184,7 @@ cudaError_t ConfigureSkinnyGemmKernels() {
 }
 
 cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStream_t stream) {
-  const ModeGeom geom = GeomOf(mode);
+  const ModeGeom geom = GeomOf(mode, plan.direct ? plan.wide : 1);
   p.wn = plan.wn;
   p.wk = plan.wk;
   p.ks = plan.ks;
@@ -1139,7 +1197,7 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
   p.stage_bytes = (R * (p.tile_row_bytes + p.scale_row_bytes) + 127) & ~127;
   const int TNc = plan.wn * geom.cols_per_warp;
   const int red_bytes = (plan.wk + (plan.cluster > 1 ? 1 : 0)) * p.M * TNc * 4;
-  const int direct_slot = mode == kNvfp4 ? 16 * 80 + 16 * 32 : 4 * 32 * geom.bytes_per_thread;
+  const int direct_slot = DirectSlotBytes(mode, plan.wide);
   const int ring = plan.direct ? plan.wn * plan.wk * plan.stages * direct_slot : plan.stages * p.stage_bytes;
   p.ring_bytes = (std::max(ring, red_bytes) + 127) & ~127;
   const int ksteps = (p.K + 15) / 16;

@@ -89,6 +89,20 @@ def test_every_plan_shape(cuda, mode, plan):
     run_case(rng, mode, 3, 2304, [[1280, 256], [512]], with_scale=True, plan=plan)
 
 
+@pytest.mark.parametrize("wide", [1, 2])
+@pytest.mark.parametrize("plan", [
+    "wn=1,wk=16,cluster=1", "wn=2,wk=4,cluster=2", "wn=5,wk=3,cluster=1,stages=3", "wn=1,wk=2,cluster=8,stages=8",
+    "wn=3,wk=4,cluster=1,stages=6,ctas=7"])
+def test_nvfp4_thread_widths_on_misaligned_rows(cuda, wide, plan):
+    """Both thread widths of the NVFP4 direct kernel, on weights whose packed row pitch is 8 mod 16
+    (odd rows start half a 16-byte piece off, as in the 151936-column LM head) and on one whose
+    pitch is 0 mod 16, with K not a multiple of 16 (zero-filled last k-step)."""
+    rng = np.random.default_rng(sum(map(ord, plan)) + wide)
+    spec = f"direct=1,wide={wide}," + plan
+    run_case(rng, 2, 3, 2312, [[640, 384], [896]], plan=spec)
+    run_case(rng, 2, 8, 1000, [[1280], [128, 128]], plan=spec)
+
+
 @pytest.mark.parametrize("mode", [0, 1, 2])
 def test_row_independence_and_determinism(cuda, mode):
     """Row r of an M-row call is bit-identical to the one-row call on that row, and a repeated

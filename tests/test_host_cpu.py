@@ -101,7 +101,7 @@ def test_plan_invariants(dtype, k, n, align):
             granules = -(-width // p["gran"])
             assert 1 <= tiles <= granules
             widest = -(-granules // tiles) * p["gran"]
-            assert widest <= p["wn"] * cpw, "a tile must fit the CTA's columns"
+            assert widest <= p["wn"] * cpw * p["wide"], "a tile must fit the CTA's columns"
         if sms == 148 and sum(n) * k > 2 ** 24:
             assert p["ctas"] >= 0.85 * 148, "a large shape must cover (nearly) every SM"
 
