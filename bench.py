@@ -35,6 +35,9 @@ UNIT = "TB/s"
 HEAD = "C5_nvfp4_lmhead_5120x151936"
 
 
+NCU_DRAM_BYTES_PER_WEIGHT_BYTE = 1.0115  # (438.78 MB read + 3.83 MB written) / 437.58 MB of packed weights
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -314,6 +317,10 @@ def run_ours(args):
     shard_bytes = k * n_local * 9 // 16
     total_bytes = wl.weight_bytes
 
+    verified = None
+    if world > 1:
+        verified = verify_sharded(torch, dist, head, x, shard, n_local, c0, world)
+
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -350,13 +357,9 @@ def run_ours(args):
             dist.destroy_process_group()
         return
     peak, peak_kind = peaks()
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(tpath):
-        with open(tpath) as f:
-            t = json.load(f).get("SkinnyGemmKernel_nvfp4_lmhead")
-            if t:
-                traffic = t["dram_bytes_per_weight_byte"] * shard_bytes
+    # DRAM bytes per launch from the ncu capture of this kernel on this workload (read + write sectors
+    # over the packed weight bytes; see profiles/skinny_gemm_nvfp4_lmhead_ncu_full.md), scaled to the shard
+    traffic = round(NCU_DRAM_BYTES_PER_WEIGHT_BYTE * shard_bytes)
     line = {
         "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(us_step / 1000.0, 6), "higher_is_better": True,
@@ -377,6 +380,8 @@ def run_ours(args):
         "gpu_launches": args.steps * (1 if world == 1 else 2),
         "clocks": clocks,
     }
+    if verified is not None:
+        line["verified"] = verified
     if world == 1 and not args.skip_cpu:
         line["cpu_baseline"] = cpu_baseline(m, k, n_total, reps=40)
     if world == 1 and not args.headline_only:
@@ -396,6 +401,29 @@ def run_ours(args):
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def verify_sharded(torch, dist, head, x, shard, n_local, c0, world):
+    """Untimed: the sharded step against the fold of every rank's unfused SkinnyGemm + ArgmaxRows
+    over its own columns (same Better order: larger value, then lower global index)."""
+    from qwen38_flash_ops_b200 import ArgmaxRows, SkinnyGemm
+
+    m = x.shape[0]
+    idx, val = head.step(x)
+    logits = SkinnyGemm([1], [n_local])(x, shard)[0]
+    lidx, lval = ArgmaxRows()(logits)
+    cand = torch.stack([lval.double(), (lidx + c0).double()], dim=1).contiguous()  # [m, 2]
+    gathered = torch.empty((world, m, 2), dtype=torch.float64, device=x.device)
+    dist.all_gather_into_tensor(gathered, cand)
+    torch.cuda.synchronize()
+    g = gathered.cpu().numpy()
+    ok = True
+    for r in range(m):
+        best = max(range(world), key=lambda w: (g[w, r, 0], -g[w, r, 1]))
+        ok = ok and int(g[best, r, 1]) == int(idx[r].item()) and float(g[best, r, 0]) == float(val[r].item())
+    if not ok:
+        raise SystemExit("sharded LM head disagrees with the fold of the per-rank unfused results")
+    return "sharded step == fold of per-rank SkinnyGemm + ArgmaxRows"
 
 
 _OUT_CACHE = {}
