@@ -186,11 +186,37 @@ def bench_small_configs(torch, quick=False):
                                        "GBps": round(wl.weight_bytes / med / 1e3, 1),
                                        "frac_of_measured_hbm": round(wl.weight_bytes / med / 1e3 / peak, 4),
                                        "frac_of_8TBps": round(wl.weight_bytes / med / 1e3 / 8000.0, 4)}
+        ref = _ref_util()
+        if ref is not None:
+            # the reference project's own kernels (generic launch configuration) under the same rotation
+            x = W.make_x(wl.m, wl.k, seed=7)
+            sc_dev = [None] * len(wl.ns)
+            if scales is not None:
+                offs = [0]
+                for n in wl.ns:
+                    offs.append(offs[-1] + n)
+                full = torch.tensor(scales, dtype=torch.float32, device="cuda")
+                sc_dev = [full[offs[i]:offs[i + 1]].contiguous() for i in range(len(wl.ns))]
+            modes = [wl.mode] * len(wl.ns)
+            med, best = time_graph_rotation(
+                torch, lambda i: ref.ref_skinny_gemm(x, sets[i], modes, list(wl.ns), sc_dev, seg_outs, widths), copies)
+            res["reference_kernel_sm100a"] = {"rows": wl.m, "us": round(med, 3), "us_best": round(best, 3),
+                                              "GBps": round(wl.weight_bytes / med / 1e3, 1)}
         res["plan"] = SkinnyGemm(seg_outs, widths, w_scale=scales).describe(wl.k, *sets[0])
         out[name] = res
         del sets
         torch.cuda.empty_cache()
     return out
+
+
+def _ref_util():
+    """tests/_util when the reference project's kernels were compiled (oracle/_ref), else None."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    try:
+        import _util as U
+    except Exception:
+        return None
+    return U if U.ref_lib() is not None else None
 
 
 def cpu_baseline(m, k, sample_cols, seed=11, reps=1):
@@ -336,18 +362,18 @@ def run_ours(args):
     us_kernel = ms_k * 1000.0 / args.steps
 
     # end to end: host x -> device, fused head (+ all-gather + fold), index and value back to the host
-    x_host = x.cpu().pin_memory()
-    x_dev = torch.empty_like(x)
-    idx_host = torch.empty(m, dtype=torch.int64).pin_memory()
-    val_host = torch.empty(m, dtype=torch.float32).pin_memory()
+    from qwen38_flash_ops_b200.lmhead_shard import HostLmHead
+
+    host_head = HostLmHead(head, m, k)
+    host_head.x_host.copy_(x.cpu())
 
     def e2e_step():
-        x_dev.copy_(x_host, non_blocking=True)
-        idx, val = head.step(x_dev)
-        idx_host.copy_(idx, non_blocking=True)
-        val_host.copy_(val, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        host_head()  # pinned x -> device, fused head (+ all-gather + fold), idx / val -> pinned host, synchronise
 
+    ih, vh = host_head()
+    ref_idx, ref_val = head.step(x)
+    if not (torch.equal(ih, ref_idx.cpu()) and torch.equal(vh, ref_val.cpu())):
+        raise SystemExit("host-buffer LM head disagrees with the device-resident step")
     ms_e = time_region(torch, e2e_step, args.steps, args.warmup, dist)
     us_e2e = ms_e * 1000.0 / args.steps
 
@@ -397,6 +423,10 @@ def run_ours(args):
                                "frac_of_measured_hbm": round(shard_bytes / usm / 1e3 / peak, 4),
                                "frac_of_8TBps": round(shard_bytes / usm / 1e3 / 8000.0, 4)}
         line["all_configs"][HEAD] = per_m
+        try:
+            line["all_configs"][HEAD]["reference_kernel_sm100a"] = time_reference_gpu_kernels(m)
+        except Exception as exc:
+            line["all_configs"][HEAD]["reference_kernel_sm100a"] = {"unavailable": str(exc)[:200]}
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

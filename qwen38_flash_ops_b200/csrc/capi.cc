@@ -73,6 +73,7 @@ struct qfg_skinny_gemm {
   int pdl_wait = 0;
   int force_slow = 0;
   int debug = 0;
+  unsigned long long phase_times = 0;  // device address given through set_option("phase_times", ...)
   std::string plan_spec;
   // plans already computed for this node, keyed by the shape of the call
   mutable std::mutex plan_mu;
@@ -80,7 +81,7 @@ struct qfg_skinny_gemm {
   qfg_skinny_gemm() = default;
   qfg_skinny_gemm(const qfg_skinny_gemm& o)
       : seg_outs(o.seg_outs), widths(o.widths), trigger(o.trigger), d_w_scale(o.d_w_scale), w_scale_len(o.w_scale_len),
-        pdl_wait(o.pdl_wait), force_slow(o.force_slow), debug(o.debug), plan_spec(o.plan_spec) {}
+        pdl_wait(o.pdl_wait), force_slow(o.force_slow), debug(o.debug), phase_times(o.phase_times), plan_spec(o.plan_spec) {}
 };
 
 struct qfg_dequant {
@@ -125,6 +126,7 @@ Prepared Prepare(const qfg_skinny_gemm& op, const void* x, int64_t m, int64_t k,
   p.pdl_wait = op.pdl_wait;
   p.force_slow = op.force_slow;
   p.debug = op.debug;
+  p.phase_times = reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(op.phase_times));
   int o = 0;
   size_t scale_off = 0;
   int row_align = 16;
@@ -290,6 +292,7 @@ int SetGemmOption(qfg_skinny_gemm* op, const char* key, const char* value) {
   if (k == "pdl_wait") op->pdl_wait = std::atoi(value);
   else if (k == "force_slow") op->force_slow = std::atoi(value);
   else if (k == "debug") op->debug = std::atoi(value);
+  else if (k == "phase_times") op->phase_times = std::strtoull(value, nullptr, 10);
   else if (k == "plan") op->plan_spec = value;
   else if (k == "trigger") op->trigger = std::atoi(value);
   else return Fail(QFG_INVALID_ARGUMENT, "set_option: unknown key " + k);

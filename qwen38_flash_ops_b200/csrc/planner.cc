@@ -234,7 +234,8 @@ Plan ChoosePlan(const PlanInput& in) {
           double score = lane_eff * balance * (warps_per_sm / 16.0) * (0.5 + 0.5 * kfactor) * rowfactor;
           // wider threads fetch fewer partly used sectors and spend fewer instructions per weight
           if (wide == 2) score *= 0.9;  // measured: the wide warp pays off only where tiles are narrow and K is split
-          score *= 1.0 - 0.015 * std::log2(static_cast<double>(c)) - 0.01 * (need - 1);
+          // a second wave pays the per-CTA fixed costs (x staging, pipeline fill, epilogue) again
+          score *= (1.0 - 0.015 * std::log2(static_cast<double>(c))) * std::pow(0.85, need - 1);
           if (score > best_score) {
             best_score = score;
             best = p;

@@ -84,7 +84,8 @@ struct GemmParams {
   int trigger = 0;
   int pdl_wait = 0;
   int force_slow = 0;  // testing: always take the BF16-MMA path of the quantised modes
-  int debug = 0;       // measurement aids of the direct kernel: 1 = no scale loads, 2 = no dequantisation
+  int debug = 0;       // unused by the kernels (kept for option compatibility)
+  unsigned long long* phase_times = nullptr;  // measurement aid: [CTA][8] globaltimer stamps of the direct kernel
   // plan
   int wn = 4, wk = 2, ks = 1, stages = 4, cluster = 1, gran = 16;
   int xpitch = 0;       // elements per x row in shared memory

@@ -643,6 +643,14 @@ __device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, fl
 //     groups a warp-wide shared-memory load touches into distinct banks.
 // A lane owns up to kPieces pieces; their sources are one 64-bit base, advanced by a k-step
 // stride per step, plus a 32-bit offset each.
+// Measurement aid: thread 0 of every CTA records the global timer at the phase boundaries.
+__device__ __forceinline__ void Stamp(const GemmParams& p, int slot) {
+  if (p.phase_times != nullptr && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.phase_times[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 8 + slot] = t;
+  }
+}
 template <typename T>
 __device__ __forceinline__ void Pin(T& v) {
   asm volatile("" : "+r"(v));  // keeps a loop invariant in its register instead of being recomputed
@@ -681,6 +689,7 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
   __shared__ SharedScratch sh;
 
   if (p.trigger == 1) GridLaunchDependents();
+  Stamp(p, 0);
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int wn = warp % p.wn, wk = warp / p.wn;
@@ -801,9 +810,11 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
     CpAsyncCommit();
   }
   if (p.pdl_wait) GridDependencyWait();
+  Stamp(p, 1);
 
   uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
   const bool slow = StageX<MODE>(p, tl, xs, sh);
+  Stamp(p, 2);
 
   float acc[NM][4];
 #pragma unroll
@@ -855,9 +866,12 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
+  Stamp(p, 3);
   if (p.trigger == 2) GridLaunchDependents();
   __syncthreads();
+  Stamp(p, 4);
   Epilogue<MODE, W>(p, tl, acc, smem, sh, warp_has_cols);
+  Stamp(p, 5);
 }
 
 // ------------------------------------------------------------------------------ ring kernel

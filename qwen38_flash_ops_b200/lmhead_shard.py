@@ -84,3 +84,58 @@ class ShardedLmHead:
             self._gathered = torch.empty(self.world * m, dtype=torch.int64, device=key.device)
         self._dist.all_gather_into_tensor(self._gathered, key, group=self.group)
         return lmhead_combine(self._gathered, self.world, m)
+
+
+class HostLmHead:
+    """The LM head for a caller whose activations and results live in host memory.
+
+    One call copies `x` (pinned host, BF16 [m, K]) to the device, runs the sharded step and copies
+    the winning index and value back.  On a single GPU the three stages are captured once into a
+    CUDA graph (the input copy and the fused kernel, which writes its results directly into the
+    pinned host buffers), so a call costs one graph launch and one stream synchronisation; with several ranks the stages are issued eagerly around the all-gather.
+    """
+
+    def __init__(self, head: ShardedLmHead, m: int, k: int):
+        torch = head._torch
+        dev = head.shard.device
+        self.head = head
+        self.x_host = torch.empty((m, k), dtype=torch.bfloat16).pin_memory()
+        self.x_dev = torch.empty((m, k), dtype=torch.bfloat16, device=dev)
+        self.idx_host = torch.empty(m, dtype=torch.int64).pin_memory()
+        self.val_host = torch.empty(m, dtype=torch.float32).pin_memory()
+        self._key = torch.empty(m, dtype=torch.int64, device=dev)
+        self.stream = torch.cuda.Stream(device=dev)
+        self.graph = None
+        if head.world == 1:
+            with torch.cuda.stream(self.stream):
+                self._enqueue()  # first call outside capture: one-time set-up of the kernels
+                self.stream.synchronize()
+                self.graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.graph, stream=self.stream):
+                    self._enqueue()
+
+    def _enqueue(self):
+        self.x_dev.copy_(self.x_host, non_blocking=True)
+        h = self.head
+        if h.world == 1:
+            # The kernel's last CTA stores the winners straight into the pinned host buffers (pinned
+            # memory is device-addressable), which saves two device-to-host copies per call.
+            h.head(self.x_dev, h.shard, h.n_local, col_offset=h.col_begin, out=(self.idx_host, self.val_host, self._key))
+            return
+        idx, val = h.step(self.x_dev)
+        self.idx_host.copy_(idx, non_blocking=True)
+        self.val_host.copy_(val, non_blocking=True)
+
+    def __call__(self, x_host=None):
+        """x_host: optional BF16 [m, K] host tensor to stage first (omit when the caller wrote
+        `self.x_host` in place).  Returns (idx_host, val_host), valid until the next call."""
+        torch = self.head._torch
+        if x_host is not None:
+            self.x_host.copy_(x_host)
+        with torch.cuda.stream(self.stream):
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self._enqueue()
+        self.stream.synchronize()
+        return self.idx_host, self.val_host

@@ -129,3 +129,22 @@ def test_lmhead_full_vocabulary(cuda, M):
         d = np.abs(bits(r).astype(np.int32) - bits(logits).astype(np.int32))
         assert np.mean(d <= 1) > 0.999
         assert _oracle_near_tie_ok(ridx.cpu().numpy(), sums, obits, oidx) == 0
+
+
+def test_host_buffer_head_matches_device_step(cuda):
+    """HostLmHead (pinned host x in, idx / val out, one captured graph) returns what the
+    device-resident step returns, call after call, for changing inputs."""
+    from qwen38_flash_ops_b200.lmhead_shard import HostLmHead, ShardedLmHead
+
+    rng = np.random.default_rng(77)
+    K, N, M = 1024, 1280, 3
+    arr, _ = U.make_weight(rng, 2, K, N, False)
+    w = U.dev_weight(arr, 2)
+    head = ShardedLmHead(w, N, 0)
+    host = HostLmHead(head, M, K)
+    for trial in range(3):
+        x = P.synth_x(rng, M, K)
+        xd = to_dev(x, "bf16")
+        idx, val = head.step(xd)
+        ih, vh = host(xd.cpu())
+        assert torch.equal(ih, idx.cpu()) and torch.equal(vh, val.cpu()), f"trial {trial}"
