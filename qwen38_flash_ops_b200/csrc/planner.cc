@@ -58,13 +58,14 @@ void FitRing(const PlanInput& in, int rows, Plan* p) {
   const ModeGeom g = GeomOf(in.mode);
   if (p->direct) {
     // warp-private rings: as deep as the CTA's share of shared memory allows, at most 8 k-steps
-    const int warps = p->wn * p->wk;
-    const int per_sm = std::max(1, (p->wide == 2 ? 16 : 20) / warps);
+    const int warps = p->warps();
+    const int per_sm = p->tc ? 1 : std::max(1, (p->wide == 2 ? 16 : 20) / warps);
     const size_t budget = static_cast<size_t>(220 * 1024) / per_sm;
     p->ks = 1;
     // the kernel is compiled for ring depths 8, 6, 4 and 3
     static const int kDepths[] = {8, 6, 4, 3};
     for (int d : kDepths) {
+      if (p->tc && d == 8) continue;  // the tcgen05 kernel is compiled for 6, 4 and 3
       p->stages = d;
       if (SmemBytes(*p, in.mode, rows, in.K) <= budget) break;
     }
@@ -82,6 +83,18 @@ void FitRing(const PlanInput& in, int rows, Plan* p) {
 
 size_t SmemBytes(const Plan& plan, int mode, int rows, int K) {
   const ModeGeom g = GeomOf(mode, plan.direct ? plan.wide : 1);
+  const int ksteps = (K + 15) / 16;
+  const int kslice = ((ksteps + plan.cluster - 1) / plan.cluster) * 16;
+  if (plan.tc) {
+    // rings of the tensor-memory warps and of the mma.sync warps, reused for the partial sums; x as the
+    // K-major MMA operand (256 bytes per k-step, one spare step that the 16-row instruction reads past the end)
+    const int tnc = PlanMaxCols(plan, mode);
+    const int red = (plan.wk + (plan.cluster > 1 ? 1 : 0)) * rows * tnc * 4;
+    const int ring_raw = (plan.wn * plan.wk + plan.wk) * plan.stages * DirectSlotBytes(mode, 1);
+    const int ring = (std::max(ring_raw, red) + 127) & ~127;
+    const size_t total = static_cast<size_t>(ring) + static_cast<size_t>(kslice / 16 + 1) * 256;
+    return std::max<size_t>(total, 120 * 1024);  // never two CTAs per SM: each allocates up to all of tensor memory
+  }
   const int tb = plan.wn * g.bytes_per_warp;
   const int srb = mode == kNvfp4 ? (plan.wn * 8 + 16 + 15) & ~15 : 0;
   const int stage = (plan.rows_per_stage() * (tb + srb) + 127) & ~127;
@@ -90,15 +103,12 @@ size_t SmemBytes(const Plan& plan, int mode, int rows, int K) {
   const int direct_slot = DirectSlotBytes(mode, plan.wide);
   const int ring_raw = plan.direct ? plan.wn * plan.wk * plan.stages * direct_slot : plan.stages * stage;
   const int ring = (std::max(ring_raw, red) + 127) & ~127;
-  const int ksteps = (K + 15) / 16;
-  const int kslice = ((ksteps + plan.cluster - 1) / plan.cluster) * 16;
   const int xpitch = ((kslice + 63) & ~63) + 16;
   return static_cast<size_t>(ring) + static_cast<size_t>(rows) * xpitch * 2;
 }
 
 void DistributeTiles(const PlanInput& in, int total_tiles, Plan* plan) {
-  const ModeGeom g = GeomOf(in.mode, plan->direct ? plan->wide : 1);
-  const int max_cols = plan->wn * g.cols_per_warp;
+  const int max_cols = PlanMaxCols(*plan, in.mode);
   long long sum_n = 0;
   int min_t[kMaxSeg], given = 0;
   for (int s = 0; s < in.nseg; ++s) {
@@ -272,6 +282,7 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
     else if (key == "gran") plan->gran = val;
     else if (key == "direct") plan->direct = val;
     else if (key == "wide") { plan->wide = val; wide_given = true; }
+    else if (key == "tc") plan->tc = val != 0 ? 1 : 0;
     else return false;
   }
   auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
@@ -279,11 +290,21 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
   if (plan->wide != 1 && plan->wide != 2) return false;
   if (plan->direct == 0 || in.mode != kNvfp4) plan->wide = 1;
   if (plan->direct != 0 && !DirectEligible(in, plan->wide)) return false;
-  if (plan->direct != 0 && ring_given && plan->stages != 3 && plan->stages != 4 && plan->stages != 6 && plan->stages != 8) return false;
+  if (plan->tc != 0) {
+    // tensor-memory budget: 64 accumulator columns per 512-column group and 3 x 32 per warpgroup
+    if (in.mode != kNvfp4 || plan->direct == 0 || plan->wide != 1 || plan->wn % 4 != 0 ||
+        (plan->wn / 4) * (64 + plan->wk * 96) > 512 || plan->warps() > 20 || plan->wn * plan->wk / 4 > 8) {
+      return false;
+    }
+  }
+  if (plan->direct != 0 && ring_given && plan->stages != 3 && plan->stages != 4 && plan->stages != 6 &&
+      (plan->stages != 8 || plan->tc != 0)) {
+    return false;
+  }
   plan->direct = plan->direct != 0 ? 1 : 0;
   if (plan->direct == 0 && plan->gran < Granule(in.mode, in.row_align, false)) plan->gran = Granule(in.mode, in.row_align, false);
   if ((plan->direct == 0 && (!pow2(plan->wn) || !pow2(plan->wk) || plan->wn * plan->wk > 8)) || plan->wn < 1 || plan->wk < 1 ||
-      plan->wn * plan->wk > (plan->wide == 2 ? 16 : 20) || plan->wn > 10 || plan->ks < 1 || plan->ks > 8 ||
+      plan->warps() > (plan->wide == 2 ? 16 : 20) || plan->wn > 12 || plan->ks < 1 || plan->ks > 8 ||
       plan->stages < 2 || plan->stages > 8 || plan->cluster < 1 || plan->cluster > 8 || !pow2(plan->cluster)) {
     return false;
   }
@@ -300,13 +321,13 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
     const int per_sm = std::max(1, std::min(20 / (plan->wn * plan->wk), static_cast<int>((220 * 1024) / std::max<size_t>(smem, 1))));
     int cluster_slots;
     if (in.max_clusters != nullptr) {
-      cluster_slots = in.max_clusters(in.mode, plan->direct * plan->wide, plan->threads(), smem, plan->cluster);
+      cluster_slots = in.max_clusters(in.mode, plan->tc ? 3 : plan->direct * plan->wide, plan->threads(), smem, plan->cluster);
     } else {
       cluster_slots = plan->cluster == 1 ? per_sm * in.sm_count : static_cast<int>(per_sm * in.sm_count * 0.89) / plan->cluster;
     }
     total = std::max(1, waves * cluster_slots);
   }
-  const int min_tiles = MinTiles(in, plan->wn * g.cols_per_warp, plan->gran);
+  const int min_tiles = MinTiles(in, PlanMaxCols(*plan, in.mode), plan->gran);
   if (total == 0) {
     total = 0;
     for (int s = 0; s < in.nseg; ++s) total += plan->tiles[s];
@@ -320,8 +341,8 @@ std::string DescribePlan(const Plan& plan, const PlanInput& in) {
   int tiles = 0;
   for (int s = 0; s < in.nseg; ++s) tiles += plan.tiles[s];
   std::snprintf(buf, sizeof(buf),
-                "direct=%d,wide=%d,wn=%d,wk=%d,ks=%d,stages=%d,cluster=%d,gran=%d,tiles=%d,ctas=%d,threads=%d,smem=%zu",
-                plan.direct, plan.wide, plan.wn, plan.wk, plan.ks, plan.stages, plan.cluster, plan.gran, tiles,
+                "direct=%d,tc=%d,wide=%d,wn=%d,wk=%d,ks=%d,stages=%d,cluster=%d,gran=%d,tiles=%d,ctas=%d,threads=%d,smem=%zu",
+                plan.direct, plan.tc, plan.wide, plan.wn, plan.wk, plan.ks, plan.stages, plan.cluster, plan.gran, tiles,
                 tiles * plan.cluster, plan.threads(),
                 SmemBytes(plan, in.mode, in.max_rows, in.K));
   return buf;

@@ -53,9 +53,18 @@ struct Plan {
   int gran = 16;    // columns per granule of the balanced column partition
   int direct = 1;   // 1: warp-private cp.async rings, no CTA barrier in the K loop; 0: CTA-wide ring
   int wide = 1;     // NVFP4 direct kernel: 16-column groups per thread (1 or 2)
-  int threads() const { return 32 * wn * wk; }
+  int tc = 0;       // NVFP4: 1 = tcgen05 kernel (wn x wk warps feed tensor memory, one warp issues the MMAs, wk more
+                    // warps run mma.sync on up to 128 columns past wn x 128)
+  int warps() const { return tc ? wn * wk + 1 + wk : wn * wk; }
+  int threads() const { return 32 * warps(); }
   int rows_per_stage() const { return 16 * wk * ks; }
 };
+
+// Columns a CTA of this plan can hold.
+inline int PlanMaxCols(const Plan& plan, int mode) {
+  const ModeGeom g = GeomOf(mode, plan.direct ? plan.wide : 1);
+  return (plan.wn + (plan.tc ? 1 : 0)) * g.cols_per_warp;
+}
 
 struct Segment {
   const uint8_t* w = nullptr;

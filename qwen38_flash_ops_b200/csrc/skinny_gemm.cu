@@ -152,6 +152,10 @@ __device__ __forceinline__ uint32_t HalfPairToBf16Pair(uint32_t h) {
 template <bool BF16>
 __device__ __forceinline__ void Mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                     uint32_t b1) {
+#ifdef QFG_EXPERIMENT_NO_MMA
+  asm volatile("" ::"r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  return;
+#endif
   if constexpr (BF16) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -339,7 +343,19 @@ __device__ __forceinline__ uint32_t ScaleToHalf2(uint32_t w, float sc) {
 // row by a power of two and converts it to FP16.  WORDS = 4: 16-byte chunks (x 16-byte aligned,
 // K % 8 == 0); WORDS = 1: 4-byte pairs (K is even and slices start on multiples of 16, so a pair
 // never straddles a slice).  Returns true if the CTA must take the BF16 path.
-template <int MODE, int WORDS>
+// Position (in 16-bit elements) of element k of row m of the staged x.  TC = false: rows of `xpitch`
+// elements.  TC = true: the K-major no-swizzle operand layout of tcgen05.mma - per k-step 256 bytes,
+// two 8-row x 16-byte core matrices (k 0..7, then k 8..15), row m at 16 m bytes inside each.
+template <bool TC>
+__device__ __forceinline__ int XsIndex(int m, int k, int xpitch) {
+  if constexpr (TC) {
+    return (k >> 4) * 128 + ((k >> 3) & 1) * 64 + m * 8 + (k & 7);
+  } else {
+    return m * xpitch + k;
+  }
+}
+
+template <int MODE, int WORDS, bool TC = false>
 __device__ __forceinline__ bool StageXImpl(const GemmParams& p, const Tile& tl, uint16_t* xs, SharedScratch& sh) {
   constexpr int kElems = 2 * WORDS;
   constexpr int kBatch = 4;
@@ -380,7 +396,7 @@ __device__ __forceinline__ bool StageXImpl(const GemmParams& p, const Tile& tl, 
       const int m = live ? idx / chunks : 0;
       if (live) {
         const int kk = (idx - m * chunks) * kElems;
-        uint32_t* dst = xw + ((m * xpitch + kk) >> 1);
+        uint32_t* dst = xw + (XsIndex<TC>(m, kk, xpitch) >> 1);
         if constexpr (WORDS == 4) {
           *reinterpret_cast<uint4*>(dst) = make_uint4(v[j][0], v[j][1], v[j][2], v[j][3]);
         } else {
@@ -436,7 +452,7 @@ __device__ __forceinline__ bool StageXImpl(const GemmParams& p, const Tile& tl, 
       for (int idx = tid; idx < total; idx += nthreads) {
         const int m = idx / chunks, kk = (idx - m * chunks) * kElems;
         const float sc = sh.scale[m];
-        uint32_t* px = xw + ((m * xpitch + kk) >> 1);
+        uint32_t* px = xw + (XsIndex<TC>(m, kk, xpitch) >> 1);
         if constexpr (WORDS == 4) {
           uint4 q = *reinterpret_cast<uint4*>(px);
           q.x = ScaleToHalf2(q.x, sc);
@@ -455,7 +471,7 @@ __device__ __forceinline__ bool StageXImpl(const GemmParams& p, const Tile& tl, 
 }
 
 // Must be called by every thread of the CTA; sh.rmax / sh.rmin are initialised here.
-template <int MODE>
+template <int MODE, bool TC = false>
 __device__ __forceinline__ bool StageX(const GemmParams& p, const Tile& tl, uint16_t* xs, SharedScratch& sh) {
   if (threadIdx.x < kMaxRows) {
     sh.rmax[threadIdx.x] = 0;
@@ -464,43 +480,23 @@ __device__ __forceinline__ bool StageX(const GemmParams& p, const Tile& tl, uint
   }
   __syncthreads();
   const bool vec8 = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.K % 8 == 0);
-  if (vec8) return StageXImpl<MODE, 4>(p, tl, xs, sh);
-  return StageXImpl<MODE, 1>(p, tl, xs, sh);
+  if (vec8) return StageXImpl<MODE, 4, TC>(p, tl, xs, sh);
+  return StageXImpl<MODE, 1, TC>(p, tl, xs, sh);
 }
 
-// Reduction of the accumulators (wk warps, then the cluster), scaling, rounding, stores, and the
-// fused argmax.  `smem` is reused for the partial sums; every thread of the CTA must call this
-// after a __syncthreads() that ends all use of the shared memory by the main loop.
-template <int MODE, int W = 1>
-__device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, float (&acc)[Geom<MODE, W>::kMmas][4],
-                                         uint8_t* smem, SharedScratch& sh, bool warp_has_cols) {
-  using G = Geom<MODE, W>;
-  constexpr int NM = G::kMmas;
+// The part of the epilogue that starts from the partial sums in shared memory: `red` holds
+// [nparts][M][TNc] floats (part w = the sum over the k-steps of K-group w), the cluster partials
+// follow it.  Every thread of the CTA must call this after a __syncthreads() that follows the
+// last write to `red`.
+template <int MODE>
+__device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl, uint8_t* smem, SharedScratch& sh,
+                                             int nparts, int TNc) {
   const int tid = threadIdx.x, nthreads = blockDim.x;
-  const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int wn = warp % p.wn, wk = warp / p.wn;
+  const int warp = tid >> 5, lane = tid & 31;
   const int M = p.M, C = tl.C, n0 = tl.n0, n1 = tl.n1;
   const Segment& sg = p.seg[tl.seg];
-  const int cols_per_warp = 8 * G::kColsPerThread * W;
-  const int TNc = p.wn * cols_per_warp;
   float* red = reinterpret_cast<float*>(smem);
-  float* part = red + static_cast<size_t>(p.wk) * M * TNc;
-  if (warp_has_cols) {
-#pragma unroll
-    for (int j = 0; j < NM; ++j) {
-      // MMA j covers columns 2 (j % 8), +1 of the thread's (j / 8)-th column group (128 columns apart)
-      const int per_group = G::kMmas / W;
-      const int cl = wn * cols_per_warp + (j / per_group) * 8 * G::kColsPerThread + g * G::kColsPerThread + 2 * (j % per_group);
-      const int m0 = 2 * t, m1 = 2 * t + 1;
-      if (m0 < M) *reinterpret_cast<float2*>(&red[(wk * M + m0) * TNc + cl]) = make_float2(acc[j][0], acc[j][2]);
-      if (m1 < M) *reinterpret_cast<float2*>(&red[(wk * M + m1) * TNc + cl]) = make_float2(acc[j][1], acc[j][3]);
-    }
-  } else {
-    for (int m = 0; m < M; ++m)
-      for (int c = lane; c < cols_per_warp; c += 32) red[(wk * M + m) * TNc + wn * cols_per_warp + c] = 0.f;
-  }
-  __syncthreads();
-
+  float* part = red + static_cast<size_t>(nparts) * M * TNc;
   const int ncols = n1 - n0;  // valid columns of the tile (<= TNc)
   float best_v[kMaxRows];
   long long best_i[kMaxRows];
@@ -537,7 +533,7 @@ __device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, fl
       const float inv = sh.inv_scale[m];
       for (int c = tid; c < ncols; c += nthreads) {
         float sum = 0.f;
-        for (int w = 0; w < p.wk; ++w) sum += red[(w * M + m) * TNc + c];
+        for (int w = 0; w < nparts; ++w) sum += red[(w * M + m) * TNc + c];
         finalize(m, c, sum * inv);
       }
     }
@@ -546,7 +542,7 @@ __device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, fl
       const float inv = sh.inv_scale[m];
       for (int c = tid; c < TNc; c += nthreads) {
         float sum = 0.f;
-        for (int w = 0; w < p.wk; ++w) sum += red[(w * M + m) * TNc + c];
+        for (int w = 0; w < nparts; ++w) sum += red[(w * M + m) * TNc + c];
         part[m * TNc + c] = sum * inv;
       }
     }
@@ -622,6 +618,41 @@ __device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, fl
       if (tid == 0) *p.lm_count = 0u;
     }
   }
+}
+
+// Reduction of the accumulators (wk warps, then the cluster), scaling, rounding, stores, and the
+// fused argmax.  `smem` is reused for the partial sums; every thread of the CTA must call this
+// after a __syncthreads() that ends all use of the shared memory by the main loop.
+template <int MODE, int W = 1>
+__device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, float (&acc)[Geom<MODE, W>::kMmas][4],
+                                         uint8_t* smem, SharedScratch& sh, bool warp_has_cols) {
+  using G = Geom<MODE, W>;
+  constexpr int NM = G::kMmas;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int wn = warp % p.wn, wk = warp / p.wn;
+  const int M = p.M, C = tl.C, n0 = tl.n0, n1 = tl.n1;
+  const Segment& sg = p.seg[tl.seg];
+  const int cols_per_warp = 8 * G::kColsPerThread * W;
+  const int TNc = p.wn * cols_per_warp;
+  float* red = reinterpret_cast<float*>(smem);
+  float* part = red + static_cast<size_t>(p.wk) * M * TNc;
+  if (warp_has_cols) {
+#pragma unroll
+    for (int j = 0; j < NM; ++j) {
+      // MMA j covers columns 2 (j % 8), +1 of the thread's (j / 8)-th column group (128 columns apart)
+      const int per_group = G::kMmas / W;
+      const int cl = wn * cols_per_warp + (j / per_group) * 8 * G::kColsPerThread + g * G::kColsPerThread + 2 * (j % per_group);
+      const int m0 = 2 * t, m1 = 2 * t + 1;
+      if (m0 < M) *reinterpret_cast<float2*>(&red[(wk * M + m0) * TNc + cl]) = make_float2(acc[j][0], acc[j][2]);
+      if (m1 < M) *reinterpret_cast<float2*>(&red[(wk * M + m1) * TNc + cl]) = make_float2(acc[j][1], acc[j][3]);
+    }
+  } else {
+    for (int m = 0; m < M; ++m)
+      for (int c = lane; c < cols_per_warp; c += 32) red[(wk * M + m) * TNc + wn * cols_per_warp + c] = 0.f;
+  }
+  __syncthreads();
+  EpilogueTail<MODE>(p, tl, smem, sh, p.wk, TNc);
 }
 
 // ------------------------------------------------------------------------------ direct kernel
@@ -874,6 +905,441 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
   Stamp(p, 5);
 }
 
+// ------------------------------------------------------------------------------ tcgen05 kernel
+// NVFP4 only.  The warp rings, the dequantisation and the epilogue are those of the direct kernel;
+// the MMAs move from the legacy mma.sync pipe (measured: busy 62 % of all cycles and the first
+// limiter of the direct kernel) to tcgen05.mma with the accumulators in tensor memory:
+//   * warps come in groups of four side by side in N (a warpgroup, 512 columns); warp q of a group
+//     can only touch TMEM lanes [32 q, 32 q + 32), so the four warps together fill the 128 lanes of
+//     an A tile.  Per k-step a warp stores its eight 16-column x 16-row fragments with two
+//     tcgen05.st.16x256b.x4 - that shape has exactly the register layout of the mma.sync A
+//     fragment - into four A tiles (fragment j goes to tile j / 2, lanes 16 (j % 2) + ...).
+//   * x is staged as the K-major no-swizzle B operand (8 rows x 16 k per step; rows 8..15 of the
+//     N = 16 instruction alias the next step's bytes and land in accumulator columns nobody reads).
+//   * one extra warp issues, in increasing k order, four M128 N16 K16 MMAs per warpgroup k-step and
+//     commits them to the mbarrier that frees the A buffer (three buffers per warpgroup).  All K
+//     groups of a column group accumulate into the same TMEM tile, so the sum over K runs in
+//     k order whatever wk is.
+//   * tile columns past wn x 128 (at most 128 more) are handled by wk extra warps on the mma.sync
+//     path, so that a tile does not have to be a multiple of 512 columns.
+// Every wait on an mbarrier is bounded.
+constexpr int kTcBuffers = 3;
+constexpr int kTcSpin = 1 << 22;
+constexpr int kTcMaxGroups = 8;  // warpgroups per CTA (TMEM: groups x buffers x 32 + 64 per column group <= 512)
+
+__device__ __forceinline__ void MbarInit(uint32_t addr, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(addr), "r"(count) : "memory");
+}
+__device__ __forceinline__ void MbarArrive(uint32_t addr) {
+  asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(addr) : "memory");
+}
+// false if the phase did not complete within the spin limit (the caller carries on; results are then wrong
+// but nothing hangs)
+__device__ __forceinline__ bool MbarWait(uint32_t addr, uint32_t parity) {
+  uint32_t done = 0;
+  for (int spin = 0; spin < kTcSpin && !done; ++spin) {
+    asm volatile("{ .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done)
+                 : "r"(addr), "r"(parity)
+                 : "memory");
+  }
+  return done != 0;
+}
+__device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void TcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+struct TcShared {
+  unsigned long long full[kTcMaxGroups][kTcBuffers];   // 4 arrivals: the warps of the group stored their fragments
+  unsigned long long empty[kTcMaxGroups][kTcBuffers];  // 1 arrival: the MMAs that read the buffer completed
+  unsigned long long done;                             // 1 arrival: every MMA of the CTA completed
+  uint32_t tmem_base;
+  uint32_t fault;
+};
+
+// One warp's NVFP4 stream (128 columns): copy plan, ring and read offsets of the direct kernel, W = 1.
+template <int DEPTH>
+struct Nvfp4Stream {
+  using S = DirectSlot<kNvfp4, 1>;
+  static constexpr int NP = S::kPieces;
+  const uint8_t* gbase;
+  long long step_stride;
+  uint32_t off[NP], dst[NP], pmask, rd_w[2], rd_s[2], ring;
+  int nsteps, careful_step, row0, lane;
+
+  __device__ __forceinline__ void Setup(const GemmParams& p, const Tile& tl, const Segment& sg, int colwarp, int wk,
+                                        uint32_t ring_addr, bool active) {
+    lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const long long pitch = sg.pitch;
+    const int ksteps = (tl.kslice + 15) >> 4;
+    nsteps = (active && ksteps > wk) ? (ksteps - wk + p.wk - 1) / p.wk : 0;
+    careful_step = (((ksteps - 1) % p.wk) == wk) ? nsteps - 1 : -1;
+    row0 = tl.kbeg + wk * 16;
+    step_stride = static_cast<long long>(p.wk) * 16 * pitch;
+    ring = ring_addr;
+    const long long warp_col_byte = colwarp / 2;
+    gbase = sg.w + static_cast<long long>(row0) * pitch + warp_col_byte - 16;
+    const int mis = static_cast<int>(pitch & 8);
+    const int cshift = static_cast<int>(warp_col_byte & 8);
+    const long long sabs = static_cast<long long>(sg.n >> 1) + (colwarp >> 4);
+    const int so_even = static_cast<int>(sabs & 15), so_odd = static_cast<int>((sabs + mis) & 15);
+    const int sh_even = cshift, sh_odd = (mis + cshift) & 15;
+    pmask = 0;
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      const int slot = lane + 32 * j;
+      const int r = slot / S::kPiecesPerRow, c = slot - r * S::kPiecesPerRow;
+      off[j] = 0;
+      dst[j] = 0;
+      if (r < 16) {
+        if (c < 5) {
+          const int shift = (r & 1) ? sh_odd : sh_even;
+          if (c < 4 || shift != 0) pmask |= 1u << j;
+          off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (c * 16 - shift) + 16);
+          dst[j] = static_cast<uint32_t>(S::NibRow(r) + c * 16);
+        } else {
+          const int c2 = c - 5;
+          const int o = (r & 1) ? so_odd : so_even;
+          if (c2 == 0 || o + 8 > 16) pmask |= 1u << j;
+          off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (sabs - o + c2 * 16 - warp_col_byte) + 16);
+          dst[j] = static_cast<uint32_t>(S::SclRow(r) + c2 * 16);
+        }
+      }
+    }
+    const int rbase = S::NibRow(4 * t) + g * 8, sbase = S::SclRow(4 * t) + g;
+    rd_w[0] = static_cast<uint32_t>(rbase + sh_even);
+    rd_w[1] = static_cast<uint32_t>(rbase + sh_odd);
+    rd_s[0] = static_cast<uint32_t>(sbase + so_even);
+    rd_s[1] = static_cast<uint32_t>(sbase + so_odd);
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      Pin(off[j]);
+      Pin(dst[j]);
+    }
+    Pin(pmask);
+    Pin(rd_w[0]);
+    Pin(rd_w[1]);
+    Pin(rd_s[0]);
+    Pin(rd_s[1]);
+  }
+
+  __device__ __forceinline__ void Issue(const GemmParams& p, const Tile& tl, const Segment& sg, int s, uint32_t slot_addr) {
+    if (s != careful_step) {
+#pragma unroll
+      for (int j = 0; j < NP; ++j) CpAsync16If(pmask & (1u << j), slot_addr + dst[j], gbase, off[j]);
+    } else {
+      const int r0 = row0 + s * p.wk * 16;
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        if (pmask & (1u << j)) {
+          const int r = (lane + 32 * j) / S::kPiecesPerRow;
+          const uint8_t* src = gbase + off[j];
+          const long long room = sg.total_bytes - (src - sg.w);
+          const int bytes = (r0 + r >= tl.kend) ? 0 : room >= 16 ? 16 : room > 0 ? static_cast<int>(room) : 0;
+          CpAsync16(slot_addr + dst[j], bytes > 0 ? src : sg.w, bytes);
+        }
+      }
+    }
+    gbase += step_stride;
+  }
+
+  __device__ __forceinline__ void Prologue(const GemmParams& p, const Tile& tl, const Segment& sg) {
+#pragma unroll
+    for (int d = 0; d < DEPTH - 1; ++d) {
+      if (d < nsteps) Issue(p, tl, sg, d, ring + d * S::kBytes);
+      CpAsyncCommit();
+    }
+  }
+
+  // consume(raw, s) for every local step s, DEPTH - 1 steps behind the copies
+  template <class F>
+  __device__ __forceinline__ void Run(const GemmParams& p, const Tile& tl, const Segment& sg, F&& consume) {
+    const uint32_t ring_end = ring + DEPTH * S::kBytes;
+    uint32_t rd_slot = ring, wr_slot = ring + (DEPTH - 1) * S::kBytes;
+    for (int s = 0; s < nsteps; ++s) {
+      __syncwarp();
+      if (s + DEPTH - 1 < nsteps) Issue(p, tl, sg, s + DEPTH - 1, wr_slot);
+      CpAsyncCommit();
+      asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
+      __syncwarp();
+      Raw<kNvfp4, 1> raw;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        raw.r[0][i] = Lds64(rd_slot + rd_w[i & 1] + i * S::kNibPitch);
+        raw.s[0][i] = Lds8(rd_slot + rd_s[i & 1] + i * S::kSclPitch);
+      }
+      wr_slot = rd_slot;
+      rd_slot += S::kBytes;
+      if (rd_slot == ring_end) rd_slot = ring;
+      consume(raw, s);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  }
+};
+
+// The A operand registers of the eight 16-column MMAs of one k-step (fr[j] = {a0, a1, a2, a3} of MMA j as
+// ComputeStep would pass them to mma.sync).
+template <bool SLOW>
+__device__ __forceinline__ void Nvfp4Fragments(const Raw<kNvfp4, 1>& w, uint32_t (&fr)[8][4]) {
+  const uint32_t s_ab = CvtE4m3x2(Prmt(w.s[0][0], w.s[0][1], 0x0040u));
+  const uint32_t s_cd = CvtE4m3x2(Prmt(w.s[0][2], w.s[0][3], 0x0040u));
+  const uint32_t a[2] = {w.r[0][0].x, w.r[0][0].y}, b[2] = {w.r[0][1].x, w.r[0][1].y};
+  const uint32_t c[2] = {w.r[0][2].x, w.r[0][2].y}, d[2] = {w.r[0][3].x, w.r[0][3].y};
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint32_t e_ab[4], o_ab[4], e_cd[4], o_cd[4];
+    CvtE2m1x8((a[i] & 0x0F0F0F0Fu) | ((b[i] << 4) & 0xF0F0F0F0u), e_ab);
+    CvtE2m1x8(((a[i] >> 4) & 0x0F0F0F0Fu) | (b[i] & 0xF0F0F0F0u), o_ab);
+    CvtE2m1x8((c[i] & 0x0F0F0F0Fu) | ((d[i] << 4) & 0xF0F0F0F0u), e_cd);
+    CvtE2m1x8(((c[i] >> 4) & 0x0F0F0F0Fu) | (d[i] & 0xF0F0F0F0u), o_cd);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t a0 = Hmul2(e_ab[q], s_ab), a1 = Hmul2(o_ab[q], s_ab);
+      uint32_t a2 = Hmul2(e_cd[q], s_cd), a3 = Hmul2(o_cd[q], s_cd);
+      if constexpr (SLOW) {
+        a0 = HalfPairToBf16Pair(a0);
+        a1 = HalfPairToBf16Pair(a1);
+        a2 = HalfPairToBf16Pair(a2);
+        a3 = HalfPairToBf16Pair(a3);
+      }
+      fr[4 * i + q][0] = a0;
+      fr[4 * i + q][1] = a1;
+      fr[4 * i + q][2] = a2;
+      fr[4 * i + q][3] = a3;
+    }
+  }
+}
+
+// Fragments `half`, `half` + 2, `half` + 4, `half` + 6 of a k-step into lanes [lane_base, lane_base + 16) of the
+// four A tiles of a buffer (32 TMEM columns from `taddr`).  A 16x256b store takes, per 8-column tile,
+// (row g: k 4t..4t+1), (row g: k 4t+2..4t+3), (row g + 8: ...), (row g + 8: ...) = a0, a2, a1, a3.
+__device__ __forceinline__ void TcStoreHalf(uint32_t taddr, const uint32_t (&fr)[8][4], int half) {
+  const uint32_t(&f0)[4] = fr[half], (&f1)[4] = fr[half + 2], (&f2)[4] = fr[half + 4], (&f3)[4] = fr[half + 6];
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(
+          taddr),
+      "r"(f0[0]), "r"(f0[2]), "r"(f0[1]), "r"(f0[3]), "r"(f1[0]), "r"(f1[2]), "r"(f1[1]), "r"(f1[3]), "r"(f2[0]), "r"(f2[2]),
+      "r"(f2[1]), "r"(f2[3]), "r"(f3[0]), "r"(f3[2]), "r"(f3[1]), "r"(f3[3])
+      : "memory");
+}
+
+template <int DEPTH>
+__global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const GemmParams p) {
+  using S = DirectSlot<kNvfp4, 1>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ SharedScratch sh;
+  __shared__ __align__(8) TcShared tc;
+
+  if (p.trigger == 1) GridLaunchDependents();
+  Stamp(p, 0);
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int nd = p.wn * p.wk;        // dequantising warps feeding tcgen05
+  const int ngroups = p.wn >> 2;     // column groups of 512
+  const bool is_tc = warp < nd, is_issuer = warp == nd, is_legacy = warp > nd;
+  const int wn = is_tc ? warp % p.wn : p.wn;                       // legacy warps own the column warp after the last
+  const int wk = is_tc ? warp / p.wn : (is_legacy ? warp - nd - 1 : 0);
+  const int q = wn & 3, ng = wn >> 2;                              // quadrant and column group of a TC warp
+  const int unit = wk * ngroups + ng;                              // warpgroup index
+  const Tile tl = LocateTile(p);
+  const Segment& sg = p.seg[tl.seg];
+  const int colwarp = tl.n0 + wn * 128;
+  const bool warp_has_cols = !is_issuer && colwarp < tl.n1;
+  const int ksteps = (tl.kslice + 15) >> 4;
+  const int TNc = (p.wn + 1) * 128;
+
+  if (tid == 0) {
+    for (int u = 0; u < p.wk * ngroups; ++u)
+      for (int b = 0; b < kTcBuffers; ++b) {
+        MbarInit(SmemAddr(&tc.full[u][b]), 4);
+        MbarInit(SmemAddr(&tc.empty[u][b]), 1);
+      }
+    MbarInit(SmemAddr(&tc.done), 1);
+    tc.fault = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  const int d_cols = ngroups * 64;
+  const int need_cols = d_cols + p.wk * ngroups * kTcBuffers * 32;
+  const int alloc_cols = need_cols <= 32 ? 32 : need_cols <= 64 ? 64 : need_cols <= 128 ? 128 : need_cols <= 256 ? 256 : 512;
+  if (is_issuer) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(&tc.tmem_base)), "r"(alloc_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+
+  Nvfp4Stream<DEPTH> st;
+  st.Setup(p, tl, sg, colwarp, wk, SmemAddr(smem) + static_cast<uint32_t>(is_legacy ? nd + wk : warp) * (DEPTH * S::kBytes),
+           warp_has_cols);
+  // a TC warp without columns still takes part in the barrier protocol of its group
+  const int proto_steps = (is_tc && ksteps > wk) ? (ksteps - wk + p.wk - 1) / p.wk : 0;
+  if (!is_issuer) st.Prologue(p, tl, sg);
+  if (p.pdl_wait) GridDependencyWait();
+  Stamp(p, 1);
+
+  uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
+  const bool slow = StageX<kNvfp4, true>(p, tl, xs, sh);
+  TcFenceBefore();
+  __syncthreads();
+  TcFenceAfter();
+  Stamp(p, 2);
+  const uint32_t tmem = tc.tmem_base;
+
+  float acc[8][4];  // legacy warps only
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+
+  if (is_tc) {
+    const uint32_t a_base = tmem + static_cast<uint32_t>(d_cols + unit * kTcBuffers * 32) + (static_cast<uint32_t>(32 * q) << 16);
+    const uint32_t full0 = SmemAddr(&tc.full[unit][0]), empty0 = SmemAddr(&tc.empty[unit][0]);
+    int b = 0, round = 0;  // buffer of step s and how many times the buffers were cycled
+    auto publish = [&](const Raw<kNvfp4, 1>* raw) {
+      uint32_t fr[8][4];
+      if (raw != nullptr) {
+        if (slow) {
+          Nvfp4Fragments<true>(*raw, fr);
+        } else {
+          Nvfp4Fragments<false>(*raw, fr);
+        }
+      }
+      if (round > 0 && !MbarWait(empty0 + b * 8, static_cast<uint32_t>((round - 1) & 1))) tc.fault = 1;
+      if (raw != nullptr) {
+        TcFenceAfter();
+        const uint32_t ta = a_base + static_cast<uint32_t>(b * 32);
+        TcStoreHalf(ta, fr, 0);
+        TcStoreHalf(ta + (16u << 16), fr, 1);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        TcFenceBefore();
+      }
+      __syncwarp();
+      if (lane == 0) MbarArrive(full0 + b * 8);
+      if (++b == kTcBuffers) {
+        b = 0;
+        ++round;
+      }
+    };
+    if (warp_has_cols) {
+      st.Run(p, tl, sg, [&](const Raw<kNvfp4, 1>& raw, int) { publish(&raw); });
+    } else {
+      for (int s = 0; s < proto_steps; ++s) publish(nullptr);
+    }
+  } else if (is_issuer) {
+    if (lane == 0) {
+      const uint32_t idesc = 0x10u | (2u << 17) | (8u << 24) | (slow ? ((1u << 7) | (1u << 10)) : 0u);
+      const uint32_t xa = SmemAddr(xs);
+      const int max_steps = (ksteps + p.wk - 1) / p.wk;
+      int b = 0, round = 0;
+      for (int s = 0; s < max_steps; ++s) {
+        for (int wkI = 0; wkI < p.wk; ++wkI) {
+          const int kk = wkI + s * p.wk;
+          if (kk >= ksteps) break;
+          // x tile of k-step kk: 256 bytes; K chunks 128 bytes apart; rows 8..15 alias the next 256 bytes
+          const unsigned long long desc = static_cast<unsigned long long>(((xa + static_cast<uint32_t>(kk) * 256u) >> 4) & 0x3FFF) |
+                                          (static_cast<unsigned long long>(128 >> 4) << 16) |
+                                          (static_cast<unsigned long long>(256 >> 4) << 32) | (1ull << 46);
+          for (int gi = 0; gi < ngroups; ++gi) {
+            const int u = wkI * ngroups + gi;
+            if (!MbarWait(SmemAddr(&tc.full[u][b]), static_cast<uint32_t>(round & 1))) tc.fault = 1;
+            TcFenceAfter();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t d_t = tmem + static_cast<uint32_t>(gi * 64 + i * 16);
+              const uint32_t a_t = tmem + static_cast<uint32_t>(d_cols + (u * kTcBuffers + b) * 32 + i * 8);
+              asm volatile(
+                  "{ .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                  " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}" ::"r"(d_t),
+                  "r"(a_t), "l"(desc), "r"(idesc), "r"(kk > 0 ? 1 : 0), "r"(0)
+                  : "memory");
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                             SmemAddr(&tc.empty[u][b]))
+                         : "memory");
+          }
+        }
+        if (++b == kTcBuffers) {
+          b = 0;
+          ++round;
+        }
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(SmemAddr(&tc.done))
+                   : "memory");
+    }
+    __syncwarp();
+  } else {
+    // mma.sync path for the tile's columns past the warpgroups
+    const int x_row = g < p.M ? g : 0;
+    uint32_t x_rd = SmemAddr(xs) + static_cast<uint32_t>(wk * 256 + (t >> 1) * 128 + x_row * 16 + (t & 1) * 8);
+    const uint32_t x_step = static_cast<uint32_t>(p.wk) * 256u;
+    st.Run(p, tl, sg, [&](const Raw<kNvfp4, 1>& raw, int) {
+      const uint2 xv = Lds64(x_rd);
+      x_rd += x_step;
+      if (slow) {
+        ComputeStep<kNvfp4, true, 1>(acc, raw, xv.x, xv.y);
+      } else {
+        ComputeStep<kNvfp4, false, 1>(acc, raw, xv.x, xv.y);
+      }
+    });
+  }
+  Stamp(p, 3);
+  if (p.trigger == 2) GridLaunchDependents();
+  // all MMAs done before anybody reads the accumulators or reuses the ring as `red`
+  if (!MbarWait(SmemAddr(&tc.done), 0)) tc.fault = 1;
+  TcFenceAfter();
+  __syncthreads();
+  Stamp(p, 4);
+
+  float* red = reinterpret_cast<float*>(smem);
+  const int M = p.M;
+  if (is_tc) {
+    if (wk == 0) {
+      // accumulators of this warp's 128 columns: TMEM lane 32 q + L of the group's four tiles, column n = x row
+      uint32_t d[4][8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t ta = tmem + static_cast<uint32_t>(ng * 64 + i * 16) + (static_cast<uint32_t>(32 * q) << 16);
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(d[i][0]), "=r"(d[i][1]), "=r"(d[i][2]), "=r"(d[i][3]), "=r"(d[i][4]), "=r"(d[i][5]), "=r"(d[i][6]),
+                       "=r"(d[i][7])
+                     : "r"(ta));
+      }
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      const int half = lane >> 4, l = lane & 15;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = 2 * i + half;  // fragment = MMA index of the direct kernel: columns 16 g' + 2 j (+ 1)
+        const int c = wn * 128 + (l < 8 ? 16 * l + 2 * j : 16 * (l - 8) + 2 * j + 1);
+#pragma unroll
+        for (int m = 0; m < kMaxRows; ++m)
+          if (m < M) red[m * TNc + c] = __uint_as_float(d[i][m]);
+      }
+    } else {
+      for (int m = 0; m < M; ++m)
+        for (int c = lane; c < 128; c += 32) red[(wk * M + m) * TNc + wn * 128 + c] = 0.f;
+    }
+  } else if (is_legacy) {
+    if (warp_has_cols) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int cl = wn * 128 + g * 16 + 2 * j;
+        const int m0 = 2 * t, m1 = 2 * t + 1;
+        if (m0 < M) *reinterpret_cast<float2*>(&red[(wk * M + m0) * TNc + cl]) = make_float2(acc[j][0], acc[j][2]);
+        if (m1 < M) *reinterpret_cast<float2*>(&red[(wk * M + m1) * TNc + cl]) = make_float2(acc[j][1], acc[j][3]);
+      }
+    } else {
+      for (int m = 0; m < M; ++m)
+        for (int c = lane; c < 128; c += 32) red[(wk * M + m) * TNc + wn * 128 + c] = 0.f;
+    }
+  }
+  TcFenceBefore();
+  __syncthreads();
+  if (is_issuer) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(alloc_cols) : "memory");
+  }
+  EpilogueTail<kNvfp4>(p, tl, smem, sh, p.wk, TNc);
+  Stamp(p, 5);
+}
+
 // ------------------------------------------------------------------------------ ring kernel
 template <int MODE>
 __global__ void __launch_bounds__(kRingThreads, 2) SkinnyGemmRingKernel(const GemmParams p) {
@@ -1114,6 +1580,14 @@ cudaError_t LaunchMode(const GemmParams& p, const Plan& plan, size_t smem, cudaS
   cfg.numAttrs = n_attr;
   if (plan.direct) {
     if constexpr (MODE == kNvfp4) {
+      if (plan.tc) {
+        switch (plan.stages) {
+          case 3: return cudaLaunchKernelEx(&cfg, SkinnyGemmTcKernel<3>, p);
+          case 4: return cudaLaunchKernelEx(&cfg, SkinnyGemmTcKernel<4>, p);
+          case 6: return cudaLaunchKernelEx(&cfg, SkinnyGemmTcKernel<6>, p);
+          default: return cudaErrorInvalidValue;
+        }
+      }
       if (plan.wide == 2) return LaunchDirect<MODE, 2>(&cfg, plan.stages, p);
     }
     return LaunchDirect<MODE, 1>(&cfg, plan.stages, p);
@@ -1147,7 +1621,8 @@ int QueryMaxActiveClusters(int mode, int direct, int threads, size_t smem, int c
     case kBf16: fn = direct ? (const void*)SkinnyGemmDirectKernel<kBf16, 4, 1> : (const void*)SkinnyGemmRingKernel<kBf16>; break;
     case kFp8: fn = direct ? (const void*)SkinnyGemmDirectKernel<kFp8, 4, 1> : (const void*)SkinnyGemmRingKernel<kFp8>; break;
     default:
-      fn = direct == 2   ? (const void*)SkinnyGemmDirectKernel<kNvfp4, 4, 2>
+      fn = direct == 3   ? (const void*)SkinnyGemmTcKernel<4>
+           : direct == 2 ? (const void*)SkinnyGemmDirectKernel<kNvfp4, 4, 2>
            : direct == 1 ? (const void*)SkinnyGemmDirectKernel<kNvfp4, 4, 1>
                          : (const void*)SkinnyGemmRingKernel<kNvfp4>;
       break;
@@ -1190,6 +1665,9 @@ cudaError_t ConfigureSkinnyGemmKernels() {
     if (status == cudaSuccess) status = ConfigureDirect<kFp8, 1>();
     if (status == cudaSuccess) status = ConfigureDirect<kNvfp4, 1>();
     if (status == cudaSuccess) status = ConfigureDirect<kNvfp4, 2>();
+    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmTcKernel<3>);
+    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmTcKernel<4>);
+    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmTcKernel<6>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRingKernel<kBf16>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRingKernel<kFp8>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRingKernel<kNvfp4>);
@@ -1209,15 +1687,22 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
   p.scale_row_bytes = mode == kNvfp4 ? (plan.wn * 8 + 16 + 15) & ~15 : 0;
   const int R = plan.rows_per_stage();
   p.stage_bytes = (R * (p.tile_row_bytes + p.scale_row_bytes) + 127) & ~127;
-  const int TNc = plan.wn * geom.cols_per_warp;
+  const int TNc = PlanMaxCols(plan, mode);
   const int red_bytes = (plan.wk + (plan.cluster > 1 ? 1 : 0)) * p.M * TNc * 4;
   const int direct_slot = DirectSlotBytes(mode, plan.wide);
-  const int ring = plan.direct ? plan.wn * plan.wk * plan.stages * direct_slot : plan.stages * p.stage_bytes;
+  const int ring_warps = plan.tc ? plan.wn * plan.wk + plan.wk : plan.wn * plan.wk;
+  const int ring = plan.direct ? ring_warps * plan.stages * direct_slot : plan.stages * p.stage_bytes;
   p.ring_bytes = (std::max(ring, red_bytes) + 127) & ~127;
   const int ksteps = (p.K + 15) / 16;
   const int kslice_max = ((ksteps + plan.cluster - 1) / plan.cluster) * 16;
   p.xpitch = ((kslice_max + 63) & ~63) + 16;  // 32 bytes off a 128-byte multiple: rows land in distinct banks
-  const size_t smem = static_cast<size_t>(p.ring_bytes) + static_cast<size_t>(p.M) * p.xpitch * 2;
+  size_t smem = static_cast<size_t>(p.ring_bytes) + static_cast<size_t>(p.M) * p.xpitch * 2;
+  if (plan.tc) {
+    // x as the MMA operand: 256 bytes per k-step plus one spare step; at least 120 KB so that two CTAs,
+    // each allocating up to all of tensor memory, can never share an SM
+    smem = static_cast<size_t>(p.ring_bytes) + static_cast<size_t>(kslice_max / 16 + 1) * 256;
+    if (smem < 120 * 1024) smem = 120 * 1024;
+  }
   if (g_max_dynamic_smem > 0 && smem > static_cast<size_t>(g_max_dynamic_smem)) return cudaErrorInvalidConfiguration;
   int tiles = 0;
   for (int s = 0; s < p.nseg; ++s) {

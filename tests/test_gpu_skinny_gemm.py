@@ -319,3 +319,30 @@ def test_linearity_at_full_size(cuda):
     rows = O.decode_weights_exact(2, host[[1234, 4321]], N)
     assert np.array_equal(y[0], rows[0])      # one-hot x reads back the dequantised row exactly
     assert np.array_equal(y[1], -2.0 * rows[1])
+
+
+@pytest.mark.parametrize("plan", [
+    "wn=4,wk=2,cluster=1", "wn=4,wk=3,cluster=2", "wn=8,wk=2,cluster=1,stages=3", "wn=4,wk=1,cluster=4,stages=6",
+    "wn=4,wk=3,cluster=1,ctas=5"])
+def test_nvfp4_tensor_memory_kernel(cuda, plan):
+    """The tcgen05 variant of the NVFP4 kernel (A fragments in tensor memory, one issuing warp, mma.sync
+    warps for the columns past the warpgroups): aligned and 8-mod-16 row pitches, K not a multiple
+    of 16, 1 to 8 rows, tiles that need the extra columns and tiles that leave warps empty."""
+    rng = np.random.default_rng(sum(map(ord, plan)))
+    spec = "direct=1,tc=1,wide=1," + plan
+    run_case(rng, 2, 3, 2312, [[640, 384], [896]], plan=spec)
+    run_case(rng, 2, 8, 1000, [[1280], [128, 128]], plan=spec)
+    run_case(rng, 2, 1, 2048, [[4096 + 128]], with_scale=True, plan=spec)
+
+
+def test_nvfp4_tensor_memory_kernel_matches_direct_kernel_on_wide_range(cuda):
+    """x with a dynamic range that forces the BF16 operand path: the tcgen05 kernel (BF16 kind) and the
+    mma.sync kernel see the same exact operands and must both satisfy the oracle."""
+    rng = np.random.default_rng(4242)
+    K, N = 1024, 1024
+    x = P.synth_x(rng, 4, K)
+    xf = O.bf16_to_f32(x)
+    xf[:, ::7] *= 2.0 ** 20
+    xf[:, 1::7] *= 2.0 ** -20
+    x = P.f32_to_bf16_bits(xf)
+    run_case(rng, 2, 4, K, [[N]], plan="direct=1,tc=1,wide=1,wn=4,wk=2,cluster=1", x_bits=x)
