@@ -155,9 +155,11 @@ QFG_API void qfg_dequant_destroy(qfg_dequant* op);
  * orders (value, index) pairs exactly like ArgmaxRows does - larger is better - which is the
  * payload the N-sharded LM head all-gathers; qfg_lmhead_combine folds the gathered words.
  *
- * `workspace` is qfg_lmhead_workspace_bytes() bytes of device memory that must be zero before
- * the first call; each call leaves it zero again.  Calls that share a workspace must not
- * overlap on the GPU. */
+ * `workspace` is qfg_lmhead_workspace_bytes() bytes of device memory (about 5 MB: 256 bytes of
+ * keys and a counter, then room for the FP32 partial sums of column groups that the CTAs share
+ * when the vocabulary does not divide evenly among them).  Its first 256 bytes must be zero
+ * before the first call; each call leaves them zero again.  Calls that share a workspace must
+ * not overlap on the GPU. */
 QFG_API size_t qfg_lmhead_workspace_bytes(void);
 QFG_API int qfg_lmhead_create(const float* w_scale, size_t n_w_scale, int trigger, qfg_lmhead** out);
 QFG_API int qfg_lmhead_compute(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,

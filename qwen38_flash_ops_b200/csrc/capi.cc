@@ -210,7 +210,7 @@ qfg::Plan ComputePlan(const qfg_skinny_gemm& op, const qfg::PlanInput& in);
 qfg::Plan PlanFor(const qfg_skinny_gemm& op, qfg::PlanInput in, int rows) {
   in.max_rows = rows;
   std::string key = std::to_string(in.K) + "/" + std::to_string(in.mode) + "/" + std::to_string(in.row_align) + "/" +
-                    std::to_string(rows) + "/" + (in.max_clusters != nullptr ? "d" : "h");
+                    std::to_string(rows) + "/" + (in.max_clusters != nullptr ? "d" : "h") + (in.allow_tail ? "t" : "");
   for (int s = 0; s < in.nseg; ++s) key += "/" + std::to_string(in.n[s]);
   {
     std::lock_guard<std::mutex> lock(op.plan_mu);
@@ -231,6 +231,7 @@ qfg::Plan ComputePlan(const qfg_skinny_gemm& op, const qfg::PlanInput& in) {
     if (e != nullptr) spec = e;
   }
   if (!spec.empty() && !qfg::ApplyPlanOverrides(spec, in, &plan)) throw InvalidArgument("SkinnyGemm: bad plan override");
+  qfg::ChooseTail(in, spec.find("tail=") != std::string::npos, &plan);
   return plan;
 }
 
@@ -307,8 +308,8 @@ int SetLastError(int code, const char* message) { return Fail(code, message); }
 
 // The fused LM head on a caller-chosen scratch area (see qfg_lmhead_compute).
 int LmheadComputeWithWorkspace(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
-                       int64_t n, int64_t col_offset, void* workspace, int64_t* idx, float* val, uint64_t* key,
-                       void* logits, void* stream) {
+                       int64_t n, int64_t col_offset, void* workspace, size_t workspace_bytes, int64_t* idx, float* val,
+                       uint64_t* key, void* logits, void* stream) {
   if (op == nullptr || weight == nullptr) return Fail(QFG_FAIL, "LmHead: null argument");
   try {
     if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 8 != 0)
@@ -327,6 +328,8 @@ int LmheadComputeWithWorkspace(const qfg_lmhead* op, const void* x, int64_t m, i
     pr.params.seg[0].vec = pr.params.seg[0].svec = a;
     pr.plan_in.row_align = a;
     pr.plan_in.max_clusters = &qfg::QueryMaxActiveClusters;
+    pr.plan_in.allow_tail = workspace_bytes >= qfg::kLmHeaderBytes + qfg::kLmTailBytes;
+    if (pr.plan_in.allow_tail) pr.params.lm_tail = reinterpret_cast<float*>(static_cast<char*>(workspace) + qfg::kLmHeaderBytes);
     pr.params.out[0] = static_cast<uint16_t*>(logits);
     pr.params.lm = 1;
     pr.params.lm_keys = static_cast<unsigned long long*>(workspace);
@@ -545,7 +548,7 @@ void qfg_dequant_destroy(qfg_dequant* op) {
   delete op;
 }
 
-size_t qfg_lmhead_workspace_bytes(void) { return 128; }
+size_t qfg_lmhead_workspace_bytes(void) { return qfg::kLmHeaderBytes + qfg::kLmTailBytes; }
 
 int qfg_lmhead_create(const float* w_scale, size_t n_w_scale, int trigger, qfg_lmhead** out) {
   if (out == nullptr) return Fail(QFG_INVALID_ARGUMENT, "LmHead: null handle pointer");
@@ -567,7 +570,8 @@ int qfg_lmhead_create(const float* w_scale, size_t n_w_scale, int trigger, qfg_l
 int qfg_lmhead_compute(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
                        int64_t n, int64_t col_offset, void* workspace, int64_t* idx, float* val, uint64_t* key,
                        void* logits, void* stream) {
-  return qfg::LmheadComputeWithWorkspace(op, x, m, k, weight, n, col_offset, workspace, idx, val, key, logits, stream);
+  return qfg::LmheadComputeWithWorkspace(op, x, m, k, weight, n, col_offset, workspace, qfg_lmhead_workspace_bytes(), idx, val,
+                                         key, logits, stream);
 }
 
 int qfg_lmhead_set_option(qfg_lmhead* op, const char* key, const char* value) {

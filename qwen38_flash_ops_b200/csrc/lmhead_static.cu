@@ -70,5 +70,6 @@ extern "C" QFG_API int qfg_lmhead_compute_static(const qfg_lmhead* op, const voi
   static_assert(kStaticScratchBytes >= qfg::kMaxRows * 8 + 4, "scratch too small for the keys and the counter");
   void* scratch = ScratchForCurrentDevice();
   if (scratch == nullptr) return QFG_FAIL;
-  return qfg::LmheadComputeWithWorkspace(op, x, m, k, weight, n, col_offset, scratch, idx, val, key, logits, stream);
+  return qfg::LmheadComputeWithWorkspace(op, x, m, k, weight, n, col_offset, scratch, kStaticScratchBytes, idx, val, key, logits,
+                                         stream);
 }

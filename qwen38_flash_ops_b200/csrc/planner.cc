@@ -283,6 +283,7 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
     else if (key == "direct") plan->direct = val;
     else if (key == "wide") { plan->wide = val; wide_given = true; }
     else if (key == "tc") plan->tc = val != 0 ? 1 : 0;
+    else if (key == "tail") plan->tail = val;
     else return false;
   }
   auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
@@ -336,13 +337,33 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
   return true;
 }
 
+// The shared tail needs: one NVFP4 weight of whole 128-column groups on the direct kernel with 128-column warps,
+// no K split across CTAs (all CTAs must stage the same x), a workspace for the partial sums, and a warp
+// column without columns of its own in every CTA.
+void ChooseTail(const PlanInput& in, bool forced, Plan* plan) {
+  const int want = plan->tail;
+  plan->tail = 0;
+  if (!in.allow_tail || in.nseg != 1 || in.mode != kNvfp4 || !plan->direct || plan->tc || plan->wide != 1 ||
+      plan->cluster != 1 || in.n[0] % 128 != 0) {
+    return;
+  }
+  const int groups = in.n[0] / 128, ctas = plan->tiles[0];
+  if (ctas < 1 || ctas > kMaxTailCtas) return;
+  const int per = groups / ctas;
+  int tail = groups - per * ctas;
+  if (forced) tail = want;  // tests: any count that leaves whole groups per CTA
+  if (tail < 1 || tail > kMaxTailGroups || tail >= groups || (groups - tail) % ctas != 0) return;
+  if ((groups - tail) / ctas > plan->wn - 1) return;
+  plan->tail = tail;
+}
+
 std::string DescribePlan(const Plan& plan, const PlanInput& in) {
   char buf[256];
   int tiles = 0;
   for (int s = 0; s < in.nseg; ++s) tiles += plan.tiles[s];
   std::snprintf(buf, sizeof(buf),
-                "direct=%d,tc=%d,wide=%d,wn=%d,wk=%d,ks=%d,stages=%d,cluster=%d,gran=%d,tiles=%d,ctas=%d,threads=%d,smem=%zu",
-                plan.direct, plan.tc, plan.wide, plan.wn, plan.wk, plan.ks, plan.stages, plan.cluster, plan.gran, tiles,
+                "direct=%d,tc=%d,tail=%d,wide=%d,wn=%d,wk=%d,ks=%d,stages=%d,cluster=%d,gran=%d,tiles=%d,ctas=%d,threads=%d,smem=%zu",
+                plan.direct, plan.tc, plan.tail, plan.wide, plan.wn, plan.wk, plan.ks, plan.stages, plan.cluster, plan.gran, tiles,
                 tiles * plan.cluster, plan.threads(),
                 SmemBytes(plan, in.mode, in.max_rows, in.K));
   return buf;

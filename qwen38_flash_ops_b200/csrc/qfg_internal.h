@@ -53,6 +53,7 @@ struct Plan {
   int gran = 16;    // columns per granule of the balanced column partition
   int direct = 1;   // 1: warp-private cp.async rings, no CTA barrier in the K loop; 0: CTA-wide ring
   int wide = 1;     // NVFP4 direct kernel: 16-column groups per thread (1 or 2)
+  int tail = 0;     // fused LM head: trailing 128-column groups whose K range is split over all CTAs (see GemmParams)
   int tc = 0;       // NVFP4: 1 = tcgen05 kernel (wn x wk warps feed tensor memory, one warp issues the MMAs, wk more
                     // warps run mma.sync on up to 128 columns past wn x 128)
   int warps() const { return tc ? wn * wk + 1 + wk : wn * wk; }
@@ -77,6 +78,7 @@ struct Segment {
   int granules = 0;
   int out_begin = 0;
   int out_end = 0;
+  int tail_cols = 0;  // trailing columns left out of the column tiles (fused LM head, see GemmParams::tail_groups)
   int vec = 16;   // cp.async width for the weight bytes of a row
   int svec = 4;   // cp.async width for the NVFP4 scale bytes of a row
 };
@@ -94,7 +96,7 @@ struct GemmParams {
   int pdl_wait = 0;
   int force_slow = 0;  // testing: always take the BF16-MMA path of the quantised modes
   int debug = 0;       // unused by the kernels (kept for option compatibility)
-  unsigned long long* phase_times = nullptr;  // measurement aid: [CTA][8] globaltimer stamps of the direct kernel
+  unsigned long long* phase_times = nullptr;  // measurement aid: [CTA][16] timer stamps and cycle counts of the direct / tcgen05 kernels
   // plan
   int wn = 4, wk = 2, ks = 1, stages = 4, cluster = 1, gran = 16;
   int xpitch = 0;       // elements per x row in shared memory
@@ -110,7 +112,19 @@ struct GemmParams {
   float* lm_val = nullptr;
   unsigned long long* lm_key_out = nullptr;
   long long lm_col_offset = 0;
+  // Shared tail of the fused LM head.  When the 128-column groups of the vocabulary do not divide by the
+  // CTA count (151936 = 1187 groups on 148 SMs), the `tail_groups` left-over groups are not given to a few
+  // CTAs, which would then run 12 % longer than the rest: every CTA computes its 1/CTAs share of their K
+  // range on warps that have no columns of their own, stores the FP32 partial sums to `lm_tail`
+  // ([group][CTA][8 rows][128]) and the last CTA to arrive adds them up in CTA order.
+  int tail_groups = 0;
+  float* lm_tail = nullptr;
 };
+
+constexpr int kMaxTailGroups = 8;
+constexpr int kMaxTailCtas = 160;
+constexpr size_t kLmHeaderBytes = 256;  // keys, counter, padding
+constexpr size_t kLmTailBytes = static_cast<size_t>(kMaxTailGroups) * kMaxTailCtas * kMaxRows * 128 * 4;
 
 // planner.cc
 struct PlanInput {
@@ -124,11 +138,14 @@ struct PlanInput {
   // Co-resident clusters (CTAs for cluster == 1) of a launch shape on the current device, or null
   // when planning without a device (then a B200-like packing loss is assumed for clusters).
   int (*max_clusters)(int mode, int direct, int threads, size_t smem, int cluster) = nullptr;
+  bool allow_tail = false;  // the call is a fused LM head whose workspace can hold the shared-tail partial sums
 };
 Plan ChoosePlan(const PlanInput& in);
 // Applies "key=value,..." overrides (wn, wk, ks, stages, cluster, ctas, gran); returns false on a bad key.
 bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan);
 void FitRing(const PlanInput& in, int rows, Plan* plan);
+// Decides Plan::tail for a fused LM head (see GemmParams::tail_groups); `forced`: the override gave a value.
+void ChooseTail(const PlanInput& in, bool forced, Plan* plan);
 void DistributeTiles(const PlanInput& in, int total_tiles, Plan* plan);
 size_t SmemBytes(const Plan& plan, int mode, int rows, int K);
 std::string DescribePlan(const Plan& plan, const PlanInput& in);
@@ -147,8 +164,8 @@ cudaError_t LaunchLmheadCombine(const uint64_t* keys, int ranks, int64_t m, int6
 
 // capi.cc
 int LmheadComputeWithWorkspace(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
-                               int64_t n, int64_t col_offset, void* workspace, int64_t* idx, float* val, uint64_t* key,
-                               void* logits, void* stream);
+                               int64_t n, int64_t col_offset, void* workspace, size_t workspace_bytes, int64_t* idx,
+                               float* val, uint64_t* key, void* logits, void* stream);
 int SetLastError(int code, const char* message);
 
 // dequant_bf16.cu

@@ -305,7 +305,7 @@ __device__ __forceinline__ Tile LocateTile(const GemmParams& p) {
   const Segment& sg = p.seg[s];
   const int t = static_cast<int>(blockIdx.x) - sg.tile_begin;
   tl.n0 = static_cast<int>(static_cast<long long>(t) * sg.granules / sg.tiles) * p.gran;
-  tl.n1 = min(sg.n, static_cast<int>(static_cast<long long>(t + 1) * sg.granules / sg.tiles) * p.gran);
+  tl.n1 = min(sg.n - sg.tail_cols, static_cast<int>(static_cast<long long>(t + 1) * sg.granules / sg.tiles) * p.gran);
   tl.C = static_cast<int>(gridDim.y);
   tl.crank = static_cast<int>(blockIdx.y);
   const int ksteps_total = (p.K + 15) >> 4;
@@ -564,41 +564,44 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
 
   if (p.lm) {
     // CTA-level (max, index) per row, folded into the workspace keys with a 64-bit atomic max.
-    __syncthreads();
+    auto fold_into_keys = [&]() {
+      __syncthreads();
 #pragma unroll
-    for (int m = 0; m < kMaxRows; ++m) {
-      if (m < M) {
-        float v = best_i[m] < 0 ? -INFINITY : best_v[m];
-        long long i = best_i[m] < 0 ? LLONG_MAX : best_i[m];
+      for (int m = 0; m < kMaxRows; ++m) {
+        if (m < M) {
+          float v = best_i[m] < 0 ? -INFINITY : best_v[m];
+          long long i = best_i[m] < 0 ? LLONG_MAX : best_i[m];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-          const float ov = __shfl_xor_sync(0xffffffffu, v, off);
-          const long long oi = __shfl_xor_sync(0xffffffffu, i, off);
-          if (Better(ov, oi, v, i)) {
-            v = ov;
-            i = oi;
+          for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, off);
+            const long long oi = __shfl_xor_sync(0xffffffffu, i, off);
+            if (Better(ov, oi, v, i)) {
+              v = ov;
+              i = oi;
+            }
+          }
+          if (lane == 0) {
+            sh.best_v[warp][m] = v;
+            sh.best_i[warp][m] = i;
           }
         }
-        if (lane == 0) {
-          sh.best_v[warp][m] = v;
-          sh.best_i[warp][m] = i;
-        }
       }
-    }
-    __syncthreads();
-    if (tid < M) {
-      float v = sh.best_v[0][tid];
-      long long i = sh.best_i[0][tid];
-      for (int w = 1; w < (nthreads >> 5); ++w) {
-        if (Better(sh.best_v[w][tid], sh.best_i[w][tid], v, i)) {
-          v = sh.best_v[w][tid];
-          i = sh.best_i[w][tid];
+      __syncthreads();
+      if (tid < M) {
+        float v = sh.best_v[0][tid];
+        long long i = sh.best_i[0][tid];
+        for (int w = 1; w < (nthreads >> 5); ++w) {
+          if (Better(sh.best_v[w][tid], sh.best_i[w][tid], v, i)) {
+            v = sh.best_v[w][tid];
+            i = sh.best_i[w][tid];
+          }
         }
+        if (i != LLONG_MAX) atomicMax(p.lm_keys + tid, PackKey(v, i));
+        __threadfence();
       }
-      if (i != LLONG_MAX) atomicMax(p.lm_keys + tid, PackKey(v, i));
-      __threadfence();
-    }
-    __syncthreads();
+      __syncthreads();
+    };
+    fold_into_keys();
     if (tid == 0) {
       const unsigned int total = gridDim.x * gridDim.y;
       const unsigned int prev = atomicAdd(p.lm_count, 1u);
@@ -607,6 +610,26 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
     }
     __syncthreads();
     if (sh.last) {
+      if (p.tail_groups > 0) {
+        // every CTA stored its partial sums of the shared tail columns before it counted itself in:
+        // add them up in CTA order, finish those columns and fold their best into the keys
+        __threadfence();
+#pragma unroll
+        for (int m = 0; m < kMaxRows; ++m) {
+          best_v[m] = 0.f;
+          best_i[m] = -1;
+        }
+        const int nct = static_cast<int>(gridDim.x);
+        const int n_main = sg.n - p.tail_groups * 128;
+        for (int idx = tid; idx < p.tail_groups * M * 128; idx += nthreads) {
+          const int col = idx & 127, m = (idx >> 7) % M, tg = (idx >> 7) / M;
+          const float* src = p.lm_tail + (static_cast<size_t>(tg) * nct * kMaxRows + m) * 128 + col;
+          float sum = 0.f;
+          for (int c = 0; c < nct; ++c) sum += __ldcg(src + static_cast<size_t>(c) * kMaxRows * 128);
+          finalize(m, n_main + tg * 128 + col - n0, sum * sh.inv_scale[m]);
+        }
+        fold_into_keys();
+      }
       if (tid < M) {
         const unsigned long long key = atomicExch(p.lm_keys + tid, 0ull);
         const uint32_t ord = static_cast<uint32_t>(key >> 32);
@@ -679,7 +702,7 @@ __device__ __forceinline__ void Stamp(const GemmParams& p, int slot) {
   if (p.phase_times != nullptr && threadIdx.x == 0) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    p.phase_times[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 8 + slot] = t;
+    p.phase_times[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16 + slot] = t;
   }
 }
 template <typename T>
@@ -708,6 +731,141 @@ struct DirectSlot {
   __device__ static constexpr int NibRow(int r) { return r * kNibPitch + ((r >> 3) & 1) * 32; }
   __device__ static constexpr int SclRow(int r) { return kNibBytes + r * kSclPitch + (r >> 2) * 32; }
 };
+
+// One warp's NVFP4 stream (128 columns): copy plan, ring and read offsets of the direct kernel, W = 1.
+template <int DEPTH>
+struct Nvfp4Stream {
+  using S = DirectSlot<kNvfp4, 1>;
+  static constexpr int NP = S::kPieces;
+  const uint8_t* gbase;
+  long long step_stride;
+  uint32_t off[NP], dst[NP], pmask, rd_w[2], rd_s[2], ring;
+  int nsteps, careful_step, row0, lane, kstride;
+
+  // k-steps wk, wk + p.wk, ... of the CTA's K slice
+  __device__ __forceinline__ void Setup(const GemmParams& p, const Tile& tl, const Segment& sg, int colwarp, int wk,
+                                        uint32_t ring_addr, bool active) {
+    const int ksteps = (tl.kslice + 15) >> 4;
+    SetupRange(tl, sg, colwarp, wk, (active && ksteps > wk) ? (ksteps - wk + p.wk - 1) / p.wk : 0, p.wk, ring_addr);
+  }
+
+  // k-steps k_first, k_first + k_stride, ... (k_count of them) of the CTA's K slice; colwarp is a column of the weight
+  __device__ __forceinline__ void SetupRange(const Tile& tl, const Segment& sg, int colwarp, int k_first, int k_count,
+                                             int k_stride, uint32_t ring_addr) {
+    lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const long long pitch = sg.pitch;
+    const int ksteps = (tl.kslice + 15) >> 4;
+    nsteps = k_count;
+    kstride = k_stride;
+    // the slice's last k-step is copied by the careful path
+    careful_step = (k_count > 0 && ksteps - 1 >= k_first && (ksteps - 1 - k_first) % k_stride == 0 &&
+                    (ksteps - 1 - k_first) / k_stride < k_count)
+                       ? (ksteps - 1 - k_first) / k_stride
+                       : -1;
+    row0 = tl.kbeg + k_first * 16;
+    step_stride = static_cast<long long>(k_stride) * 16 * pitch;
+    ring = ring_addr;
+    const long long warp_col_byte = colwarp / 2;
+    gbase = sg.w + static_cast<long long>(row0) * pitch + warp_col_byte - 16;
+    const int mis = static_cast<int>(pitch & 8);
+    const int cshift = static_cast<int>(warp_col_byte & 8);
+    const long long sabs = static_cast<long long>(sg.n >> 1) + (colwarp >> 4);
+    const int so_even = static_cast<int>(sabs & 15), so_odd = static_cast<int>((sabs + mis) & 15);
+    const int sh_even = cshift, sh_odd = (mis + cshift) & 15;
+    pmask = 0;
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      const int slot = lane + 32 * j;
+      const int r = slot / S::kPiecesPerRow, c = slot - r * S::kPiecesPerRow;
+      off[j] = 0;
+      dst[j] = 0;
+      if (r < 16) {
+        if (c < 5) {
+          const int shift = (r & 1) ? sh_odd : sh_even;
+          if (c < 4 || shift != 0) pmask |= 1u << j;
+          off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (c * 16 - shift) + 16);
+          dst[j] = static_cast<uint32_t>(S::NibRow(r) + c * 16);
+        } else {
+          const int c2 = c - 5;
+          const int o = (r & 1) ? so_odd : so_even;
+          if (c2 == 0 || o + 8 > 16) pmask |= 1u << j;
+          off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (sabs - o + c2 * 16 - warp_col_byte) + 16);
+          dst[j] = static_cast<uint32_t>(S::SclRow(r) + c2 * 16);
+        }
+      }
+    }
+    const int rbase = S::NibRow(4 * t) + g * 8, sbase = S::SclRow(4 * t) + g;
+    rd_w[0] = static_cast<uint32_t>(rbase + sh_even);
+    rd_w[1] = static_cast<uint32_t>(rbase + sh_odd);
+    rd_s[0] = static_cast<uint32_t>(sbase + so_even);
+    rd_s[1] = static_cast<uint32_t>(sbase + so_odd);
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      Pin(off[j]);
+      Pin(dst[j]);
+    }
+    Pin(pmask);
+    Pin(rd_w[0]);
+    Pin(rd_w[1]);
+    Pin(rd_s[0]);
+    Pin(rd_s[1]);
+  }
+
+  __device__ __forceinline__ void Issue(const GemmParams& p, const Tile& tl, const Segment& sg, int s, uint32_t slot_addr) {
+    if (s != careful_step) {
+#pragma unroll
+      for (int j = 0; j < NP; ++j) CpAsync16If(pmask & (1u << j), slot_addr + dst[j], gbase, off[j]);
+    } else {
+      const int r0 = row0 + s * kstride * 16;
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        if (pmask & (1u << j)) {
+          const int r = (lane + 32 * j) / S::kPiecesPerRow;
+          const uint8_t* src = gbase + off[j];
+          const long long room = sg.total_bytes - (src - sg.w);
+          const int bytes = (r0 + r >= tl.kend) ? 0 : room >= 16 ? 16 : room > 0 ? static_cast<int>(room) : 0;
+          CpAsync16(slot_addr + dst[j], bytes > 0 ? src : sg.w, bytes);
+        }
+      }
+    }
+    gbase += step_stride;
+  }
+
+  __device__ __forceinline__ void Prologue(const GemmParams& p, const Tile& tl, const Segment& sg) {
+#pragma unroll
+    for (int d = 0; d < DEPTH - 1; ++d) {
+      if (d < nsteps) Issue(p, tl, sg, d, ring + d * S::kBytes);
+      CpAsyncCommit();
+    }
+  }
+
+  // consume(raw, s) for every local step s, DEPTH - 1 steps behind the copies
+  template <class F>
+  __device__ __forceinline__ void Run(const GemmParams& p, const Tile& tl, const Segment& sg, F&& consume) {
+    const uint32_t ring_end = ring + DEPTH * S::kBytes;
+    uint32_t rd_slot = ring, wr_slot = ring + (DEPTH - 1) * S::kBytes;
+    for (int s = 0; s < nsteps; ++s) {
+      __syncwarp();
+      if (s + DEPTH - 1 < nsteps) Issue(p, tl, sg, s + DEPTH - 1, wr_slot);
+      CpAsyncCommit();
+      asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
+      __syncwarp();
+      Raw<kNvfp4, 1> raw;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        raw.r[0][i] = Lds64(rd_slot + rd_w[i & 1] + i * S::kNibPitch);
+        raw.s[0][i] = Lds8(rd_slot + rd_s[i & 1] + i * S::kSclPitch);
+      }
+      wr_slot = rd_slot;
+      rd_slot += S::kBytes;
+      if (rd_slot == ring_end) rd_slot = ring;
+      consume(raw, s);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  }
+};
+
 
 template <int MODE, int DEPTH, int W>
 __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) SkinnyGemmDirectKernel(const GemmParams p) {
@@ -897,6 +1055,46 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if constexpr (MODE == kNvfp4 && W == 1) {
+    if (p.tail_groups > 0 && !warp_has_cols && wn == p.wn - 1) {
+      // Shared tail of the fused LM head: this warp has no columns of the tile, so it computes this CTA's
+      // share of the K range of the left-over column groups and stores the partial sums.
+      const int nct = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
+      const int k0 = static_cast<int>(static_cast<long long>(cta) * ksteps / nct);
+      const int k1 = static_cast<int>(static_cast<long long>(cta + 1) * ksteps / nct);
+      const int n_main = sg.n - p.tail_groups * 128;
+      const int x_row = g < p.M ? g : 0;
+      for (int tg = wk; tg < p.tail_groups; tg += p.wk) {
+        Nvfp4Stream<DEPTH> ts;
+        ts.SetupRange(tl, sg, n_main + tg * 128, k0, k1 - k0, 1, ring);
+        ts.Prologue(p, tl, sg);
+        // this warp's own accumulators are unused (it has no columns): accumulate the tail in them
+#pragma unroll
+        for (int j = 0; j < NM; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+        uint32_t xr = SmemAddr(xs) + static_cast<uint32_t>((x_row * p.xpitch + 4 * t + k0 * 16) * 2);
+        ts.Run(p, tl, sg, [&](const Raw<kNvfp4, 1>& raw, int) {
+          const uint2 xv = Lds64(xr);
+          xr += 32;
+          if (slow) {
+            ComputeStep<kNvfp4, true, 1>(acc, raw, xv.x, xv.y);
+          } else {
+            ComputeStep<kNvfp4, false, 1>(acc, raw, xv.x, xv.y);
+          }
+        });
+        float* dstp = p.lm_tail + (static_cast<size_t>(tg) * nct + cta) * kMaxRows * 128;
+#pragma unroll
+        for (int j = 0; j < NM; ++j) {
+          const int cl = g * 16 + 2 * j;
+          const int m0 = 2 * t, m1 = 2 * t + 1;
+          if (m0 < p.M) *reinterpret_cast<float2*>(&dstp[m0 * 128 + cl]) = make_float2(acc[j][0], acc[j][2]);
+          if (m1 < p.M) *reinterpret_cast<float2*>(&dstp[m1 * 128 + cl]) = make_float2(acc[j][1], acc[j][3]);
+        }
+      }
+      __threadfence();
+    }
+  }
   Stamp(p, 3);
   if (p.trigger == 2) GridLaunchDependents();
   __syncthreads();
@@ -954,127 +1152,6 @@ struct TcShared {
   unsigned long long done;                             // 1 arrival: every MMA of the CTA completed
   uint32_t tmem_base;
   uint32_t fault;
-};
-
-// One warp's NVFP4 stream (128 columns): copy plan, ring and read offsets of the direct kernel, W = 1.
-template <int DEPTH>
-struct Nvfp4Stream {
-  using S = DirectSlot<kNvfp4, 1>;
-  static constexpr int NP = S::kPieces;
-  const uint8_t* gbase;
-  long long step_stride;
-  uint32_t off[NP], dst[NP], pmask, rd_w[2], rd_s[2], ring;
-  int nsteps, careful_step, row0, lane;
-
-  __device__ __forceinline__ void Setup(const GemmParams& p, const Tile& tl, const Segment& sg, int colwarp, int wk,
-                                        uint32_t ring_addr, bool active) {
-    lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const long long pitch = sg.pitch;
-    const int ksteps = (tl.kslice + 15) >> 4;
-    nsteps = (active && ksteps > wk) ? (ksteps - wk + p.wk - 1) / p.wk : 0;
-    careful_step = (((ksteps - 1) % p.wk) == wk) ? nsteps - 1 : -1;
-    row0 = tl.kbeg + wk * 16;
-    step_stride = static_cast<long long>(p.wk) * 16 * pitch;
-    ring = ring_addr;
-    const long long warp_col_byte = colwarp / 2;
-    gbase = sg.w + static_cast<long long>(row0) * pitch + warp_col_byte - 16;
-    const int mis = static_cast<int>(pitch & 8);
-    const int cshift = static_cast<int>(warp_col_byte & 8);
-    const long long sabs = static_cast<long long>(sg.n >> 1) + (colwarp >> 4);
-    const int so_even = static_cast<int>(sabs & 15), so_odd = static_cast<int>((sabs + mis) & 15);
-    const int sh_even = cshift, sh_odd = (mis + cshift) & 15;
-    pmask = 0;
-#pragma unroll
-    for (int j = 0; j < NP; ++j) {
-      const int slot = lane + 32 * j;
-      const int r = slot / S::kPiecesPerRow, c = slot - r * S::kPiecesPerRow;
-      off[j] = 0;
-      dst[j] = 0;
-      if (r < 16) {
-        if (c < 5) {
-          const int shift = (r & 1) ? sh_odd : sh_even;
-          if (c < 4 || shift != 0) pmask |= 1u << j;
-          off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (c * 16 - shift) + 16);
-          dst[j] = static_cast<uint32_t>(S::NibRow(r) + c * 16);
-        } else {
-          const int c2 = c - 5;
-          const int o = (r & 1) ? so_odd : so_even;
-          if (c2 == 0 || o + 8 > 16) pmask |= 1u << j;
-          off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (sabs - o + c2 * 16 - warp_col_byte) + 16);
-          dst[j] = static_cast<uint32_t>(S::SclRow(r) + c2 * 16);
-        }
-      }
-    }
-    const int rbase = S::NibRow(4 * t) + g * 8, sbase = S::SclRow(4 * t) + g;
-    rd_w[0] = static_cast<uint32_t>(rbase + sh_even);
-    rd_w[1] = static_cast<uint32_t>(rbase + sh_odd);
-    rd_s[0] = static_cast<uint32_t>(sbase + so_even);
-    rd_s[1] = static_cast<uint32_t>(sbase + so_odd);
-#pragma unroll
-    for (int j = 0; j < NP; ++j) {
-      Pin(off[j]);
-      Pin(dst[j]);
-    }
-    Pin(pmask);
-    Pin(rd_w[0]);
-    Pin(rd_w[1]);
-    Pin(rd_s[0]);
-    Pin(rd_s[1]);
-  }
-
-  __device__ __forceinline__ void Issue(const GemmParams& p, const Tile& tl, const Segment& sg, int s, uint32_t slot_addr) {
-    if (s != careful_step) {
-#pragma unroll
-      for (int j = 0; j < NP; ++j) CpAsync16If(pmask & (1u << j), slot_addr + dst[j], gbase, off[j]);
-    } else {
-      const int r0 = row0 + s * p.wk * 16;
-#pragma unroll
-      for (int j = 0; j < NP; ++j) {
-        if (pmask & (1u << j)) {
-          const int r = (lane + 32 * j) / S::kPiecesPerRow;
-          const uint8_t* src = gbase + off[j];
-          const long long room = sg.total_bytes - (src - sg.w);
-          const int bytes = (r0 + r >= tl.kend) ? 0 : room >= 16 ? 16 : room > 0 ? static_cast<int>(room) : 0;
-          CpAsync16(slot_addr + dst[j], bytes > 0 ? src : sg.w, bytes);
-        }
-      }
-    }
-    gbase += step_stride;
-  }
-
-  __device__ __forceinline__ void Prologue(const GemmParams& p, const Tile& tl, const Segment& sg) {
-#pragma unroll
-    for (int d = 0; d < DEPTH - 1; ++d) {
-      if (d < nsteps) Issue(p, tl, sg, d, ring + d * S::kBytes);
-      CpAsyncCommit();
-    }
-  }
-
-  // consume(raw, s) for every local step s, DEPTH - 1 steps behind the copies
-  template <class F>
-  __device__ __forceinline__ void Run(const GemmParams& p, const Tile& tl, const Segment& sg, F&& consume) {
-    const uint32_t ring_end = ring + DEPTH * S::kBytes;
-    uint32_t rd_slot = ring, wr_slot = ring + (DEPTH - 1) * S::kBytes;
-    for (int s = 0; s < nsteps; ++s) {
-      __syncwarp();
-      if (s + DEPTH - 1 < nsteps) Issue(p, tl, sg, s + DEPTH - 1, wr_slot);
-      CpAsyncCommit();
-      asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
-      __syncwarp();
-      Raw<kNvfp4, 1> raw;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        raw.r[0][i] = Lds64(rd_slot + rd_w[i & 1] + i * S::kNibPitch);
-        raw.s[0][i] = Lds8(rd_slot + rd_s[i & 1] + i * S::kSclPitch);
-      }
-      wr_slot = rd_slot;
-      rd_slot += S::kBytes;
-      if (rd_slot == ring_end) rd_slot = ring;
-      consume(raw, s);
-    }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-  }
 };
 
 // The A operand registers of the eight 16-column MMAs of one k-step (fr[j] = {a0, a1, a2, a3} of MMA j as
@@ -1194,6 +1271,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const GemmP
     const uint32_t a_base = tmem + static_cast<uint32_t>(d_cols + unit * kTcBuffers * 32) + (static_cast<uint32_t>(32 * q) << 16);
     const uint32_t full0 = SmemAddr(&tc.full[unit][0]), empty0 = SmemAddr(&tc.empty[unit][0]);
     int b = 0, round = 0;  // buffer of step s and how many times the buffers were cycled
+    long long t_empty = 0, t_store = 0;
+    const bool probe = p.phase_times != nullptr && warp == 0 && lane == 0;
     auto publish = [&](const Raw<kNvfp4, 1>* raw) {
       uint32_t fr[8][4];
       if (raw != nullptr) {
@@ -1203,7 +1282,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const GemmP
           Nvfp4Fragments<false>(*raw, fr);
         }
       }
+      const long long c0 = probe ? clock64() : 0;
       if (round > 0 && !MbarWait(empty0 + b * 8, static_cast<uint32_t>((round - 1) & 1))) tc.fault = 1;
+      const long long c1 = probe ? clock64() : 0;
       if (raw != nullptr) {
         TcFenceAfter();
         const uint32_t ta = a_base + static_cast<uint32_t>(b * 32);
@@ -1214,6 +1295,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const GemmP
       }
       __syncwarp();
       if (lane == 0) MbarArrive(full0 + b * 8);
+      if (probe) {
+        t_empty += c1 - c0;
+        t_store += clock64() - c1;
+      }
       if (++b == kTcBuffers) {
         b = 0;
         ++round;
@@ -1224,12 +1309,19 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const GemmP
     } else {
       for (int s = 0; s < proto_steps; ++s) publish(nullptr);
     }
+    if (probe) {
+      unsigned long long* o = p.phase_times + (static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16;
+      o[6] = static_cast<unsigned long long>(t_empty);
+      o[7] = static_cast<unsigned long long>(t_store);
+    }
   } else if (is_issuer) {
     if (lane == 0) {
       const uint32_t idesc = 0x10u | (2u << 17) | (8u << 24) | (slow ? ((1u << 7) | (1u << 10)) : 0u);
       const uint32_t xa = SmemAddr(xs);
       const int max_steps = (ksteps + p.wk - 1) / p.wk;
       int b = 0, round = 0;
+      long long t_full = 0, t_issue = 0;
+      const bool probe = p.phase_times != nullptr;
       for (int s = 0; s < max_steps; ++s) {
         for (int wkI = 0; wkI < p.wk; ++wkI) {
           const int kk = wkI + s * p.wk;
@@ -1240,7 +1332,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const GemmP
                                           (static_cast<unsigned long long>(256 >> 4) << 32) | (1ull << 46);
           for (int gi = 0; gi < ngroups; ++gi) {
             const int u = wkI * ngroups + gi;
+            const long long c0 = probe ? clock64() : 0;
             if (!MbarWait(SmemAddr(&tc.full[u][b]), static_cast<uint32_t>(round & 1))) tc.fault = 1;
+            const long long c1 = probe ? clock64() : 0;
             TcFenceAfter();
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -1255,6 +1349,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const GemmP
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                              SmemAddr(&tc.empty[u][b]))
                          : "memory");
+            if (probe) {
+              t_full += c1 - c0;
+              t_issue += clock64() - c1;
+            }
           }
         }
         if (++b == kTcBuffers) {
@@ -1264,6 +1362,11 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const GemmP
       }
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(SmemAddr(&tc.done))
                    : "memory");
+      if (probe) {
+        unsigned long long* o = p.phase_times + (static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16;
+        o[8] = static_cast<unsigned long long>(t_full);
+        o[9] = static_cast<unsigned long long>(t_issue);
+      }
     }
     __syncwarp();
   } else {
@@ -1704,11 +1807,14 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
     if (smem < 120 * 1024) smem = 120 * 1024;
   }
   if (g_max_dynamic_smem > 0 && smem > static_cast<size_t>(g_max_dynamic_smem)) return cudaErrorInvalidConfiguration;
+  p.tail_groups = plan.tail;
+  if (plan.tail > 0 && (!p.lm || p.lm_tail == nullptr || p.nseg != 1 || plan.cluster != 1)) return cudaErrorInvalidValue;
   int tiles = 0;
   for (int s = 0; s < p.nseg; ++s) {
     p.seg[s].tile_begin = tiles;
     p.seg[s].tiles = plan.tiles[s];
-    p.seg[s].granules = (p.seg[s].n + plan.gran - 1) / plan.gran;
+    p.seg[s].tail_cols = (s == 0) ? plan.tail * 128 : 0;
+    p.seg[s].granules = (p.seg[s].n - p.seg[s].tail_cols + plan.gran - 1) / plan.gran;
     tiles += plan.tiles[s];
   }
   switch (mode) {
