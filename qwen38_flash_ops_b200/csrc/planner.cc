@@ -348,7 +348,7 @@ void ChooseTail(const PlanInput& in, bool forced, Plan* plan) {
     return;
   }
   const int groups = in.n[0] / 128, ctas = plan->tiles[0];
-  if (ctas < 1 || ctas > kMaxTailCtas) return;
+  if (ctas < 1) return;
   const int per = groups / ctas;
   int tail = groups - per * ctas;
   if (forced) tail = want;  // tests: any count that leaves whole groups per CTA

@@ -114,17 +114,19 @@ struct GemmParams {
   long long lm_col_offset = 0;
   // Shared tail of the fused LM head.  When the 128-column groups of the vocabulary do not divide by the
   // CTA count (151936 = 1187 groups on 148 SMs), the `tail_groups` left-over groups are not given to a few
-  // CTAs, which would then run 12 % longer than the rest: every CTA computes its 1/CTAs share of their K
-  // range on warps that have no columns of their own, stores the FP32 partial sums to `lm_tail`
-  // ([group][CTA][8 rows][128]) and the last CTA to arrive adds them up in CTA order.
+  // CTAs, which would then run 12 % longer than the rest: warps that have no columns of their own (the last
+  // warp column of every CTA) each take one of `tail_split` slices of the K range of one left-over group,
+  // store the FP32 partial sums to `lm_tail` ([group][slice][8 rows][128]), and the last CTA to arrive adds
+  // the slices up in slice order.
   int tail_groups = 0;
+  int tail_split = 1;
   float* lm_tail = nullptr;
 };
 
 constexpr int kMaxTailGroups = 8;
-constexpr int kMaxTailCtas = 160;
+constexpr int kMaxTailSplit = 8;
 constexpr size_t kLmHeaderBytes = 256;  // keys, counter, padding
-constexpr size_t kLmTailBytes = static_cast<size_t>(kMaxTailGroups) * kMaxTailCtas * kMaxRows * 128 * 4;
+constexpr size_t kLmTailBytes = static_cast<size_t>(kMaxTailGroups) * kMaxTailSplit * kMaxRows * 128 * 4;
 
 // planner.cc
 struct PlanInput {

@@ -611,21 +611,20 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
     __syncthreads();
     if (sh.last) {
       if (p.tail_groups > 0) {
-        // every CTA stored its partial sums of the shared tail columns before it counted itself in:
-        // add them up in CTA order, finish those columns and fold their best into the keys
+        // the partial sums of the shared columns were stored before their CTAs counted themselves in:
+        // add the K slices up in order, finish those columns and fold their best into the keys
         __threadfence();
 #pragma unroll
         for (int m = 0; m < kMaxRows; ++m) {
           best_v[m] = 0.f;
           best_i[m] = -1;
         }
-        const int nct = static_cast<int>(gridDim.x);
         const int n_main = sg.n - p.tail_groups * 128;
         for (int idx = tid; idx < p.tail_groups * M * 128; idx += nthreads) {
           const int col = idx & 127, m = (idx >> 7) % M, tg = (idx >> 7) / M;
-          const float* src = p.lm_tail + (static_cast<size_t>(tg) * nct * kMaxRows + m) * 128 + col;
+          const float* src = p.lm_tail + (static_cast<size_t>(tg) * p.tail_split * kMaxRows + m) * 128 + col;
           float sum = 0.f;
-          for (int c = 0; c < nct; ++c) sum += __ldcg(src + static_cast<size_t>(c) * kMaxRows * 128);
+          for (int c = 0; c < p.tail_split; ++c) sum += __ldcg(src + static_cast<size_t>(c) * kMaxRows * 128);
           finalize(m, n_main + tg * 128 + col - n0, sum * sh.inv_scale[m]);
         }
         fold_into_keys();
@@ -1059,12 +1058,13 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
     if (p.tail_groups > 0 && !warp_has_cols && wn == p.wn - 1) {
       // Shared tail of the fused LM head: this warp has no columns of the tile, so it computes this CTA's
       // share of the K range of the left-over column groups and stores the partial sums.
-      const int nct = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
-      const int k0 = static_cast<int>(static_cast<long long>(cta) * ksteps / nct);
-      const int k1 = static_cast<int>(static_cast<long long>(cta + 1) * ksteps / nct);
+      const int worker = static_cast<int>(blockIdx.x) * p.wk + wk;  // one (group, K slice) per idle warp
       const int n_main = sg.n - p.tail_groups * 128;
       const int x_row = g < p.M ? g : 0;
-      for (int tg = wk; tg < p.tail_groups; tg += p.wk) {
+      if (worker < p.tail_groups * p.tail_split) {
+        const int tg = worker / p.tail_split, slice = worker - tg * p.tail_split;
+        const int k0 = static_cast<int>(static_cast<long long>(slice) * ksteps / p.tail_split);
+        const int k1 = static_cast<int>(static_cast<long long>(slice + 1) * ksteps / p.tail_split);
         Nvfp4Stream<DEPTH> ts;
         ts.SetupRange(tl, sg, n_main + tg * 128, k0, k1 - k0, 1, ring);
         ts.Prologue(p, tl, sg);
@@ -1083,7 +1083,7 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
             ComputeStep<kNvfp4, false, 1>(acc, raw, xv.x, xv.y);
           }
         });
-        float* dstp = p.lm_tail + (static_cast<size_t>(tg) * nct + cta) * kMaxRows * 128;
+        float* dstp = p.lm_tail + static_cast<size_t>(worker) * kMaxRows * 128;
 #pragma unroll
         for (int j = 0; j < NM; ++j) {
           const int cl = g * 16 + 2 * j;
@@ -1808,6 +1808,8 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
   }
   if (g_max_dynamic_smem > 0 && smem > static_cast<size_t>(g_max_dynamic_smem)) return cudaErrorInvalidConfiguration;
   p.tail_groups = plan.tail;
+  // K slices per shared group: one per idle warp as far as they go, at most kMaxTailSplit
+  p.tail_split = plan.tail > 0 ? std::max(1, std::min(kMaxTailSplit, plan.tiles[0] * plan.wk / plan.tail)) : 1;
   if (plan.tail > 0 && (!p.lm || p.lm_tail == nullptr || p.nseg != 1 || plan.cluster != 1)) return cudaErrorInvalidValue;
   int tiles = 0;
   for (int s = 0; s < p.nseg; ++s) {

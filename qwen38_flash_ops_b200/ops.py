@@ -160,7 +160,7 @@ class LmHeadArgmax:
 
     Returns (idx int64 [m], val float32 [m], key uint64-as-int64 [m]); `key` orders
     (value, index) pairs like ArgmaxRows does and is what the N-sharded head all-gathers.
-    The instance owns a zeroed workspace (about 5 MB); calls on one instance must not overlap on the GPU.
+    The instance owns a zeroed workspace (about 256 KB); calls on one instance must not overlap on the GPU.
     """
 
     def __init__(self, w_scale=None, trigger: int = 0, device="cuda"):
