@@ -51,7 +51,8 @@ struct Plan {
   int cluster = 1;  // CTAs splitting K, reduced through distributed shared memory
   int tiles[kMaxSeg] = {0, 0, 0, 0};  // column tiles per segment
   int gran = 16;    // columns per granule of the balanced column partition
-  int direct = 1;   // 1: warp-private cp.async rings, no CTA barrier in the K loop; 0: CTA-wide ring
+  int direct = 1;   // 1: warp-private cp.async rings, no CTA barrier in the K loop; 2: warps stream straight into
+                    // registers (BF16 / FP8); 0: CTA-wide ring
   int wide = 1;     // NVFP4 direct kernel: 16-column groups per thread (1 or 2)
   int tail = 0;     // fused LM head: trailing 128-column groups whose K range is split over all CTAs (see GemmParams)
   int tc = 0;       // NVFP4: 1 = tcgen05 kernel (wn x wk warps feed tensor memory, one warp issues the MMAs, wk more

@@ -1103,6 +1103,147 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
   Stamp(p, 5);
 }
 
+// ------------------------------------------------------------------------------ register-streaming kernel
+// BF16 / FP8 only.  Every warp loads its rows straight into registers with 128-bit non-allocating
+// loads, D k-steps ahead of the MMAs: no shared-memory ring, no cp.async, nothing to fill before the
+// first MMA.  On the 50 MB decode projections (a dozen k-steps per warp) that start-up matters more
+// than the deeper prefetch of the warp rings; on long streams the rings win.
+constexpr int kRegThreads = 512;
+
+template <int MODE>
+__global__ void __launch_bounds__(kRegThreads, 1) SkinnyGemmRegKernel(const GemmParams p) {
+  using G = Geom<MODE>;
+  constexpr int NM = G::kMmas;
+  constexpr int D = MODE == kBf16 ? 4 : 3;  // k-steps in flight per warp (16 registers each)
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ SharedScratch sh;
+
+  if (p.trigger == 1) GridLaunchDependents();
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int wn = warp % p.wn, wk = warp / p.wn;
+  const Tile tl = LocateTile(p);
+  const Segment& sg = p.seg[tl.seg];
+  const long long pitch = sg.pitch;
+
+  // this thread's columns and this warp's k-steps (local step s is k-step wk + s * p.wk of the slice)
+  const int cols_per_warp = 8 * G::kColsPerThread;
+  const int colbase = tl.n0 + wn * cols_per_warp + g * G::kColsPerThread;
+  const bool warp_has_cols = tl.n0 + wn * cols_per_warp < tl.n1;
+  // threads past the tile's last column load nothing; their pointer is parked on the tile's first chunk
+  const bool cvalid = colbase < tl.n1;
+  const int colload = cvalid ? colbase : tl.n0;
+  const int ksteps = (tl.kslice + 15) >> 4;
+  const int nsteps = ksteps > wk ? (ksteps - wk + p.wk - 1) / p.wk : 0;
+  // only the last k-step of the slice can be partial (K not a multiple of 16)
+  const bool tail_here = (tl.kslice & 15) != 0 && ((ksteps - 1) % p.wk) == wk;
+  const long long col_byte = (MODE == kBf16) ? static_cast<long long>(colload) * 2 : (MODE == kFp8) ? colload : colload / 2;
+  // a thread owns rows 4t .. 4t+3 of a k-step (the k index of an MMA is a free permutation)
+  const uint8_t* wq = sg.w + static_cast<long long>(tl.kbeg + wk * 16 + 4 * t) * pitch + col_byte;  // next step to load
+  const long long scale_delta = static_cast<long long>(sg.n >> 1) + (colload >> 4) - col_byte;
+  const long long step_stride = static_cast<long long>(p.wk) * 16 * pitch;
+  const long long pitch2 = 2 * pitch, pitch3 = 3 * pitch;
+
+  // loads local step s (steps are loaded in increasing order, so a running pointer suffices)
+  auto load_step = [&](Raw<MODE>& raw, int s) {
+    const uint8_t* q0 = wq;
+    wq += step_stride;
+    if (tail_here && s == nsteps - 1) {
+      const int r = tl.kbeg + (wk + s * p.wk) * 16 + 4 * t;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool ok = cvalid && r + i < tl.kend;
+        if constexpr (MODE == kNvfp4) {
+          raw.r[i] = ok ? Ldg64(q0 + i * pitch) : make_uint2(0, 0);
+          raw.s[i] = ok ? Ldg8(q0 + i * pitch + scale_delta) : 0u;
+        } else {
+          raw.r[i] = ok ? Ldg128(q0 + i * pitch) : make_uint4(0, 0, 0, 0);
+        }
+      }
+      return;
+    }
+    const uint8_t* q1 = q0 + pitch;
+    const uint8_t* q2 = q0 + pitch2;
+    const uint8_t* q3 = q0 + pitch3;
+    if (!cvalid) {  // columns past the tile: nothing to stream, the sums are never stored
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if constexpr (MODE == kNvfp4) {
+          raw.r[i] = make_uint2(0, 0);
+          raw.s[i] = 0u;
+        } else {
+          raw.r[i] = make_uint4(0, 0, 0, 0);
+        }
+      }
+      return;
+    }
+    if constexpr (MODE == kNvfp4) {
+      raw.r[0] = Ldg64(q0);
+      raw.r[1] = Ldg64(q1);
+      raw.r[2] = Ldg64(q2);
+      raw.r[3] = Ldg64(q3);
+      raw.s[0] = Ldg8(q0 + scale_delta);
+      raw.s[1] = Ldg8(q1 + scale_delta);
+      raw.s[2] = Ldg8(q2 + scale_delta);
+      raw.s[3] = Ldg8(q3 + scale_delta);
+    } else {
+      raw.r[0] = Ldg128(q0);
+      raw.r[1] = Ldg128(q1);
+      raw.r[2] = Ldg128(q2);
+      raw.r[3] = Ldg128(q3);
+    }
+  };
+
+  // weights do not depend on the predecessor kernel: get the first k-steps in flight, then wait
+  Raw<MODE> buf[D];
+#pragma unroll
+  for (int d = 0; d < D; ++d) {
+    if (warp_has_cols && d < nsteps) load_step(buf[d], d);
+  }
+  if (p.pdl_wait) GridDependencyWait();
+
+  uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
+  const bool slow = StageX<MODE>(p, tl, xs, sh);
+
+  float acc[NM][4];
+#pragma unroll
+  for (int j = 0; j < NM; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+
+  const uint32_t xs_addr = SmemAddr(xs) + static_cast<uint32_t>((g * p.xpitch + 4 * t) * 2);
+  const bool has_row = g < p.M;
+  if (warp_has_cols) {
+    for (int base = 0; base < nsteps; base += D) {
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        const int s = base + d;
+        if (s < nsteps) {
+          uint32_t b0 = 0, b1 = 0;
+          if (has_row) {
+            const uint2 xv = Lds64(xs_addr + static_cast<uint32_t>(wk + s * p.wk) * 32u);
+            b0 = xv.x;
+            b1 = xv.y;
+          }
+          if constexpr (MODE == kBf16) {
+            ComputeStep<MODE, false>(acc, buf[d], b0, b1);
+          } else {
+            if (slow) {
+              ComputeStep<MODE, true>(acc, buf[d], b0, b1);
+            } else {
+              ComputeStep<MODE, false>(acc, buf[d], b0, b1);
+            }
+          }
+          if (s + D < nsteps) load_step(buf[d], s + D);
+        }
+      }
+    }
+  }
+  if (p.trigger == 2) GridLaunchDependents();
+  __syncthreads();
+  Epilogue<MODE>(p, tl, acc, smem, sh, warp_has_cols);
+}
+
 // ------------------------------------------------------------------------------ tcgen05 kernel
 // NVFP4 only.  The warp rings, the dequantisation and the epilogue are those of the direct kernel;
 // the MMAs move from the legacy mma.sync pipe (measured: busy 62 % of all cycles and the first
@@ -1681,6 +1822,9 @@ cudaError_t LaunchMode(const GemmParams& p, const Plan& plan, size_t smem, cudaS
   }
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
+  if constexpr (MODE != kNvfp4) {
+    if (plan.direct == 2) return cudaLaunchKernelEx(&cfg, SkinnyGemmRegKernel<MODE>, p);
+  }
   if (plan.direct) {
     if constexpr (MODE == kNvfp4) {
       if (plan.tc) {
@@ -1721,8 +1865,16 @@ int QueryMaxActiveClusters(int mode, int direct, int threads, size_t smem, int c
   if (it != cache.end()) return it->second;
   const void* fn = nullptr;
   switch (mode) {
-    case kBf16: fn = direct ? (const void*)SkinnyGemmDirectKernel<kBf16, 4, 1> : (const void*)SkinnyGemmRingKernel<kBf16>; break;
-    case kFp8: fn = direct ? (const void*)SkinnyGemmDirectKernel<kFp8, 4, 1> : (const void*)SkinnyGemmRingKernel<kFp8>; break;
+    case kBf16:
+      fn = direct == 4 ? (const void*)SkinnyGemmRegKernel<kBf16>
+           : direct    ? (const void*)SkinnyGemmDirectKernel<kBf16, 4, 1>
+                       : (const void*)SkinnyGemmRingKernel<kBf16>;
+      break;
+    case kFp8:
+      fn = direct == 4 ? (const void*)SkinnyGemmRegKernel<kFp8>
+           : direct    ? (const void*)SkinnyGemmDirectKernel<kFp8, 4, 1>
+                       : (const void*)SkinnyGemmRingKernel<kFp8>;
+      break;
     default:
       fn = direct == 3   ? (const void*)SkinnyGemmTcKernel<4>
            : direct == 2 ? (const void*)SkinnyGemmDirectKernel<kNvfp4, 4, 2>
@@ -1768,6 +1920,8 @@ cudaError_t ConfigureSkinnyGemmKernels() {
     if (status == cudaSuccess) status = ConfigureDirect<kFp8, 1>();
     if (status == cudaSuccess) status = ConfigureDirect<kNvfp4, 1>();
     if (status == cudaSuccess) status = ConfigureDirect<kNvfp4, 2>();
+    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRegKernel<kBf16>);
+    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRegKernel<kFp8>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmTcKernel<3>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmTcKernel<4>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmTcKernel<6>);
@@ -1794,7 +1948,7 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
   const int red_bytes = (plan.wk + (plan.cluster > 1 ? 1 : 0)) * p.M * TNc * 4;
   const int direct_slot = DirectSlotBytes(mode, plan.wide);
   const int ring_warps = plan.tc ? plan.wn * plan.wk + plan.wk : plan.wn * plan.wk;
-  const int ring = plan.direct ? ring_warps * plan.stages * direct_slot : plan.stages * p.stage_bytes;
+  const int ring = plan.direct == 2 ? 0 : plan.direct ? ring_warps * plan.stages * direct_slot : plan.stages * p.stage_bytes;
   p.ring_bytes = (std::max(ring, red_bytes) + 127) & ~127;
   const int ksteps = (p.K + 15) / 16;
   const int kslice_max = ((ksteps + plan.cluster - 1) / plan.cluster) * 16;

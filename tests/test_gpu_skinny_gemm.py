@@ -346,3 +346,14 @@ def test_nvfp4_tensor_memory_kernel_matches_direct_kernel_on_wide_range(cuda):
     xf[:, 1::7] *= 2.0 ** -20
     x = P.f32_to_bf16_bits(xf)
     run_case(rng, 2, 4, K, [[N]], plan="direct=1,tc=1,wide=1,wn=4,wk=2,cluster=1", x_bits=x)
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("plan", [
+    "direct=2,wn=1,wk=16,cluster=1", "direct=2,wn=2,wk=8,cluster=2,ctas=6", "direct=2,wn=4,wk=4,cluster=4",
+    "direct=2,wn=8,wk=2,cluster=8", "direct=2,wn=2,wk=2,cluster=1", "direct=2,wn=4,wk=1,cluster=2,ctas=40"])
+def test_register_streaming_kernel(cuda, mode, plan):
+    """The BF16 / FP8 variant that loads weights straight into registers (no shared-memory ring)."""
+    rng = np.random.default_rng(sum(map(ord, plan)) + mode)
+    run_case(rng, mode, 3, 2304, [[1280, 256], [512]], with_scale=True, plan=plan)
+    run_case(rng, mode, 8, 1000, [[640], [128, 128]], with_scale=True, plan=plan)
