@@ -403,11 +403,15 @@ def run_ours(args):
                      "kernel_us": round(us_kernel, 2), "algorithmic_bytes": shard_bytes},
         "e2e": {"value": round(total_bytes / us_e2e / 1e6, 4), "unit": UNIT, "h2d_bytes_per_step": x.numel() * 2,
                 "d2h_bytes_per_step": m * 12, "us_per_step": round(us_e2e, 2)},
-        "gpu_launches": args.steps * (1 if world == 1 else 2),
+        "gpu_launches": args.steps * (1 if (world == 1 or head.peer is not None) else 2),
         "clocks": clocks,
     }
     if verified is not None:
         line["verified"] = verified
+        line["config"]["exchange"] = ("keys stored into the peers' memory by the fused kernel (no collective launch)"
+                                      if head.peer is not None else "NCCL all-gather + fold kernel")
+        if head.peer is not None and head.peer.status() != 0:
+            raise SystemExit("a wait for a peer's keys ran out during the run")
     if world == 1 and not args.skip_cpu:
         line["cpu_baseline"] = cpu_baseline(m, k, n_total, reps=40)
     if world == 1 and not args.headline_only:
@@ -472,7 +476,7 @@ def describe_plan(head, k, shard):
 
     n = shard.shape[1] * 16 // 9
     align = 16 if (shard.data_ptr() % 16 == 0 and shard.shape[1] % 16 == 0) else 8 if shard.shape[1] % 8 == 0 else 4
-    p = _lib.plan_describe(_lib.QFG_UINT8, k, [n], align)
+    p = _lib.plan_describe(_lib.QFG_UINT8, k, [n], align, spec="lmhead")
     return ",".join(f"{a}={b}" for a, b in p.items() if a != "seg_tiles")
 
 

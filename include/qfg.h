@@ -180,6 +180,38 @@ QFG_API int qfg_lmhead_compute_static(const qfg_lmhead* op, const void* x, int64
 QFG_API int qfg_lmhead_set_option(qfg_lmhead* op, const char* key, const char* value);
 QFG_API void qfg_lmhead_destroy(qfg_lmhead* op);
 
+/* The N-sharded LM head without a separate collective: every rank runs qfg_lmhead_compute_sharded on
+ * its own columns; the last CTA of each rank stores its per-row keys straight into every rank's
+ * exchange buffer (peer memory over NVLink), waits - bounded - until the keys of all ranks have
+ * arrived in its own buffer, folds them and writes the same idx / val on every rank.  No counterpart
+ * in the reference (single GPU).
+ *
+ * An exchange buffer is qfg_lmhead_exchange_bytes() bytes of zero-initialised device memory per rank that
+ * every other rank can address (qfg_peer_alloc / qfg_peer_open below, or any peer-mapped memory).
+ * `peers[r]` is this process's address of rank r's buffer, `peers[rank]` its own.  All ranks must make
+ * the same sequence of calls.  If a peer's keys do not arrive within the wait limit the call still
+ * returns (the result then lacks that peer) and qfg_lmhead_exchange_status reports 1. */
+#define QFG_MAX_RANKS 8
+typedef struct qfg_lmhead_exchange {
+  int world;
+  int rank;
+  void* peers[QFG_MAX_RANKS];
+} qfg_lmhead_exchange;
+QFG_API size_t qfg_lmhead_exchange_bytes(void);
+QFG_API int qfg_lmhead_compute_sharded(const qfg_lmhead* op, const void* x, int64_t m, int64_t k,
+                                       const qfg_tensor2d* weight, int64_t n, int64_t col_offset, void* workspace,
+                                       const qfg_lmhead_exchange* exchange, int64_t* idx, float* val, void* logits,
+                                       void* stream);
+/* 0 = every wait so far completed, 1 = a wait ran out.  Synchronises the device. */
+QFG_API int qfg_lmhead_exchange_status(const void* own_buffer, int* status);
+/* Device memory that other processes on the node can map (cudaMalloc + cudaIpcGetMemHandle; `handle`
+ * receives 64 bytes), the mapping of another process's handle (peer access enabled lazily), and their
+ * releases.  Set-up calls: they allocate and synchronise. */
+QFG_API int qfg_peer_alloc(size_t bytes, void** ptr, unsigned char handle[64]);
+QFG_API int qfg_peer_open(const unsigned char handle[64], void** ptr);
+QFG_API int qfg_peer_close(void* ptr);
+QFG_API int qfg_peer_free(void* ptr);
+
 /* Fold `ranks` gathered key rows (keys[rank * m + row]) into idx[row] / val[row]. */
 QFG_API int qfg_lmhead_combine(const uint64_t* keys, int ranks, int64_t m, int64_t* idx, float* val, void* stream);
 

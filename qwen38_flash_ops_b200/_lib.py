@@ -25,7 +25,13 @@ EXPORTS = (
     "qfg_lmhead_workspace_bytes", "qfg_lmhead_create", "qfg_lmhead_compute", "qfg_lmhead_static_max_rows",
     "qfg_lmhead_compute_static", "qfg_lmhead_set_option",
     "qfg_lmhead_destroy", "qfg_lmhead_combine",
+    "qfg_lmhead_exchange_bytes", "qfg_lmhead_compute_sharded", "qfg_lmhead_exchange_status",
+    "qfg_peer_alloc", "qfg_peer_open", "qfg_peer_close", "qfg_peer_free",
 )
+
+
+class LmExchange(ctypes.Structure):
+    _fields_ = [("world", c_int), ("rank", c_int), ("peers", c_void_p * 8)]
 
 
 class Tensor2D(ctypes.Structure):
@@ -75,6 +81,14 @@ def load() -> ctypes.CDLL:
     lib.qfg_lmhead_static_max_rows.restype = c_size_t
     lib.qfg_lmhead_compute_static.argtypes = [c_void_p, c_void_p, c_int64, c_int64, POINTER(Tensor2D), c_int64, c_int64,
                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.qfg_lmhead_exchange_bytes.restype = c_size_t
+    lib.qfg_lmhead_compute_sharded.argtypes = [c_void_p, c_void_p, c_int64, c_int64, POINTER(Tensor2D), c_int64, c_int64,
+                                               c_void_p, POINTER(LmExchange), c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.qfg_lmhead_exchange_status.argtypes = [c_void_p, POINTER(c_int)]
+    lib.qfg_peer_alloc.argtypes = [c_size_t, POINTER(c_void_p), ctypes.c_char_p]
+    lib.qfg_peer_open.argtypes = [ctypes.c_char_p, POINTER(c_void_p)]
+    lib.qfg_peer_close.argtypes = [c_void_p]
+    lib.qfg_peer_free.argtypes = [c_void_p]
     lib.qfg_lmhead_set_option.argtypes = [c_void_p, c_char_p, c_char_p]
     lib.qfg_lmhead_destroy.argtypes = [c_void_p]
     lib.qfg_lmhead_destroy.restype = None

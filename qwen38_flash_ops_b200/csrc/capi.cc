@@ -309,7 +309,7 @@ int SetLastError(int code, const char* message) { return Fail(code, message); }
 // The fused LM head on a caller-chosen scratch area (see qfg_lmhead_compute).
 int LmheadComputeWithWorkspace(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
                        int64_t n, int64_t col_offset, void* workspace, size_t workspace_bytes, int64_t* idx, float* val,
-                       uint64_t* key, void* logits, void* stream) {
+                       uint64_t* key, void* logits, void* stream, const qfg_lmhead_exchange* exchange) {
   if (op == nullptr || weight == nullptr) return Fail(QFG_FAIL, "LmHead: null argument");
   try {
     if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 8 != 0)
@@ -338,6 +338,17 @@ int LmheadComputeWithWorkspace(const qfg_lmhead* op, const void* x, int64_t m, i
     pr.params.lm_val = val;
     pr.params.lm_key_out = reinterpret_cast<unsigned long long*>(key);
     pr.params.lm_col_offset = col_offset;
+    if (exchange != nullptr && exchange->world > 1) {
+      if (exchange->world > QFG_MAX_RANKS || exchange->rank < 0 || exchange->rank >= exchange->world)
+        throw InvalidArgument("LmHead: bad exchange (1 <= world <= 8, 0 <= rank < world)");
+      pr.params.xworld = exchange->world;
+      pr.params.xrank = exchange->rank;
+      for (int r = 0; r < exchange->world; ++r) {
+        if (exchange->peers[r] == nullptr || reinterpret_cast<uintptr_t>(exchange->peers[r]) % 8 != 0)
+          throw InvalidArgument("LmHead: exchange buffers must be 8-byte aligned device pointers");
+        pr.params.xpeer[r] = static_cast<qfg::LmExchange*>(exchange->peers[r]);
+      }
+    }
     Run(call, pr, m, static_cast<cudaStream_t>(stream), "LmHead");
     return QFG_OK;
   } catch (const InvalidArgument& e) {
@@ -421,9 +432,17 @@ int qfg_plan_describe(int dtype, int64_t k, const int64_t* n, int nseg, int row_
   }
   in.row_align = row_align;
   in.sm_count = sm_count;
+  // a spec that starts with "lmhead" (optionally followed by ",key=value...") describes the fused LM head,
+  // whose workspace allows the shared tail
+  std::string overrides = spec != nullptr ? spec : "";
+  if (overrides.rfind("lmhead", 0) == 0) {
+    in.allow_tail = true;
+    overrides = overrides.size() > 7 ? overrides.substr(7) : "";
+  }
   qfg::Plan plan = qfg::ChoosePlan(in);
-  if (spec != nullptr && spec[0] != 0 && !qfg::ApplyPlanOverrides(spec, in, &plan))
+  if (!overrides.empty() && !qfg::ApplyPlanOverrides(overrides, in, &plan))
     return Fail(QFG_INVALID_ARGUMENT, "plan_describe: bad plan override");
+  qfg::ChooseTail(in, overrides.find("tail=") != std::string::npos, &plan);
   std::string d = qfg::DescribePlan(plan, in);
   d += ",seg_tiles=";
   for (int s = 0; s < nseg; ++s) d += (s ? "/" : "") + std::to_string(plan.tiles[s]);
@@ -546,6 +565,62 @@ void qfg_dequant_destroy(qfg_dequant* op) {
   if (op == nullptr) return;
   cudaFree(op->d_w_scale);
   delete op;
+}
+
+size_t qfg_lmhead_exchange_bytes(void) { return (sizeof(qfg::LmExchange) + 255) & ~static_cast<size_t>(255); }
+
+int qfg_lmhead_compute_sharded(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
+                               int64_t n, int64_t col_offset, void* workspace, const qfg_lmhead_exchange* exchange,
+                               int64_t* idx, float* val, void* logits, void* stream) {
+  if (exchange == nullptr) return Fail(QFG_INVALID_ARGUMENT, "LmHead: null exchange");
+  return qfg::LmheadComputeWithWorkspace(op, x, m, k, weight, n, col_offset, workspace, qfg_lmhead_workspace_bytes(), idx, val,
+                                         nullptr, logits, stream, exchange);
+}
+
+int qfg_lmhead_exchange_status(const void* own_buffer, int* status) {
+  if (own_buffer == nullptr || status == nullptr) return Fail(QFG_INVALID_ARGUMENT, "LmHead: null argument");
+  unsigned int s = 0;
+  const cudaError_t err = cudaMemcpy(&s, &static_cast<const qfg::LmExchange*>(own_buffer)->status, sizeof(s), cudaMemcpyDeviceToHost);
+  if (err != cudaSuccess) return Fail(QFG_FAIL, (std::string("LmHead: ") + cudaGetErrorString(err)).c_str());
+  *status = static_cast<int>(s);
+  return QFG_OK;
+}
+
+int qfg_peer_alloc(size_t bytes, void** ptr, unsigned char handle[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  if (ptr == nullptr || handle == nullptr || bytes == 0) return Fail(QFG_INVALID_ARGUMENT, "peer_alloc: bad argument");
+  void* p = nullptr;
+  cudaError_t err = cudaMalloc(&p, bytes);
+  if (err == cudaSuccess) err = cudaMemset(p, 0, bytes);
+  cudaIpcMemHandle_t h;
+  if (err == cudaSuccess) err = cudaIpcGetMemHandle(&h, p);
+  if (err == cudaSuccess) err = cudaDeviceSynchronize();
+  if (err != cudaSuccess) {
+    if (p != nullptr) cudaFree(p);
+    return Fail(QFG_FAIL, (std::string("peer_alloc: ") + cudaGetErrorString(err)).c_str());
+  }
+  std::memcpy(handle, &h, 64);
+  *ptr = p;
+  return QFG_OK;
+}
+
+int qfg_peer_open(const unsigned char handle[64], void** ptr) {
+  if (ptr == nullptr || handle == nullptr) return Fail(QFG_INVALID_ARGUMENT, "peer_open: bad argument");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  const cudaError_t err = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (err != cudaSuccess) return Fail(QFG_FAIL, (std::string("peer_open: ") + cudaGetErrorString(err)).c_str());
+  return QFG_OK;
+}
+
+int qfg_peer_close(void* ptr) {
+  const cudaError_t err = cudaIpcCloseMemHandle(ptr);
+  return err == cudaSuccess ? QFG_OK : Fail(QFG_FAIL, (std::string("peer_close: ") + cudaGetErrorString(err)).c_str());
+}
+
+int qfg_peer_free(void* ptr) {
+  const cudaError_t err = cudaFree(ptr);
+  return err == cudaSuccess ? QFG_OK : Fail(QFG_FAIL, (std::string("peer_free: ") + cudaGetErrorString(err)).c_str());
 }
 
 size_t qfg_lmhead_workspace_bytes(void) { return qfg::kLmHeaderBytes + qfg::kLmTailBytes; }

@@ -122,7 +122,22 @@ struct GemmParams {
   int tail_groups = 0;
   int tail_split = 1;
   float* lm_tail = nullptr;
+
+  // Key exchange of the N-sharded LM head through peer memory (world > 1): xpeer[r] is rank r's buffer.
+  int xworld = 1;
+  int xrank = 0;
+  struct LmExchange* xpeer[8] = {};
 };
+
+// One rank's exchange buffer.  Slots alternate with the parity of the call count, so a rank that is one
+// call ahead never overwrites keys a slower rank has not read yet.
+struct LmExchange {
+  unsigned long long keys[2][8][kMaxRows];  // [parity][source rank][row]
+  unsigned int flags[2][8];                 // [parity][source rank] = call count of the writer
+  unsigned int epoch;                       // calls made by the owner
+  unsigned int status;                      // 1 after a wait that ran out
+};
+constexpr int kExchangeSpin = 1 << 22;
 
 constexpr int kMaxTailGroups = 8;
 constexpr int kMaxTailSplit = 8;
@@ -168,7 +183,8 @@ cudaError_t LaunchLmheadCombine(const uint64_t* keys, int ranks, int64_t m, int6
 // capi.cc
 int LmheadComputeWithWorkspace(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
                                int64_t n, int64_t col_offset, void* workspace, size_t workspace_bytes, int64_t* idx,
-                               float* val, uint64_t* key, void* logits, void* stream);
+                               float* val, uint64_t* key, void* logits, void* stream,
+                               const qfg_lmhead_exchange* exchange = nullptr);
 int SetLastError(int code, const char* message);
 
 // dequant_bf16.cu

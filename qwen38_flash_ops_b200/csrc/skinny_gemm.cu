@@ -629,6 +629,47 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
         }
         fold_into_keys();
       }
+      if (p.xworld > 1) {
+        // Sharded head: this rank's keys go straight into every rank's exchange buffer (peer memory), then
+        // the keys of all ranks are awaited - bounded - in the own buffer and folded; the maximum of the
+        // order-preserving keys is the Better order, so every rank ends with the same winner.
+        LmExchange* own = p.xpeer[p.xrank];
+        const unsigned int epoch = own->epoch + 1;  // every thread reads it before thread 0 advances it below
+        const int par = static_cast<int>(epoch & 1u);
+        __syncthreads();
+        if (tid < M) {
+          const unsigned long long mine = atomicExch(p.lm_keys + tid, 0ull);
+          for (int r = 0; r < p.xworld; ++r)
+            *reinterpret_cast<volatile unsigned long long*>(&p.xpeer[r]->keys[par][p.xrank][tid]) = mine;
+          __threadfence_system();
+        }
+        __syncthreads();
+        if (tid == 0) {
+          own->epoch = epoch;
+          for (int r = 0; r < p.xworld; ++r) *reinterpret_cast<volatile unsigned int*>(&p.xpeer[r]->flags[par][p.xrank]) = epoch;
+        }
+        if (tid < p.xworld) {
+          const volatile unsigned int* flag = &own->flags[par][tid];
+          int spin = 0;
+          while (*flag != epoch && spin < kExchangeSpin) {
+            ++spin;
+            __nanosleep(64);
+          }
+          if (*flag != epoch) own->status = 1;
+          __threadfence_system();
+        }
+        __syncthreads();
+        if (tid < M) {
+          unsigned long long best = 0ull;
+          for (int r = 0; r < p.xworld; ++r) {
+            const bool arrived = *reinterpret_cast<const volatile unsigned int*>(&own->flags[par][r]) == epoch;
+            const unsigned long long k = *reinterpret_cast<const volatile unsigned long long*>(&own->keys[par][r][tid]);
+            if (arrived && k > best) best = k;
+          }
+          p.lm_keys[tid] = best;  // decoded and cleared right below
+        }
+        __syncthreads();
+      }
       if (tid < M) {
         const unsigned long long key = atomicExch(p.lm_keys + tid, 0ull);
         const uint32_t ord = static_cast<uint32_t>(key >> 32);

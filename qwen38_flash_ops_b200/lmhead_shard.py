@@ -4,8 +4,9 @@ Every rank holds its own re-packed NVFP4 shard `[K, 9 * N_r / 16]` (a column sha
 contiguous slice of the packed tensor, see packing.nvfp4_column_slice) and the replicated
 activations.  One step is: the fused SkinnyGemm + ArgmaxRows kernel over the local columns,
 which emits per row a 64-bit key ordering (value, global index) pairs exactly like ArgmaxRows;
-one all-gather of those keys (8 bytes per row per rank, over NCCL / NVLink on GPUs); a fold of
-the gathered keys.  Larger key = better pair: larger value, then lower index; NaN above all.
+the exchange of those keys (8 bytes per row per rank) - on GPUs inside the fused kernel, whose last
+CTA stores them into every rank's peer-mapped buffer and folds what arrives, else one all-gather
+followed by a fold kernel.  Larger key = better pair: larger value, then lower index; NaN above all.
 
 The reference has no distributed code; this is the sharding BASELINE's LM-head case asks for.
 """
@@ -42,6 +43,57 @@ def fold_keys_host(keys: np.ndarray):
     return idx, val
 
 
+class PeerExchange:
+    """This rank's exchange buffer and its mappings of the other ranks' buffers (CUDA IPC handles passed
+    around with torch.distributed).  Set-up allocates and synchronises; steps do neither."""
+
+    def __init__(self, group=None):
+        import ctypes
+
+        import torch.distributed as dist
+
+        from . import _lib
+
+        lib = _lib.load()
+        self._lib = lib
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.own = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        _lib.check(lib.qfg_peer_alloc(lib.qfg_lmhead_exchange_bytes(), ctypes.byref(self.own), handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self.struct = _lib.LmExchange()
+        self.struct.world, self.struct.rank = self.world, self.rank
+        self._opened = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.struct.peers[r] = self.own.value
+            else:
+                ptr = ctypes.c_void_p()
+                _lib.check(lib.qfg_peer_open(ctypes.create_string_buffer(h, 64), ctypes.byref(ptr)))
+                self._opened.append(ptr)
+                self.struct.peers[r] = ptr.value
+        dist.barrier(group=group)  # nobody steps before every mapping exists
+
+    def status(self) -> int:
+        import ctypes
+
+        from . import _lib
+
+        s = ctypes.c_int(0)
+        _lib.check(self._lib.qfg_lmhead_exchange_status(self.own, ctypes.byref(s)))
+        return s.value
+
+    def close(self):
+        for ptr in self._opened:
+            self._lib.qfg_peer_close(ptr)
+        self._opened = []
+        if self.own:
+            self._lib.qfg_peer_free(self.own)
+            self.own = None
+
+
 class ShardedLmHead:
     """One rank of the N-sharded LM head.
 
@@ -50,7 +102,7 @@ class ShardedLmHead:
     for CUDA tensors); with world size 1 no collective is issued.
     """
 
-    def __init__(self, shard, n_local: int, col_begin: int, group=None, w_scale=None):
+    def __init__(self, shard, n_local: int, col_begin: int, group=None, w_scale=None, exchange: str = "auto"):
         import torch
         import torch.distributed as dist
 
@@ -65,6 +117,23 @@ class ShardedLmHead:
         self._torch = torch
         self._dist = dist
         self._gathered = None
+        # "peer": keys exchanged inside the fused kernel through peer memory; "nccl": all-gather + fold kernel;
+        # "auto": peer memory on CUDA when the mappings can be set up, else NCCL
+        self.peer = None
+        if self.world > 1 and exchange in ("auto", "peer") and shard.is_cuda:
+            try:
+                self.peer = PeerExchange(group)
+            except Exception:
+                if exchange == "peer":
+                    raise
+                self.peer = None
+            # every rank must take the same path
+            ok = torch.tensor([1 if self.peer is not None else 0], device=shard.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 0:
+                if self.peer is not None:
+                    self.peer.close()
+                self.peer = None
 
     @staticmethod
     def column_range(n_total: int, rank: int, world: int, granule: int = 128):
@@ -76,6 +145,8 @@ class ShardedLmHead:
         from .ops import lmhead_combine
 
         torch = self._torch
+        if self.peer is not None:
+            return self.head.call_sharded(x, self.shard, self.n_local, self.col_begin, self.peer.struct)
         idx, val, key = self.head(x, self.shard, self.n_local, col_offset=self.col_begin)
         if self.world == 1:
             return idx, val

@@ -198,6 +198,22 @@ class LmHeadArgmax:
                                            lg.data_ptr() if logits else None, _stream_ptr()))
         return (idx, val, key, lg) if logits else (idx, val, key)
 
+    def call_sharded(self, x: torch.Tensor, w: torch.Tensor, n: int, col_offset: int, exchange, out=None):
+        """qfg_lmhead_compute_sharded: this rank's columns, keys exchanged through the peers' memory inside
+        the kernel; returns the node-wide (idx, val), identical on every rank.  `exchange` is an
+        _lib.LmExchange whose buffers the caller set up (see lmhead_shard.PeerExchange)."""
+        _require_cuda(x, "x")
+        k = x.shape[-1]
+        m = x.numel() // k
+        t = _tensor2d(w)
+        if out is None:
+            out = (torch.empty(m, dtype=torch.int64, device=x.device), torch.empty(m, dtype=torch.float32, device=x.device))
+        idx, val = out
+        check(self._lib.qfg_lmhead_compute_sharded(self._h, x.data_ptr(), m, k, ctypes.byref(t), int(n), int(col_offset),
+                                                   self.workspace.data_ptr(), ctypes.byref(exchange), idx.data_ptr(),
+                                                   val.data_ptr(), None, _stream_ptr()))
+        return idx, val
+
     def call_static(self, x: torch.Tensor, w: torch.Tensor, n: int, col_offset: int = 0, out=None):
         """The same computation through qfg_lmhead_compute_static: the scratch is the library's
         built-in array, nothing is taken from this instance's workspace.  `out` must be given by
