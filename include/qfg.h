@@ -66,6 +66,8 @@ typedef struct qfg_tensor2d {
 
 typedef struct qfg_skinny_gemm qfg_skinny_gemm;
 typedef struct qfg_dequant qfg_dequant;
+typedef struct qfg_untile_hc qfg_untile_hc;
+typedef struct qfg_shared_expert_down qfg_shared_expert_down;
 typedef struct qfg_lmhead qfg_lmhead;
 
 /* Message of the last non-OK status returned on the calling thread ("" if none). */
@@ -143,6 +145,35 @@ QFG_API int qfg_dequant_create(int64_t n_cols, int64_t col_offset, const int64_t
 QFG_API int qfg_dequant_compute(const qfg_dequant* op, const qfg_tensor2d* w, void* const* outs, int n_outs,
                         void* stream);
 QFG_API void qfg_dequant_destroy(qfg_dequant* op);
+
+/* ---------------------------------------------------------------- SharedExpertDown
+ * y[m, :] = routed[m, :] + bf16( bf16( swish_mul(g, u)[m, :] @ W ) * bf16( sigmoid( bf16( dot(gx[m, :], gw) ) ) ) )
+ * with swish_mul(g, u) = bf16( bf16( g * bf16(sigmoid(g)) ) * u ), FP32 accumulation in the product and
+ * `w_scale[n]` applied to the FP32 sum before the first rounding.  Replaces
+ * SharedExpertDownKernelState (src/fused_gemm/fused_gemm.cu:595-727; arithmetic:
+ * src/fused_gemm/skinny_gemm.cuh:73-80, 226-240, 302-327, 494-505, src/common/sigmoid_acc.cuh:12-21).
+ * Attributes: optional `w_scale` (per column of the quantised weight), `trigger` as for SkinnyGemm.
+ * g, u: BF16 [m, k]; weight [k, n] BF16 / FP8 E4M3FN, or UINT8 [k, 9n/16] NVFP4; gx: BF16 [m, gk];
+ * gw: BF16 [gk]; routed: BF16 [m, n] (NULL: y is the shared term alone); out: BF16 [m, n].
+ * n % 8 == 0 (NVFP4: n % 64 == 0 as for SkinnyGemm), gk even, any m >= 1 (the reference sends m > 4 to a
+ * dense prefill kernel; here rows are processed eight at a time) and any k (the reference: k <= 1024).
+ * The deferred-merge hook of the reference (QMoESharedExpertBridge, :34-92, :704-718) belongs to an
+ * ORT-internal peer and is not reproduced. */
+QFG_API int qfg_shared_expert_down_create(const float* w_scale, size_t n_w_scale, int trigger,
+                                          qfg_shared_expert_down** out);
+QFG_API int qfg_shared_expert_down_compute(const qfg_shared_expert_down* op, const void* g, const void* u, int64_t m,
+                                           int64_t k, const qfg_tensor2d* weight, const void* gx, int64_t gk,
+                                           const void* gw, const void* routed, int64_t n, void* out, void* stream);
+QFG_API void qfg_shared_expert_down_destroy(qfg_shared_expert_down* op);
+
+/* ---------------------------------------------------------------- UntileHcBf16
+ * Replaces UntileHcBf16KernelState (src/fused_gemm/fused_gemm.cu:1013-1072): attribute `kind`
+ * (0: output [10240, 320], 1: output [320, 10240]) and optional `w_scale` indexed by output column.
+ * The input is the pre-tiled [160, 20480] tensor, BFLOAT16 (pure permutation) or FLOAT8E4M3FN
+ * (dequantised: bf16(float(q) * w_scale[col]), 1 if no scale); any other shape or type is refused. */
+QFG_API int qfg_untile_hc_create(int kind, const float* w_scale, size_t n_w_scale, qfg_untile_hc** out);
+QFG_API int qfg_untile_hc_compute(const qfg_untile_hc* op, const qfg_tensor2d* w, void* out, void* stream);
+QFG_API void qfg_untile_hc_destroy(qfg_untile_hc* op);
 
 /* ---------------------------------------------------------------- fused LM head
  * SkinnyGemm over one weight followed by ArgmaxRows over the BF16-rounded logits, in one

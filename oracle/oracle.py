@@ -264,3 +264,85 @@ def lmhead_argmax(x_bits, mode, w, n, w_scale=None):
     logits = outs[0]
     idx, val = argmax_rows(bf16_to_f32(logits))
     return idx, val, logits, sums[0]
+
+
+# ----------------------------------------------------------------------------- UntileHcBf16
+def untile_hc_bf16(w: np.ndarray, kind: int, fp8: bool, w_scale: np.ndarray | None = None) -> np.ndarray:
+    """UntileHcBf16 (fused_gemm.cu:979-1011): the pre-tiled [160, 20480] tensor (uint16 BF16 bits, or
+    uint8 E4M3FN codes when `fp8`) back to row-major BF16 bits, [10240, 320] (kind 0) or [320, 10240]
+    (kind 1).  The tensor is 204800 groups of 16 consecutive elements and the op permutes groups:
+    kind 0 reads group idx = ((s*20 + j)*10 + i)*128 + r and writes group ((s*10 + i)*128 + r)*20 + j
+    (:985-993); kind 1 reads idx = ((h*10 + i)*32 + r)*4 + c and writes ((i*32 + r)*4 + c)*160 + h
+    (:994-1003).  FP8 is dequantised with the scale of the OUTPUT column (:1008-1010)."""
+    groups = np.asarray(w).reshape(204800, 16)
+    idx = np.arange(204800)
+    if kind == 0:
+        r = idx & 127
+        t1 = idx >> 7
+        i = t1 % 10
+        t2 = t1 // 10
+        j = t2 % 20
+        s = t2 // 20
+        dst = ((s * 10 + i) * 128 + r) * 20 + j
+        shape = (10240, 320)
+    else:
+        c = idx & 3
+        t1 = idx >> 2
+        r = t1 & 31
+        t2 = t1 >> 5
+        i = t2 % 10
+        h = t2 // 10
+        dst = ((i * 32 + r) * 4 + c) * 160 + h
+        shape = (320, 10240)
+    out_groups = np.empty_like(groups)
+    out_groups[dst] = groups
+    out = out_groups.reshape(shape)
+    if not fp8:
+        return out.astype(np.uint16)
+    s = np.ones(shape[1], np.float32) if w_scale is None else np.asarray(w_scale, np.float32)[:shape[1]]
+    with np.errstate(invalid="ignore", over="ignore"):
+        return f32_to_bf16(E4M3[out.astype(np.uint8)] * s[None, :])
+
+
+# ----------------------------------------------------------------------------- SharedExpertDown
+def _round_bf16(v: np.ndarray) -> np.ndarray:
+    """FP32 -> BF16 (RN) -> FP32: `Round` of skinny_gemm.cuh:73."""
+    return bf16_to_f32(f32_to_bf16(np.asarray(v, np.float32)))
+
+
+def sigmoid_bf16(a: np.ndarray) -> np.ndarray:
+    """SigmoidBf16 of src/common/sigmoid_acc.cuh:12-18: e = exp(-|a|), 1/(1+e) for a > 0 else e/(1+e), in
+    FP32, rounded once to BF16.  Evaluated in float64 here and rounded to FP32 first, which agrees with the
+    device's expf except where the FP32 result sits on a BF16 rounding boundary."""
+    a64 = np.asarray(a, np.float32).astype(np.float64)
+    e = np.exp(-np.abs(a64))
+    s = np.where(a64 > 0, 1.0 / (1.0 + e), e / (1.0 + e))
+    return _round_bf16(s.astype(np.float32))
+
+
+def swish_mul(g_bits: np.ndarray, u_bits: np.ndarray) -> np.ndarray:
+    """SwishMulValue (skinny_gemm.cuh:77-80): bf16( bf16( g * bf16(sigmoid(g)) ) * u ), as BF16 bits."""
+    g = bf16_to_f32(g_bits)
+    u = bf16_to_f32(u_bits)
+    swish = _round_bf16(g * sigmoid_bf16(g))
+    return f32_to_bf16(swish * u)
+
+
+def shared_expert_down(g_bits, u_bits, mode, w, n, gx_bits, gw_bits, routed_bits=None, w_scale=None):
+    """SharedExpertDown (fused_gemm.cu:595; skinny_gemm.cuh:226-240, 302-327, 494-505):
+    y = routed + bf16( bf16( swish_mul(g, u) @ W [* w_scale] ) * gate ),  gate = bf16(sigmoid(bf16(gx . gw))).
+    The matrix product and the gate dot product are accumulated in float64 here (FP32 on the device, in
+    kernel-dependent orders).  Returns (y bits, x' bits, gate, shared term before the routed add)."""
+    x_bits = swish_mul(g_bits, u_bits)
+    wf = decode_weights_exact(mode, w, n).astype(np.float64)
+    acc = bf16_to_f32(x_bits).astype(np.float64) @ wf
+    if w_scale is not None and mode != MODE_BF16:
+        acc = acc * np.asarray(w_scale, np.float32)[:n].astype(np.float64)[None, :]
+    logit = (bf16_to_f32(gx_bits).astype(np.float64) * bf16_to_f32(np.asarray(gw_bits).reshape(-1)).astype(np.float64)[None, :]).sum(axis=1)
+    gate = sigmoid_bf16(_round_bf16(logit.astype(np.float32)))
+    shared = _round_bf16(_round_bf16(acc.astype(np.float32)) * gate[:, None])
+    if routed_bits is None:
+        y = f32_to_bf16(shared)
+    else:
+        y = f32_to_bf16(bf16_to_f32(routed_bits) + shared)
+    return y, x_bits, gate, shared

@@ -82,6 +82,51 @@ __attribute__((visibility("default"))) int ref_skinny_gemm(
   return static_cast<int>(err);
 }
 
+// SharedExpertDown of at most four rows with the launch configuration the reference operator uses
+// (src/fused_gemm/fused_gemm.cu:680-689: 512 threads, no cluster, unroll 8, tx = 8 for FP8 and 4 otherwise).
+// Only m = 1, 2 and 4 are instantiated, to keep the build short.
+__attribute__((visibility("default"))) int ref_shared_expert_down(
+    const void* g, const void* u, int m, int k, const void* w, int w_mode, int n, const float* w_scale, const void* gx,
+    int gk, const void* gw, const void* routed, void* out, int trigger, void* stream) {
+  skinny::Params p = {};
+  p.trigger = trigger;
+  p.x = static_cast<const skinny::bf16*>(g);
+  p.x2 = static_cast<const skinny::bf16*>(u);
+  p.K = k;
+  p.nseg = 1;
+  p.n[0] = n;
+  p.w_mode[0] = w_mode;
+  if (w_mode == 0) {
+    p.w[0] = static_cast<const skinny::bf16*>(w);
+  } else {
+    p.w_q[0] = static_cast<const uint8_t*>(w);
+    p.w_scale[0] = w_scale;
+  }
+  p.out_begin[0] = 0;
+  p.out_begin[1] = 1;
+  p.out[0] = static_cast<skinny::bf16*>(out);
+  p.col_begin[0] = 0;
+  p.width[0] = n;
+  p.gx = static_cast<const skinny::bf16*>(gx);
+  p.gw = static_cast<const skinny::bf16*>(gw);
+  p.routed = static_cast<const skinny::bf16*>(routed);
+  p.gk = gk;
+  if (k > skinny::kFuseMaxK) return static_cast<int>(cudaErrorInvalidValue);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t err = cudaErrorInvalidValue;
+  if (w_mode == 1) {
+    if (m == 1) err = skinny::LaunchT<1, 8, 512, 1, 8, true>(p, s);
+    if (m == 2) err = skinny::LaunchT<2, 8, 512, 1, 8, true>(p, s);
+    if (m == 4) err = skinny::LaunchT<4, 8, 512, 1, 8, true>(p, s);
+  } else {
+    if (m == 1) err = skinny::LaunchT<1, 4, 512, 1, 8, true>(p, s);
+    if (m == 2) err = skinny::LaunchT<2, 4, 512, 1, 8, true>(p, s);
+    if (m == 4) err = skinny::LaunchT<4, 4, 512, 1, 8, true>(p, s);
+  }
+  if (err == cudaSuccess) err = cudaGetLastError();
+  return static_cast<int>(err);
+}
+
 // type: 0 = BF16, 1 = FP16, 2 = FP32 (skinny::LogitType).
 __attribute__((visibility("default"))) int ref_argmax_rows(int type, const void* x, long long rows, long long vocab,
                                                            long long* idx, float* val, void* stream) {

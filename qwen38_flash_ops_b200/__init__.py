@@ -8,7 +8,8 @@ from ._lib import QfgError, load  # noqa: F401
 
 def __getattr__(name):
     # the operator classes need torch; import them lazily so packing / loading work without it
-    if name in ("SkinnyGemm", "ArgmaxRows", "DequantWeightBf16", "LmHeadArgmax", "lmhead_combine"):
+    if name in ("SkinnyGemm", "SharedExpertDown", "ArgmaxRows", "DequantWeightBf16", "UntileHcBf16", "LmHeadArgmax",
+                "lmhead_combine"):
         from . import ops
 
         return getattr(ops, name)

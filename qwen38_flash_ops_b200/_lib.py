@@ -22,6 +22,8 @@ EXPORTS = (
     "qfg_skinny_gemm_describe", "qfg_plan_describe", "qfg_skinny_gemm_destroy",
     "qfg_argmax_rows",
     "qfg_dequant_create", "qfg_dequant_compute", "qfg_dequant_destroy",
+    "qfg_untile_hc_create", "qfg_untile_hc_compute", "qfg_untile_hc_destroy",
+    "qfg_shared_expert_down_create", "qfg_shared_expert_down_compute", "qfg_shared_expert_down_destroy",
     "qfg_lmhead_workspace_bytes", "qfg_lmhead_create", "qfg_lmhead_compute", "qfg_lmhead_static_max_rows",
     "qfg_lmhead_compute_static", "qfg_lmhead_set_option",
     "qfg_lmhead_destroy", "qfg_lmhead_combine",
@@ -81,6 +83,15 @@ def load() -> ctypes.CDLL:
     lib.qfg_lmhead_static_max_rows.restype = c_size_t
     lib.qfg_lmhead_compute_static.argtypes = [c_void_p, c_void_p, c_int64, c_int64, POINTER(Tensor2D), c_int64, c_int64,
                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.qfg_shared_expert_down_create.argtypes = [POINTER(c_float), c_size_t, c_int, POINTER(c_void_p)]
+    lib.qfg_shared_expert_down_compute.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, POINTER(Tensor2D), c_void_p,
+                                                   c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]
+    lib.qfg_shared_expert_down_destroy.argtypes = [c_void_p]
+    lib.qfg_shared_expert_down_destroy.restype = None
+    lib.qfg_untile_hc_create.argtypes = [c_int, POINTER(c_float), c_size_t, POINTER(c_void_p)]
+    lib.qfg_untile_hc_compute.argtypes = [c_void_p, POINTER(Tensor2D), c_void_p, c_void_p]
+    lib.qfg_untile_hc_destroy.argtypes = [c_void_p]
+    lib.qfg_untile_hc_destroy.restype = None
     lib.qfg_lmhead_exchange_bytes.restype = c_size_t
     lib.qfg_lmhead_compute_sharded.argtypes = [c_void_p, c_void_p, c_int64, c_int64, POINTER(Tensor2D), c_int64, c_int64,
                                                c_void_p, POINTER(LmExchange), c_void_p, c_void_p, c_void_p, c_void_p]

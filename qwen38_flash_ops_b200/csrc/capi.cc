@@ -96,6 +96,16 @@ struct qfg_lmhead {
   qfg_skinny_gemm gemm;
 };
 
+struct qfg_shared_expert_down {
+  qfg_skinny_gemm gemm;
+};
+
+struct qfg_untile_hc {
+  int kind = 0;
+  float* d_w_scale = nullptr;
+  size_t w_scale_len = 0;
+};
+
 namespace {
 
 struct Prepared {
@@ -246,6 +256,11 @@ void Run(const qfg_skinny_gemm& op, Prepared& pr, int64_t m, cudaStream_t stream
     qfg::GemmParams q = base;
     q.M = chunk;
     q.x = base.x + static_cast<size_t>(done) * base.K;
+    if (base.fuse) {
+      q.x2 = base.x2 + static_cast<size_t>(done) * base.K;
+      q.gx = base.gx + static_cast<size_t>(done) * base.gk;
+      if (base.routed != nullptr) q.routed = base.routed + static_cast<size_t>(done) * base.seg[0].n;
+    }
     if (done + chunk < m) q.trigger = 0;
     const int n_out = base.seg[base.nseg - 1].out_end;
     for (int o = 0; o < n_out; ++o) {
@@ -475,6 +490,95 @@ int qfg_argmax_rows(int dtype, const void* x, int64_t rows, int64_t vocab, int64
     if (err != cudaSuccess) return Fail(QFG_FAIL, std::string("ArgmaxRows: ") + cudaGetErrorString(err));
   }
   return QFG_OK;
+}
+
+int qfg_shared_expert_down_create(const float* w_scale, size_t n_w_scale, int trigger, qfg_shared_expert_down** out) {
+  if (out == nullptr) return Fail(QFG_INVALID_ARGUMENT, "SharedExpertDown: null handle pointer");
+  *out = nullptr;
+  qfg_shared_expert_down* op = new qfg_shared_expert_down();
+  const int64_t one = 1;
+  try {
+    InitGemmOp(&op->gemm, &one, 1, &one, 1, w_scale, n_w_scale, trigger, "SharedExpertDown");
+  } catch (const std::exception& e) {
+    delete op;
+    return Fail(QFG_INVALID_ARGUMENT, e.what());
+  }
+  *out = op;
+  return QFG_OK;
+}
+
+int qfg_shared_expert_down_compute(const qfg_shared_expert_down* op, const void* g, const void* u, int64_t m, int64_t k,
+                                   const qfg_tensor2d* weight, const void* gx, int64_t gk, const void* gw,
+                                   const void* routed, int64_t n, void* out, void* stream) {
+  if (op == nullptr || weight == nullptr) return Fail(QFG_FAIL, "SharedExpertDown: null argument");
+  try {
+    if (m < 1 || n < 1 || n > INT_MAX || n % 8 != 0 || gk < 0 || gk > INT_MAX || gk % 2 != 0)
+      throw std::runtime_error("SharedExpertDown: shape mismatch");
+    if (g == nullptr || u == nullptr || gx == nullptr || gw == nullptr || out == nullptr ||
+        reinterpret_cast<uintptr_t>(u) % 4 != 0 || reinterpret_cast<uintptr_t>(gx) % 2 != 0 ||
+        reinterpret_cast<uintptr_t>(gw) % 2 != 0 || reinterpret_cast<uintptr_t>(routed) % 2 != 0) {
+      throw std::runtime_error("SharedExpertDown: null or misaligned input");
+    }
+    void* outs[1] = {out};
+    Prepared pr = Prepare(op->gemm, g, m, k, weight, 1, outs, 1, true, n);
+    pr.params.fuse = 1;
+    pr.params.x2 = static_cast<const uint16_t*>(u);
+    pr.params.gx = static_cast<const uint16_t*>(gx);
+    pr.params.gw = static_cast<const uint16_t*>(gw);
+    pr.params.routed = static_cast<const uint16_t*>(routed);
+    pr.params.gk = static_cast<int>(gk);
+    Run(op->gemm, pr, m, static_cast<cudaStream_t>(stream), "SharedExpertDown");
+    return QFG_OK;
+  } catch (const InvalidArgument& e) {
+    return Fail(QFG_FAIL, e.what());
+  } catch (const std::exception& e) {
+    return Fail(QFG_FAIL, e.what());
+  }
+}
+
+void qfg_shared_expert_down_destroy(qfg_shared_expert_down* op) {
+  if (op == nullptr) return;
+  cudaFree(op->gemm.d_w_scale);
+  delete op;
+}
+
+int qfg_untile_hc_create(int kind, const float* w_scale, size_t n_w_scale, qfg_untile_hc** out) {
+  if (out == nullptr) return Fail(QFG_INVALID_ARGUMENT, "UntileHcBf16: null handle pointer");
+  *out = nullptr;
+  if (kind != 0 && kind != 1) return Fail(QFG_INVALID_ARGUMENT, "UntileHcBf16: kind must be 0 or 1");
+  qfg_untile_hc* op = new qfg_untile_hc();
+  try {
+    op->kind = kind;
+    op->d_w_scale = UploadScales(w_scale, n_w_scale, "UntileHcBf16");
+    op->w_scale_len = op->d_w_scale != nullptr ? n_w_scale : 0;
+  } catch (const std::exception& e) {
+    delete op;
+    return Fail(QFG_INVALID_ARGUMENT, e.what());
+  }
+  *out = op;
+  return QFG_OK;
+}
+
+int qfg_untile_hc_compute(const qfg_untile_hc* op, const qfg_tensor2d* w, void* out, void* stream) {
+  if (op == nullptr || w == nullptr) return Fail(QFG_FAIL, "UntileHcBf16: null argument");
+  if (w->rows != 160 || w->cols != 20480) return Fail(QFG_FAIL, "UntileHcBf16: expected [160, 20480]");
+  if (w->dtype != QFG_BFLOAT16 && w->dtype != QFG_FLOAT8E4M3FN) return Fail(QFG_FAIL, "UntileHcBf16: unsupported input element type");
+  if (w->data == nullptr || out == nullptr || reinterpret_cast<uintptr_t>(w->data) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(out) % 16 != 0) {
+    return Fail(QFG_FAIL, "UntileHcBf16: null or misaligned tensor");
+  }
+  const bool fp8 = w->dtype == QFG_FLOAT8E4M3FN;
+  const size_t need = op->kind == 0 ? 320 : 10240;
+  if (fp8 && op->d_w_scale != nullptr && op->w_scale_len < need) return Fail(QFG_FAIL, "UntileHcBf16: w_scale shorter than the output width");
+  const cudaError_t err = qfg::LaunchUntileHc(fp8, w->data, out, op->d_w_scale, op->kind, static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return Fail(QFG_FAIL, (std::string("UntileHcBf16: ") + cudaGetErrorString(err)).c_str());
+  return QFG_OK;
+}
+
+void qfg_untile_hc_destroy(qfg_untile_hc* op) {
+  if (op == nullptr) return;
+  cudaFree(op->d_w_scale);
+  delete op;
 }
 
 int qfg_dequant_create(int64_t n_cols, int64_t col_offset, const int64_t* widths, int n_widths,

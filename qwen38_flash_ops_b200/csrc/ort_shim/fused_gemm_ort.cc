@@ -5,9 +5,9 @@
 // This is the only translation unit that includes ONNX Runtime headers; it compiles only where
 // ORT_INCLUDE_DIR points at genuine headers (make ORT_INCLUDE_DIR=... in qwen38_flash_ops_b200/csrc).
 //
-// Registered ops: SkinnyGemm, ArgmaxRows, DequantWeightBf16.  The reference library also
-// registers SharedExpertDown and UntileHcBf16; a model that uses those two still needs the
-// reference library for them.
+// Registered ops: SkinnyGemm, SharedExpertDown, ArgmaxRows, DequantWeightBf16, UntileHcBf16 - the five
+// names of the reference library.  SharedExpertDown runs without the reference's deferred-merge hook
+// (QMoESharedExpertBridge, an ORT-internal peer): `routed` is always added by this op.
 #ifndef ORT_API_MANUAL_INIT
 #define ORT_API_MANUAL_INIT
 #endif
@@ -260,6 +260,121 @@ struct DequantWeightBf16Op : Ort::CustomOpBase<DequantWeightBf16Op, DequantWeigh
   }
 };
 
+int64_t ElementCount(const Ort::ConstValue& v) {
+  int64_t n = 1;
+  for (int64_t d : v.GetTensorTypeAndShapeInfo().GetShape()) n *= d;
+  return n;
+}
+
+// Six inputs g, u, w, gx, gw, routed -> one output shaped like routed (src/fused_gemm/fused_gemm.cu:630-727, :799-816).
+struct SharedExpertDownState {
+  const OrtApi& api;
+  qfg_shared_expert_down* op = nullptr;
+
+  SharedExpertDownState(const OrtApi& a, const OrtKernelInfo* info) : api(a) {
+    Ort::ConstKernelInfo k(info);
+    const std::vector<float> w_scale = OptionalAttributes<float>(k, "w_scale");
+    const int trigger = static_cast<int>(OptionalAttribute(k, "trigger", 0));
+    if (qfg_shared_expert_down_create(w_scale.empty() ? nullptr : w_scale.data(), w_scale.size(), trigger, &op) != QFG_OK)
+      throw std::invalid_argument(qfg_last_error());
+  }
+  ~SharedExpertDownState() { qfg_shared_expert_down_destroy(op); }
+
+  OrtStatus* ComputeV2(OrtKernelContext* raw) noexcept {
+    try {
+      Ort::KernelContext c(raw);
+      if (c.GetInputCount() != 6) throw std::invalid_argument("SharedExpertDown: needs 6 inputs");
+      const qfg_tensor2d w = Tensor2d(c.GetInput(2), "SharedExpertDown");
+      const auto routed_shape = c.GetInput(5).GetTensorTypeAndShapeInfo().GetShape();
+      const int64_t K = w.rows, N = routed_shape.empty() ? 0 : routed_shape.back();
+      const int64_t M = K > 0 ? ElementCount(c.GetInput(0)) / K : 0;
+      const int64_t gk = ElementCount(c.GetInput(4));
+      const auto gw_shape = c.GetInput(4).GetTensorTypeAndShapeInfo().GetShape();
+      if (M < 1 || ElementCount(c.GetInput(0)) != M * K || ElementCount(c.GetInput(1)) != M * K ||
+          ElementCount(c.GetInput(5)) != M * N || ElementCount(c.GetInput(3)) != M * gk || gw_shape.empty() ||
+          gw_shape.back() != 1) {
+        throw std::invalid_argument("SharedExpertDown: shape mismatch");
+      }
+      if (w.dtype == QFG_UINT8 ? (N % 16 != 0 || w.cols != N * 9 / 16) : w.cols != N)
+        throw std::invalid_argument("SharedExpertDown: weight N mismatch");
+      auto out = c.GetOutput(0, routed_shape);
+      return ToStatus(api, qfg_shared_expert_down_compute(op, c.GetInput(0).GetTensorRawData(), c.GetInput(1).GetTensorRawData(),
+                                                          M, K, &w, c.GetInput(3).GetTensorRawData(), gk,
+                                                          c.GetInput(4).GetTensorRawData(), c.GetInput(5).GetTensorRawData(), N,
+                                                          out.GetTensorMutableRawData(), ComputeStream(api, raw)));
+    } catch (const std::exception& e) {
+      return api.CreateStatus(ORT_FAIL, e.what());
+    }
+  }
+};
+
+struct SharedExpertDownOp : Ort::CustomOpBase<SharedExpertDownOp, SharedExpertDownState, true> {
+  const char* GetName() const { return "SharedExpertDown"; }
+  const char* GetExecutionProviderType() const { return "CUDAExecutionProvider"; }
+  size_t GetInputTypeCount() const { return 6; }
+  ONNXTensorElementDataType GetInputType(size_t i) const {
+    return i == 2 ? ONNX_TENSOR_ELEMENT_DATA_TYPE_UNDEFINED : ONNX_TENSOR_ELEMENT_DATA_TYPE_BFLOAT16;
+  }
+  size_t GetOutputTypeCount() const { return 1; }
+  ONNXTensorElementDataType GetOutputType(size_t) const { return ONNX_TENSOR_ELEMENT_DATA_TYPE_BFLOAT16; }
+  OrtStatus* CreateKernelV2(const OrtApi& api, const OrtKernelInfo* info, void** kernel) const noexcept {
+    try {
+      *kernel = new SharedExpertDownState(api, info);
+      return nullptr;
+    } catch (const std::exception& e) {
+      return api.CreateStatus(ORT_INVALID_ARGUMENT, e.what());
+    }
+  }
+};
+
+// [160, 20480] -> [10240, 320] (kind 0) or [320, 10240] (kind 1) (src/fused_gemm/fused_gemm.cu:1013-1089).
+struct UntileHcBf16State {
+  const OrtApi& api;
+  qfg_untile_hc* op = nullptr;
+  int kind = 0;
+
+  UntileHcBf16State(const OrtApi& a, const OrtKernelInfo* info) : api(a) {
+    Ort::ConstKernelInfo k(info);
+    kind = static_cast<int>(k.GetAttribute<int64_t>("kind"));
+    const std::vector<float> w_scale = OptionalAttributes<float>(k, "w_scale");
+    if (qfg_untile_hc_create(kind, w_scale.empty() ? nullptr : w_scale.data(), w_scale.size(), &op) != QFG_OK)
+      throw std::invalid_argument(qfg_last_error());
+  }
+  ~UntileHcBf16State() { qfg_untile_hc_destroy(op); }
+
+  OrtStatus* ComputeV2(OrtKernelContext* raw) noexcept {
+    try {
+      Ort::KernelContext c(raw);
+      const qfg_tensor2d w = Tensor2d(c.GetInput(0), "UntileHcBf16");
+      if (w.rows != 160 || w.cols != 20480) throw std::invalid_argument("UntileHcBf16: expected [160, 20480]");
+      auto out = kind == 0 ? c.GetOutput(0, {10240, 320}) : c.GetOutput(0, {320, 10240});
+      return ToStatus(api, qfg_untile_hc_compute(op, &w, out.GetTensorMutableRawData(), ComputeStream(api, raw)));
+    } catch (const std::exception& e) {
+      return api.CreateStatus(ORT_FAIL, e.what());
+    }
+  }
+};
+
+struct UntileHcBf16Op : Ort::CustomOpBase<UntileHcBf16Op, UntileHcBf16State, true> {
+  const char* GetName() const { return "UntileHcBf16"; }
+  const char* GetExecutionProviderType() const { return "CUDAExecutionProvider"; }
+  size_t GetInputTypeCount() const { return 2; }
+  ONNXTensorElementDataType GetInputType(size_t) const { return ONNX_TENSOR_ELEMENT_DATA_TYPE_UNDEFINED; }
+  OrtCustomOpInputOutputCharacteristic GetInputCharacteristic(size_t i) const {
+    return i == 0 ? INPUT_OUTPUT_REQUIRED : INPUT_OUTPUT_OPTIONAL;
+  }
+  size_t GetOutputTypeCount() const { return 1; }
+  ONNXTensorElementDataType GetOutputType(size_t) const { return ONNX_TENSOR_ELEMENT_DATA_TYPE_BFLOAT16; }
+  OrtStatus* CreateKernelV2(const OrtApi& api, const OrtKernelInfo* info, void** kernel) const noexcept {
+    try {
+      *kernel = new UntileHcBf16State(api, info);
+      return nullptr;
+    } catch (const std::exception& e) {
+      return api.CreateStatus(ORT_INVALID_ARGUMENT, e.what());
+    }
+  }
+};
+
 }  // namespace
 
 extern "C" __attribute__((visibility("default"))) OrtStatus* ORT_API_CALL RegisterCustomOps(
@@ -269,14 +384,18 @@ extern "C" __attribute__((visibility("default"))) OrtStatus* ORT_API_CALL Regist
   Ort::InitApi(api);
   try {
     static SkinnyGemmOp skinny_gemm;
+    static SharedExpertDownOp shared_down;
     static ArgmaxRowsOp argmax_rows;
     static DequantWeightBf16Op dequant;
+    static UntileHcBf16Op untile;
     static Ort::CustomOpDomain domain("qwen.fused_gemm");
     static std::once_flag registered;
     std::call_once(registered, [&]() {
       domain.Add(&skinny_gemm);
+      domain.Add(&shared_down);
       domain.Add(&argmax_rows);
       domain.Add(&dequant);
+      domain.Add(&untile);
     });
     Ort::UnownedSessionOptions(options).Add(domain);
     return nullptr;

@@ -123,6 +123,14 @@ struct GemmParams {
   int tail_split = 1;
   float* lm_tail = nullptr;
 
+  // SharedExpertDown (fuse != 0): x is replaced by swish_mul(x, x2) while it is staged, and the output is
+  // routed + bf16(bf16(sum) * gate[m]) with gate[m] = bf16(sigmoid(bf16(dot(gx[m], gw)))).
+  int fuse = 0;
+  const uint16_t* x2 = nullptr;      // BF16 [M, K]
+  const uint16_t* gx = nullptr;      // BF16 [M, gk]
+  const uint16_t* gw = nullptr;      // BF16 [gk]
+  const uint16_t* routed = nullptr;  // BF16 [M, N] or null
+  int gk = 0;
   // Key exchange of the N-sharded LM head through peer memory (world > 1): xpeer[r] is rank r's buffer.
   int xworld = 1;
   int xrank = 0;
@@ -203,5 +211,8 @@ struct DequantParams {
   int aligned = 1;      // vector loads are legal for every row
 };
 cudaError_t LaunchDequant(const DequantParams& p, cudaStream_t stream);
+
+// untile_hc.cu
+cudaError_t LaunchUntileHc(bool fp8, const void* w, void* out, const float* scale, int kind, cudaStream_t stream);
 
 }  // namespace qfg

@@ -322,8 +322,25 @@ struct SharedScratch {
   uint32_t rmin[kMaxRows];  // smallest non-zero BF16 magnitude bits (0x7FFF if the slice is all zero)
   float best_v[kMaxThreads / 32][kMaxRows];
   long long best_i[kMaxThreads / 32][kMaxRows];
+  float gate[kMaxRows];  // SharedExpertDown: the BF16 sigmoid gate of every row (best_v holds its partial sums first)
   int last;
 };
+
+// The BF16 arithmetic of SharedExpertDown (src/common/sigmoid_acc.cuh:12-21, skinny_gemm.cuh:73-80): sigmoid
+// in FP32 from exp(-|a|), rounded once to BF16; Swish = bf16(x * bf16(sigmoid(x))); swish_mul = bf16(Swish(g) * u).
+__device__ __forceinline__ float RoundBf16(float v) { return __bfloat162float(__float2bfloat16(v)); }
+__device__ __forceinline__ float SigmoidBf16(float a) {
+  const float e = expf(-fabsf(a));
+  return RoundBf16(a > 0.0f ? 1.0f / (1.0f + e) : e / (1.0f + e));
+}
+__device__ __forceinline__ uint32_t SwishMulBits(uint32_t g_bits, uint32_t u_bits) {  // one BF16 each, in the low 16 bits
+  const float g = __uint_as_float(g_bits << 16), u = __uint_as_float(u_bits << 16);
+  const float swish = RoundBf16(g * SigmoidBf16(g));
+  return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16(swish * u)));
+}
+__device__ __forceinline__ uint32_t SwishMulWord(uint32_t g2, uint32_t u2) {  // two BF16 per word
+  return SwishMulBits(g2 & 0xFFFFu, u2 & 0xFFFFu) | (SwishMulBits(g2 >> 16, u2 >> 16) << 16);
+}
 
 // max / min-nonzero of the two BF16 magnitudes packed in a word
 __device__ __forceinline__ void TrackWord(uint32_t w, uint32_t& mx, uint32_t& mn) {
@@ -385,6 +402,11 @@ __device__ __forceinline__ bool StageXImpl(const GemmParams& p, const Tile& tl, 
             v[j][0] = q.x, v[j][1] = q.y, v[j][2] = q.z, v[j][3] = q.w;
           } else {
             v[j][0] = __ldg(reinterpret_cast<const uint32_t*>(src));
+          }
+          if (p.fuse) {  // SharedExpertDown: the row of x is swish_mul(g, u)
+            const uint16_t* src2 = p.x2 + static_cast<size_t>(m) * p.K + tl.kbeg + kk;
+#pragma unroll
+            for (int e = 0; e < WORDS; ++e) v[j][e] = SwishMulWord(v[j][e], __ldg(reinterpret_cast<const uint32_t*>(src2) + e));
           }
         }
       }
@@ -479,7 +501,30 @@ __device__ __forceinline__ bool StageX(const GemmParams& p, const Tile& tl, uint
     sh.inv_scale[threadIdx.x] = 1.f;
   }
   __syncthreads();
-  const bool vec8 = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.K % 8 == 0);
+  if (p.fuse) {
+    // gate logit of every row: thread-strided partial sums, warps in order, then bf16 -> sigmoid -> bf16
+    const int tid = threadIdx.x, nthreads = blockDim.x, warp = tid >> 5, lane = tid & 31;
+    for (int m = 0; m < p.M; ++m) {  // one row at a time: a single running sum per thread
+      float part = 0.f;
+      const uint16_t* gxm = p.gx + static_cast<size_t>(m) * p.gk;
+      for (int i = tid; i < p.gk; i += nthreads)
+        part += __uint_as_float(static_cast<uint32_t>(gxm[i]) << 16) * __uint_as_float(static_cast<uint32_t>(p.gw[i]) << 16);
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+      if (lane == 0) sh.best_v[warp][m] = part;
+    }
+    __syncthreads();
+    if (tid < kMaxRows) {
+      float logit = 0.f;
+      if (tid < p.M)
+        for (int w = 0; w < (nthreads >> 5); ++w) logit += sh.best_v[w][tid];
+      sh.gate[tid] = SigmoidBf16(RoundBf16(logit));
+    }
+    __syncthreads();
+  }
+  // swish_mul reads x2 with the same vector width as x
+  const bool vec8 = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.K % 8 == 0) &&
+                    (!p.fuse || reinterpret_cast<uintptr_t>(p.x2) % 16 == 0);
   if (vec8) return StageXImpl<MODE, 4, TC>(p, tl, xs, sh);
   return StageXImpl<MODE, 1, TC>(p, tl, xs, sh);
 }
@@ -508,6 +553,12 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
   auto finalize = [&](int m, int c, float v) {
     const int n = n0 + c;
     if (sg.w_scale != nullptr) v *= sg.w_scale[n];
+    if (p.fuse) {
+      // SharedExpertDown: routed + bf16(bf16(sum) * gate), every step rounded to BF16 (skinny_gemm.cuh:226-240)
+      const float shared = RoundBf16(RoundBf16(v) * sh.gate[m]);
+      v = p.routed != nullptr ? __uint_as_float(static_cast<uint32_t>(p.routed[static_cast<size_t>(m) * sg.n + n]) << 16) + shared
+                              : shared;
+    }
     const __nv_bfloat16 b = __float2bfloat16(v);
     if (!p.lm || p.out[sg.out_begin] != nullptr) {
       int j = sg.out_begin;

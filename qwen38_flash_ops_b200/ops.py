@@ -155,6 +155,84 @@ class DequantWeightBf16:
             self._h = None
 
 
+class SharedExpertDown:
+    """y = routed + bf16(bf16(swish_mul(g, u) @ W) * bf16(sigmoid(bf16(dot(gx, gw))))) per row.
+    Inputs as the reference node: g, u BF16 [..., K]; W [K, N] (BF16 / FP8) or UINT8 [K, 9N/16] (NVFP4);
+    gx BF16 [..., gk]; gw BF16 [gk, 1]; routed BF16 [..., N].  Attributes: optional `w_scale`, `trigger`."""
+
+    def __init__(self, w_scale=None, trigger: int = 0):
+        lib = _lib.load()
+        self._lib = lib
+        self._h = c_void_p()
+        if w_scale is not None and len(w_scale) > 0:
+            keep, ptr = _lib.f32_array(w_scale)
+            n = keep.size
+        else:
+            keep, ptr, n = None, None, 0
+        check(lib.qfg_shared_expert_down_create(ptr, n, int(trigger), ctypes.byref(self._h)))
+
+    def __call__(self, g, u, w, gx, gw, routed):
+        for name, t in (("g", g), ("u", u), ("gx", gx), ("gw", gw), ("routed", routed)):
+            _require_cuda(t, name)
+            if t.dtype != torch.bfloat16:
+                raise QfgError(_lib.QFG_FAIL, f"SharedExpertDown: {name} must be BF16")
+        k = w.shape[0]
+        n = routed.shape[-1]
+        m = g.numel() // k if k > 0 else 0
+        gk = gw.numel()
+        if (m < 1 or g.numel() != m * k or u.numel() != m * k or routed.numel() != m * n or gx.numel() != m * gk
+                or gw.shape[-1] != 1):
+            raise QfgError(_lib.QFG_FAIL, "SharedExpertDown: shape mismatch")
+        t = _tensor2d(w)
+        if w.dtype == torch.uint8:
+            if n % 16 != 0 or w.shape[1] != n * 9 // 16:
+                raise QfgError(_lib.QFG_FAIL, "SharedExpertDown: NVFP4 weight N mismatch")
+        elif w.shape[1] != n:
+            raise QfgError(_lib.QFG_FAIL, "SharedExpertDown: weight N mismatch")
+        out = torch.empty_like(routed)
+        check(self._lib.qfg_shared_expert_down_compute(self._h, g.data_ptr(), u.data_ptr(), m, k, ctypes.byref(t), gx.data_ptr(),
+                                                       gk, gw.data_ptr(), routed.data_ptr(), n, out.data_ptr(), _stream_ptr()))
+        return out
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            self._lib.qfg_shared_expert_down_destroy(h)
+            self._h = None
+
+
+class UntileHcBf16:
+    """The pre-tiled hyper-connection weight [160, 20480] (BF16, or FP8 E4M3FN with a per-output-column
+    `w_scale`) as row-major BF16: [10240, 320] for kind 0, [320, 10240] for kind 1.  The optional second
+    input of the reference op only ties buffer lifetimes and is omitted here."""
+
+    def __init__(self, kind: int, w_scale=None):
+        lib = _lib.load()
+        self._lib = lib
+        self._h = c_void_p()
+        self.kind = int(kind)
+        if w_scale is not None and len(w_scale) > 0:
+            keep, ptr = _lib.f32_array(w_scale)
+            n = keep.size
+        else:
+            keep, ptr, n = None, None, 0
+        check(lib.qfg_untile_hc_create(self.kind, ptr, n, ctypes.byref(self._h)))
+
+    def __call__(self, w: torch.Tensor):
+        _require_cuda(w, "w")
+        t = _tensor2d(w)
+        shape = (10240, 320) if self.kind == 0 else (320, 10240)
+        out = torch.empty(shape, dtype=torch.bfloat16, device=w.device)
+        check(self._lib.qfg_untile_hc_compute(self._h, ctypes.byref(t), out.data_ptr(), _stream_ptr()))
+        return out
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            self._lib.qfg_untile_hc_destroy(h)
+            self._h = None
+
+
 class LmHeadArgmax:
     """SkinnyGemm over one LM-head weight fused with ArgmaxRows over the BF16-rounded logits.
 

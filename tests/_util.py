@@ -62,6 +62,9 @@ def ref_lib():
                                         ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_int), ctypes.POINTER(vp),
                                         ctypes.POINTER(ctypes.c_int), ctypes.c_int, ctypes.c_int, vp]
         lib.ref_argmax_rows.argtypes = [ctypes.c_int, vp, ctypes.c_longlong, ctypes.c_longlong, vp, vp, vp]
+        if hasattr(lib, "ref_shared_expert_down"):
+            ci = ctypes.c_int
+            lib.ref_shared_expert_down.argtypes = [vp, vp, ci, ci, vp, ci, ci, vp, vp, ci, vp, vp, vp, ci, vp]
         _ref = lib
     return _ref
 

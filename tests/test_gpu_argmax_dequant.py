@@ -139,3 +139,44 @@ def test_dequant_errors(cuda):
         op(torch.zeros((8, 128), dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn))  # slice past the row
     with pytest.raises(QfgError):
         op(torch.zeros((8, 256), dtype=torch.float32, device="cuda"))
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+@pytest.mark.parametrize("fp8", [False, True])
+def test_untile_hc_bf16(cuda, kind, fp8):
+    """UntileHcBf16 bit-exact against the oracle; kind 0 also against the construction of the reference's
+    own test (tests/test_load.py:404-423)."""
+    from qwen38_flash_ops_b200 import UntileHcBf16
+
+    g = torch.Generator(device="cuda").manual_seed(5 + kind)
+    cols = 320 if kind == 0 else 10240
+    if not fp8:
+        src = torch.randint(0, 30000, (160, 20480), dtype=torch.int16, device="cuda", generator=g)
+        out = UntileHcBf16(kind)(src.view(torch.bfloat16))
+        expect = O.untile_hc_bf16(src.cpu().numpy().view(np.uint16), kind, False)
+        assert np.array_equal(bits(out), expect)
+        if kind == 0:
+            w_orig = torch.randint(0, 30000, (10240, 320), dtype=torch.int16, device="cuda", generator=g)
+            tiled = w_orig.view(8, 10, 128, 20, 2, 8).permute(0, 3, 1, 2, 4, 5).contiguous().view(160, 20480)
+            assert torch.equal(UntileHcBf16(0)(tiled.view(torch.bfloat16)).view(torch.int16), w_orig)
+    else:
+        codes = torch.randint(0, 256, (160, 20480), dtype=torch.uint8, device="cuda", generator=g)
+        sc = (torch.rand(cols, device="cuda", generator=g) * 0.01 + 1e-4).float()
+        out = UntileHcBf16(kind, w_scale=sc.cpu().numpy())(codes.view(torch.float8_e4m3fn))
+        expect = O.untile_hc_bf16(codes.cpu().numpy(), kind, True, sc.cpu().numpy())
+        got = bits(out)
+        nan = (expect & 0x7FFF) > 0x7F80          # E4M3 NaN codes: any NaN pattern is accepted
+        assert np.array_equal(got[~nan], expect[~nan]) and np.all((got[nan] & 0x7FFF) > 0x7F80)
+        out1 = UntileHcBf16(kind)(codes.view(torch.float8_e4m3fn))     # no scale: factor 1
+        expect1 = O.untile_hc_bf16(codes.cpu().numpy(), kind, True, None)
+        g1 = bits(out1)
+        assert np.array_equal(g1[~nan], expect1[~nan])
+
+
+def test_untile_hc_rejects_other_shapes(cuda):
+    from qwen38_flash_ops_b200 import QfgError, UntileHcBf16
+
+    with pytest.raises(QfgError):
+        UntileHcBf16(0)(torch.zeros((160, 20472), dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(QfgError):
+        UntileHcBf16(2)

@@ -213,3 +213,30 @@ def test_golden_fixtures_from_reference_kernels():
             # and the oracle's own rounding differs from the reference kernel by at most one BF16 ULP
             diff = np.abs(out.astype(np.int32) - z["y"].astype(np.int32))
             assert np.mean(diff <= 1) > 0.999, f
+
+
+def test_untile_hc_matches_the_reference_test_construction():
+    """tests/test_load.py:404-423 of the reference builds the tiled tensor as
+    w.view(8,10,128,20,2,8).permute(0,3,1,2,4,5) and expects UntileHcBf16(kind=0) to return w (BF16,
+    bit-exact) or its dequantisation (FP8).  Kind 1 is pinned by its index formula only."""
+    import torch
+
+    g = torch.Generator().manual_seed(11)
+    w_orig = torch.randint(0, 30000, (10240, 320), dtype=torch.int16, generator=g)
+    tiled = w_orig.view(8, 10, 128, 20, 2, 8).permute(0, 3, 1, 2, 4, 5).contiguous().view(160, 20480)
+    out = O.untile_hc_bf16(tiled.numpy().view(np.uint16), 0, False)
+    assert np.array_equal(out, w_orig.numpy().view(np.uint16))
+
+    wd_f = (torch.randn(10240, 320, generator=g) * 0.03).bfloat16()
+    sc = (wd_f.float().abs().amax(dim=0).clamp(min=1e-8) / 448.0).to(torch.float32)
+    q = (wd_f.float() / sc[None, :]).clamp(-448, 448).to(torch.float8_e4m3fn)
+    deq = (q.float() * sc[None, :]).bfloat16()
+    q_tiled = q.view(torch.uint8).view(8, 10, 128, 20, 2, 8).permute(0, 3, 1, 2, 4, 5).contiguous().view(160, 20480)
+    out8 = O.untile_hc_bf16(q_tiled.numpy(), 0, True, sc.numpy())
+    assert np.array_equal(out8, deq.view(torch.int16).numpy().view(np.uint16))
+
+    # kind 1: out[i*32 + r][(c*160 + h)*16 + e] = in[h][((i*32 + r)*4 + c)*16 + e]
+    src = torch.randint(0, 30000, (160, 20480), dtype=torch.int16, generator=g)
+    out1 = O.untile_hc_bf16(src.numpy().view(np.uint16), 1, False)
+    expect = src.view(160, 320, 4, 16).permute(1, 2, 0, 3).contiguous().view(320, 10240)
+    assert np.array_equal(out1, expect.numpy().view(np.uint16))
