@@ -54,6 +54,33 @@ def main(out_dir):
         np.savez_compressed(os.path.join(out_dir, f"ref_gemm_{tag}.npz"), kind="gemm", mode=mode, n=N, x=x,
                             w=arr.view(np.uint8) if mode != 0 else arr, y=bits(y),
                             w_scale=s if s is not None else np.zeros(0, np.float32))
+    # SharedExpertDown: the reference's fused GEMV (its operator's launch configuration), one case per weight type
+    import ctypes
+
+    lib = U.ref_lib()
+    if hasattr(lib, "ref_shared_expert_down"):
+        for tag, mode, M, K, N, gk, scaled in (("bf16", 0, 1, 256, 128, 64, False), ("fp8", 1, 2, 320, 256, 128, True),
+                                               ("nvfp4", 2, 4, 512, 128, 256, True)):
+            rng = np.random.default_rng(40 + mode)
+            bf = lambda a: P.f32_to_bf16_bits(a.astype(np.float32))
+            g, u = bf(rng.standard_normal((M, K)) * 0.8), bf(rng.standard_normal((M, K)) * 0.8)
+            gx, gw = bf(rng.standard_normal((M, gk)) * 0.2), bf(rng.standard_normal((gk, 1)) * 0.2)
+            routed = bf(rng.standard_normal((M, N)) * 0.2)
+            arr, s = U.make_weight(rng, mode, K, N, scaled)
+            dev = [to_dev(t, "bf16") for t in (g, u, gx, gw, routed)]
+            w = U.dev_weight(arr, mode)
+            sd = torch.from_numpy(s).cuda() if s is not None else None
+            out = torch.empty_like(dev[4])
+            vp = ctypes.c_void_p
+            err = lib.ref_shared_expert_down(vp(dev[0].data_ptr()), vp(dev[1].data_ptr()), M, K, vp(w.data_ptr()), mode, N,
+                                             vp(sd.data_ptr() if sd is not None else None), vp(dev[2].data_ptr()), gk,
+                                             vp(dev[3].data_ptr()), vp(dev[4].data_ptr()), vp(out.data_ptr()), 0,
+                                             vp(torch.cuda.current_stream().cuda_stream))
+            assert err == 0
+            torch.cuda.synchronize()
+            np.savez_compressed(os.path.join(out_dir, f"ref_shared_expert_down_{tag}.npz"), kind="shared_expert_down", mode=mode,
+                                n=N, g=g, u=u, gx=gx, gw=gw, routed=routed, w=arr.view(np.uint8) if mode != 0 else arr,
+                                w_scale=s if s is not None else np.zeros(0, np.float32), y=bits(out))
     print("wrote", sorted(os.listdir(out_dir)))
 
 

@@ -213,6 +213,15 @@ def test_golden_fixtures_from_reference_kernels():
             # and the oracle's own rounding differs from the reference kernel by at most one BF16 ULP
             diff = np.abs(out.astype(np.int32) - z["y"].astype(np.int32))
             assert np.mean(diff <= 1) > 0.999, f
+        elif kind == "shared_expert_down":
+            mode, n = int(z["mode"]), int(z["n"])
+            scale = z["w_scale"] if z["w_scale"].size else None
+            w = z["w"] if mode != 0 else z["w"].view(np.uint16)
+            y, xb, gate, shared = O.shared_expert_down(z["g"], z["u"], mode, w, n, z["gx"], z["gw"], z["routed"], scale)
+            got, exp = O.bf16_to_f32(z["y"]), O.bf16_to_f32(y)
+            tol = np.maximum(np.maximum(np.abs(O.bf16_to_f32(z["routed"])), np.abs(shared)), np.abs(exp)) * 2.0 ** -7 + 1e-30
+            assert np.all(np.abs(got - exp) <= tol), f
+            assert np.mean(z["y"] == y) > 0.97, f
 
 
 def test_untile_hc_matches_the_reference_test_construction():
