@@ -372,7 +372,7 @@ __device__ __forceinline__ int XsIndex(int m, int k, int xpitch) {
   }
 }
 
-template <int MODE, int WORDS, bool TC = false>
+template <int MODE, int WORDS, bool TC = false, bool FUSE = false>
 __device__ __forceinline__ bool StageXImpl(const GemmParams& p, const Tile& tl, uint16_t* xs, SharedScratch& sh) {
   constexpr int kElems = 2 * WORDS;
   constexpr int kBatch = 4;
@@ -403,7 +403,7 @@ __device__ __forceinline__ bool StageXImpl(const GemmParams& p, const Tile& tl, 
           } else {
             v[j][0] = __ldg(reinterpret_cast<const uint32_t*>(src));
           }
-          if (p.fuse) {  // SharedExpertDown: the row of x is swish_mul(g, u)
+          if constexpr (FUSE) {  // SharedExpertDown: the row of x is swish_mul(g, u)
             const uint16_t* src2 = p.x2 + static_cast<size_t>(m) * p.K + tl.kbeg + kk;
 #pragma unroll
             for (int e = 0; e < WORDS; ++e) v[j][e] = SwishMulWord(v[j][e], __ldg(reinterpret_cast<const uint32_t*>(src2) + e));
@@ -492,6 +492,36 @@ __device__ __forceinline__ bool StageXImpl(const GemmParams& p, const Tile& tl, 
   }
 }
 
+// SharedExpertDown's staging: the gate of every row, then x = swish_mul(g, u) staged like a plain x.  Kept
+// out of line: the streaming kernels were measured to slow down by several percent whenever code was added
+// to their inlined body, executed or not, so everything this op adds to them is one call on a cold branch.
+template <int MODE, bool TC>
+__device__ __noinline__ bool StageXFused(const GemmParams& p, const Tile& tl, uint16_t* xs, SharedScratch& sh) {
+  // gate logit of every row: thread-strided partial sums, warps in order, then bf16 -> sigmoid -> bf16
+  const int tid = threadIdx.x, nthreads = blockDim.x, warp = tid >> 5, lane = tid & 31;
+  for (int m = 0; m < p.M; ++m) {  // one row at a time: a single running sum per thread
+    float part = 0.f;
+    const uint16_t* gxm = p.gx + static_cast<size_t>(m) * p.gk;
+    for (int i = tid; i < p.gk; i += nthreads)
+      part += __uint_as_float(static_cast<uint32_t>(gxm[i]) << 16) * __uint_as_float(static_cast<uint32_t>(p.gw[i]) << 16);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+    if (lane == 0) sh.best_v[warp][m] = part;
+  }
+  __syncthreads();
+  if (tid < kMaxRows) {
+    float logit = 0.f;
+    if (tid < p.M)
+      for (int w = 0; w < (nthreads >> 5); ++w) logit += sh.best_v[w][tid];
+    sh.gate[tid] = SigmoidBf16(RoundBf16(logit));
+  }
+  __syncthreads();
+  // swish_mul reads x2 with the same vector width as x
+  const bool vec8 = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.K % 8 == 0) && (reinterpret_cast<uintptr_t>(p.x2) % 16 == 0);
+  if (vec8) return StageXImpl<MODE, 4, TC, true>(p, tl, xs, sh);
+  return StageXImpl<MODE, 1, TC, true>(p, tl, xs, sh);
+}
+
 // Must be called by every thread of the CTA; sh.rmax / sh.rmin are initialised here.
 template <int MODE, bool TC = false>
 __device__ __forceinline__ bool StageX(const GemmParams& p, const Tile& tl, uint16_t* xs, SharedScratch& sh) {
@@ -501,30 +531,8 @@ __device__ __forceinline__ bool StageX(const GemmParams& p, const Tile& tl, uint
     sh.inv_scale[threadIdx.x] = 1.f;
   }
   __syncthreads();
-  if (p.fuse) {
-    // gate logit of every row: thread-strided partial sums, warps in order, then bf16 -> sigmoid -> bf16
-    const int tid = threadIdx.x, nthreads = blockDim.x, warp = tid >> 5, lane = tid & 31;
-    for (int m = 0; m < p.M; ++m) {  // one row at a time: a single running sum per thread
-      float part = 0.f;
-      const uint16_t* gxm = p.gx + static_cast<size_t>(m) * p.gk;
-      for (int i = tid; i < p.gk; i += nthreads)
-        part += __uint_as_float(static_cast<uint32_t>(gxm[i]) << 16) * __uint_as_float(static_cast<uint32_t>(p.gw[i]) << 16);
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-      if (lane == 0) sh.best_v[warp][m] = part;
-    }
-    __syncthreads();
-    if (tid < kMaxRows) {
-      float logit = 0.f;
-      if (tid < p.M)
-        for (int w = 0; w < (nthreads >> 5); ++w) logit += sh.best_v[w][tid];
-      sh.gate[tid] = SigmoidBf16(RoundBf16(logit));
-    }
-    __syncthreads();
-  }
-  // swish_mul reads x2 with the same vector width as x
-  const bool vec8 = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.K % 8 == 0) &&
-                    (!p.fuse || reinterpret_cast<uintptr_t>(p.x2) % 16 == 0);
+  if (p.fuse) return StageXFused<MODE, TC>(p, tl, xs, sh);
+  const bool vec8 = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.K % 8 == 0);
   if (vec8) return StageXImpl<MODE, 4, TC>(p, tl, xs, sh);
   return StageXImpl<MODE, 1, TC>(p, tl, xs, sh);
 }
@@ -959,7 +967,7 @@ struct Nvfp4Stream {
 
 
 template <int MODE, int DEPTH, int W>
-__global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) SkinnyGemmDirectKernel(const GemmParams p) {
+__global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) SkinnyGemmDirectKernel(const __grid_constant__ GemmParams p) {
   using G = Geom<MODE, W>;
   using S = DirectSlot<MODE, W>;
   constexpr int NM = G::kMmas;
@@ -1109,40 +1117,45 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
   const uint32_t ring_end = ring + DEPTH * S::kBytes;
   uint32_t rd_slot = ring;                               // slot of step s
   uint32_t wr_slot = ring + (DEPTH - 1) * S::kBytes;     // slot of step s - 1, refilled with step s + DEPTH - 1
-  for (int s = 0; s < nsteps; ++s) {
-    __syncwarp();
-    if (s + DEPTH - 1 < nsteps) issue_step(s + DEPTH - 1, wr_slot);
-    CpAsyncCommit();
-    asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
-    __syncwarp();
-    Raw<MODE, W> raw;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if constexpr (MODE == kNvfp4) {
-        const uint32_t wa = rd_slot + rd_w[i & 1] + i * S::kNibPitch;
-        const uint32_t sa = rd_slot + rd_s[i & 1] + i * S::kSclPitch;
-#pragma unroll
-        for (int h = 0; h < W; ++h) {
-          raw.r[h][i] = Lds64(wa + h * 64);
-          raw.s[h][i] = Lds8(sa + h * 8);
+  // One copy of the loop per operand path: the loop body then holds a single dequantisation and stays
+  // half as large (the loop's speed was seen to depend on its code footprint).
+  auto k_loop = [&](auto slow_tag) {
+    for (int s = 0; s < nsteps; ++s) {
+      __syncwarp();
+      if (s + DEPTH - 1 < nsteps) issue_step(s + DEPTH - 1, wr_slot);
+      CpAsyncCommit();
+      asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
+      __syncwarp();
+      Raw<MODE, W> raw;
+  #pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if constexpr (MODE == kNvfp4) {
+          const uint32_t wa = rd_slot + rd_w[i & 1] + i * S::kNibPitch;
+          const uint32_t sa = rd_slot + rd_s[i & 1] + i * S::kSclPitch;
+  #pragma unroll
+          for (int h = 0; h < W; ++h) {
+            raw.r[h][i] = Lds64(wa + h * 64);
+            raw.s[h][i] = Lds8(sa + h * 8);
+          }
+        } else {
+          raw.r[i] = Lds128(rd_slot + rd_w[0] + i * (32 * CB));
         }
-      } else {
-        raw.r[i] = Lds128(rd_slot + rd_w[0] + i * (32 * CB));
       }
+      const uint2 xv = Lds64(x_rd);
+      x_rd += x_step;
+      wr_slot = rd_slot;
+      rd_slot += S::kBytes;
+      if (rd_slot == ring_end) rd_slot = ring;
+      ComputeStep<MODE, decltype(slow_tag)::value, W>(acc, raw, xv.x, xv.y);
     }
-    const uint2 xv = Lds64(x_rd);
-    x_rd += x_step;
-    wr_slot = rd_slot;
-    rd_slot += S::kBytes;
-    if (rd_slot == ring_end) rd_slot = ring;
-    if constexpr (MODE == kBf16) {
-      ComputeStep<MODE, false, W>(acc, raw, xv.x, xv.y);
+  };
+  if constexpr (MODE == kBf16) {
+    k_loop(std::false_type{});
+  } else {
+    if (slow) {
+      k_loop(std::true_type{});
     } else {
-      if (slow) {
-        ComputeStep<MODE, true, W>(acc, raw, xv.x, xv.y);
-      } else {
-        ComputeStep<MODE, false, W>(acc, raw, xv.x, xv.y);
-      }
+      k_loop(std::false_type{});
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -1203,7 +1216,7 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
 constexpr int kRegThreads = 512;
 
 template <int MODE>
-__global__ void __launch_bounds__(kRegThreads, 1) SkinnyGemmRegKernel(const GemmParams p) {
+__global__ void __launch_bounds__(kRegThreads, 1) SkinnyGemmRegKernel(const __grid_constant__ GemmParams p) {
   using G = Geom<MODE>;
   constexpr int NM = G::kMmas;
   constexpr int D = MODE == kBf16 ? 4 : 3;  // k-steps in flight per warp (16 registers each)
@@ -1434,7 +1447,7 @@ __device__ __forceinline__ void TcStoreHalf(uint32_t taddr, const uint32_t (&fr)
 }
 
 template <int DEPTH>
-__global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const GemmParams p) {
+__global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const __grid_constant__ GemmParams p) {
   using S = DirectSlot<kNvfp4, 1>;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ SharedScratch sh;
@@ -1678,7 +1691,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const GemmP
 
 // ------------------------------------------------------------------------------ ring kernel
 template <int MODE>
-__global__ void __launch_bounds__(kRingThreads, 2) SkinnyGemmRingKernel(const GemmParams p) {
+__global__ void __launch_bounds__(kRingThreads, 2) SkinnyGemmRingKernel(const __grid_constant__ GemmParams p) {
   using G = Geom<MODE>;
   constexpr int NM = G::kMmas;
   extern __shared__ __align__(128) uint8_t smem[];

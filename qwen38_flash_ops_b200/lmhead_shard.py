@@ -8,7 +8,8 @@ the exchange of those keys (8 bytes per row per rank) - on GPUs inside the fused
 CTA stores them into every rank's peer-mapped buffer and folds what arrives, else one all-gather
 followed by a fold kernel.  Larger key = better pair: larger value, then lower index; NaN above all.
 
-The reference has no distributed code; this is the sharding BASELINE's LM-head case asks for.
+The reference has no distributed code; the vocabulary projection is the one op of the path whose
+columns can be split over the GPUs of a node with a single small exchange.
 """
 from __future__ import annotations
 
