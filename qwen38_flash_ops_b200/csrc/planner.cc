@@ -165,7 +165,7 @@ const TunedShape kTunedB200[] = {
     {kBf16, 5120, 1, {5120, 0, 0, 0}, "direct=2,wn=1,wk=16,cluster=1,waves=1"},
     {kFp8, 5120, 3, {8192, 1024, 1024, 0}, "direct=1,wn=1,wk=6,cluster=4,waves=1"},
     {kNvfp4, 5120, 2, {17408, 17408, 0, 0}, "direct=1,wide=2,wn=1,wk=8,cluster=2,waves=1"},
-    {kNvfp4, 17408, 1, {5120, 0, 0, 0}, "direct=1,wide=1,wn=5,wk=4,cluster=8,waves=1"},
+    {kNvfp4, 17408, 1, {5120, 0, 0, 0}, "direct=1,wide=1,wn=2,wk=8,cluster=6,ctas=120"},
     {kNvfp4, 5120, 1, {151936, 0, 0, 0}, "direct=1,wide=1,wn=9,wk=2,cluster=1,waves=1"},
 };
 
@@ -320,7 +320,7 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
   if (plan->direct == 0 && plan->gran < Granule(in.mode, in.row_align, false)) plan->gran = Granule(in.mode, in.row_align, false);
   if ((plan->direct == 0 && (!pow2(plan->wn) || !pow2(plan->wk) || plan->wn * plan->wk > 8)) || plan->wn < 1 || plan->wk < 1 ||
       plan->warps() > (plan->wide == 2 ? 16 : 20) || plan->wn > 12 || plan->ks < 1 || plan->ks > 8 ||
-      plan->stages < 2 || plan->stages > 8 || plan->cluster < 1 || plan->cluster > 8 || !pow2(plan->cluster)) {
+      plan->stages < 2 || plan->stages > 8 || plan->cluster < 1 || plan->cluster > 8) {
     return false;
   }
   if (plan->gran % Granule(in.mode, in.row_align, plan->direct != 0, plan->wide) != 0) plan->gran = Granule(in.mode, in.row_align, plan->direct != 0, plan->wide);

@@ -607,7 +607,7 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
     }
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();
-    const int cper = TNc / C;  // TNc is a multiple of 64 and C <= 8
+    const int cper = (TNc + C - 1) / C;  // the last rank's share may be short (any C <= 8)
     const int cb = tl.crank * cper;
     for (int m = 0; m < M; ++m) {
       for (int cc = tid; cc < cper; cc += nthreads) {

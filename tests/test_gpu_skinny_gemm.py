@@ -83,7 +83,9 @@ def test_ragged_shapes(cuda, mode):
     # the cp.async ring kernel
     "direct=0,wn=1,wk=8,cluster=1", "direct=0,wn=2,wk=4,cluster=2,ctas=6", "direct=0,wn=4,wk=2,cluster=4,stages=3",
     "direct=0,wn=8,wk=1,cluster=8,ks=2,stages=5", "direct=0,wn=2,wk=2,cluster=1,ks=3,stages=2",
-    "direct=0,wn=4,wk=1,cluster=2,ctas=40", "direct=1,wn=9,wk=2,cluster=1", "direct=1,wn=3,wk=5,cluster=2"])
+    "direct=0,wn=4,wk=1,cluster=2,ctas=40", "direct=1,wn=9,wk=2,cluster=1", "direct=1,wn=3,wk=5,cluster=2",
+    # cluster sizes that are not powers of two (the last rank's column share is short)
+    "direct=1,wn=2,wk=4,cluster=3", "direct=1,wn=3,wk=2,cluster=6,ctas=18", "direct=0,wn=2,wk=2,cluster=5"])
 def test_every_plan_shape(cuda, mode, plan):
     rng = np.random.default_rng(sum(map(ord, plan)) + mode)
     run_case(rng, mode, 3, 2304, [[1280, 256], [512]], with_scale=True, plan=plan)
