@@ -103,7 +103,7 @@ def test_plan_invariants(dtype, k, n, align):
             widest = -(-granules // tiles) * p["gran"]
             assert widest <= p["wn"] * cpw * p["wide"], "a tile must fit the CTA's columns"
         if sms == 148 and sum(n) * k > 2 ** 24:
-            assert p["ctas"] >= 0.85 * 148, "a large shape must cover (nearly) every SM"
+            assert p["ctas"] >= 0.8 * 148, "a large shape must cover (nearly) every SM"
 
 
 def test_plan_override_and_errors():
