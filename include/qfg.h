@@ -97,7 +97,14 @@ QFG_API int qfg_skinny_gemm_create(const int64_t* seg_outs, int n_seg, const int
  * Stricter than the reference where it misreads memory: weights of one call must share one
  * element type, a BF16/FP8 weight must be 4-byte aligned per row and an NVFP4 weight needs
  * N % 64 == 0.  Rows are processed eight at a time, so any m >= 1 is accepted; row r of an
- * m-row call is computed with the arithmetic of the one-row call on that row. */
+ * m-row call is computed with the arithmetic of the one-row call on that row.
+ *
+ * Prefill-shaped calls: with more rows than the "dense_rows" option (unless set: 8 for BF16, 16 for
+ * FP8, 32 for NVFP4 weights, where the branch starts to win on a B200; 0 switches it off) and every width a multiple of 8, the call dequantises the weights to BF16 in column
+ * tiles (w_scale folded in before the rounding) and runs cublasGemmEx with FP32 accumulation, as
+ * the reference does for M > 8 (fused_gemm.cu:365-428, dispatch at :578-583).  Like the
+ * reference's, this branch allocates a handle and a buffer on first use, is not graph-capturable,
+ * ignores `trigger`, and its accumulation order is the library's; cuBLAS is loaded at run time. */
 QFG_API int qfg_skinny_gemm_compute(const qfg_skinny_gemm* op, const void* x, int64_t m, int64_t k,
                             const qfg_tensor2d* weights, int n_weights, void* const* outs, int n_outs,
                             void* stream);
@@ -105,7 +112,8 @@ QFG_API int qfg_skinny_gemm_compute(const qfg_skinny_gemm* op, const void* x, in
 /* Launch options that are not node attributes.  "pdl_wait" = 1 launches the kernel with the
  * programmatic-stream-serialisation attribute and makes it wait for its predecessor
  * (griddepcontrol.wait) only after its first weight tiles are in flight.  "plan" pins the
- * launch geometry ("wn=4,wk=2,ks=1,stages=4,cluster=8,ctas=296"); used by the tuning sweeps. */
+ * launch geometry ("wn=4,wk=2,ks=1,stages=4,cluster=8,ctas=296"); used by the tuning sweeps.
+ * "dense_rows" moves or disables (0) the row count above which the prefill branch is taken. */
 QFG_API int qfg_skinny_gemm_set_option(qfg_skinny_gemm* op, const char* key, const char* value);
 
 /* Writes a one-line description of the launch plan chosen for these shapes into buf. */

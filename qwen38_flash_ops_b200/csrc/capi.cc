@@ -73,6 +73,7 @@ struct qfg_skinny_gemm {
   int pdl_wait = 0;
   int force_slow = 0;
   int debug = 0;
+  int dense_rows = -1;  // calls with more rows take the dequantise + library GEMM branch; -1 = qfg::DenseRowsDefault(mode), 0 = never
   unsigned long long phase_times = 0;  // device address given through set_option("phase_times", ...)
   std::string plan_spec;
   // plans already computed for this node, keyed by the shape of the call
@@ -81,7 +82,8 @@ struct qfg_skinny_gemm {
   qfg_skinny_gemm() = default;
   qfg_skinny_gemm(const qfg_skinny_gemm& o)
       : seg_outs(o.seg_outs), widths(o.widths), trigger(o.trigger), d_w_scale(o.d_w_scale), w_scale_len(o.w_scale_len),
-        pdl_wait(o.pdl_wait), force_slow(o.force_slow), debug(o.debug), phase_times(o.phase_times), plan_spec(o.plan_spec) {}
+        pdl_wait(o.pdl_wait), force_slow(o.force_slow), debug(o.debug), dense_rows(o.dense_rows), phase_times(o.phase_times),
+        plan_spec(o.plan_spec) {}
 };
 
 struct qfg_dequant {
@@ -248,6 +250,11 @@ qfg::Plan ComputePlan(const qfg_skinny_gemm& op, const qfg::PlanInput& in) {
 // Launches row blocks of at most eight rows; only the last block may release PDL dependents
 // (skinny_gemm.cuh:661-676 does the same with blocks of four).
 void Run(const qfg_skinny_gemm& op, Prepared& pr, int64_t m, cudaStream_t stream, const char* name) {
+  const int dense_rows = op.dense_rows < 0 ? qfg::DenseRowsDefault(pr.mode) : op.dense_rows;
+  if (dense_rows > 0 && m > dense_rows && qfg::DenseEligible(pr.params)) {
+    qfg::LaunchDenseGemm(pr.mode, pr.params, m, stream);
+    return;
+  }
   const qfg::Plan plan = PlanFor(op, pr.plan_in, static_cast<int>(std::min<int64_t>(m, qfg::kMaxRows)));
   qfg::GemmParams base = pr.params;
   int64_t done = 0;
@@ -308,6 +315,7 @@ int SetGemmOption(qfg_skinny_gemm* op, const char* key, const char* value) {
   if (k == "pdl_wait") op->pdl_wait = std::atoi(value);
   else if (k == "force_slow") op->force_slow = std::atoi(value);
   else if (k == "debug") op->debug = std::atoi(value);
+  else if (k == "dense_rows") op->dense_rows = std::atoi(value);
   else if (k == "phase_times") op->phase_times = std::strtoull(value, nullptr, 10);
   else if (k == "plan") op->plan_spec = value;
   else if (k == "trigger") op->trigger = std::atoi(value);

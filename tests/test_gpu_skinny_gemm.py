@@ -20,7 +20,7 @@ import _util as U
 pytestmark = pytest.mark.gpu
 
 
-def run_case(rng, mode, M, K, seg_widths, with_scale=None, plan=None, force_slow=False, x_bits=None):
+def run_case(rng, mode, M, K, seg_widths, with_scale=None, plan=None, force_slow=False, x_bits=None, dense_rows=None):
     """seg_widths: list (per weight) of lists of output widths."""
     seg_outs = [len(w) for w in seg_widths]
     widths = [w for ws in seg_widths for w in ws]
@@ -39,6 +39,8 @@ def run_case(rng, mode, M, K, seg_widths, with_scale=None, plan=None, force_slow
         op.set_option("plan", plan)
     if force_slow:
         op.set_option("force_slow", 1)
+    if dense_rows is not None:
+        op.set_option("dense_rows", dense_rows)
     outs = op(to_dev(x, "bf16"), *[U.dev_weight(a, mode) for a in stored])
     torch.cuda.synchronize()
     o = 0
@@ -72,7 +74,8 @@ def test_ragged_shapes(cuda, mode):
         run_case(rng, mode, 2, 512, [[324 - 4], [4]])
     run_case(rng, mode, 5, 512, [[320]])       # more than four rows in one pass
     run_case(rng, mode, 8, 512, [[320]])
-    run_case(rng, mode, 11, 512, [[320]])      # two passes of eight and three rows
+    run_case(rng, mode, 11, 512, [[320]], dense_rows=0)  # two passes of eight and three rows
+    run_case(rng, mode, 11, 512, [[320]])      # BF16 weights: the library GEMM branch (more than 8 rows)
 
 
 @pytest.mark.parametrize("mode", [0, 1, 2])
@@ -359,3 +362,70 @@ def test_register_streaming_kernel(cuda, mode, plan):
     rng = np.random.default_rng(sum(map(ord, plan)) + mode)
     run_case(rng, mode, 3, 2304, [[1280, 256], [512]], with_scale=True, plan=plan)
     run_case(rng, mode, 8, 1000, [[640], [128, 128]], with_scale=True, plan=plan)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_many_rows_take_the_dense_branch(cuda, mode):
+    """Prefill-shaped calls (more rows than the `dense_rows` option; by default 8 / 16 / 32 for BF16 / FP8 / NVFP4) dequantise the weights to
+    BF16 with w_scale folded in and run a library GEMM, as the reference does for M > 8 (fused_gemm.cu:365-428).
+    The accumulation order of that GEMM is not pinned, so the check is the tolerance against the exact sum over
+    the BF16-rounded weights, and agreement with the streaming passes within the rounding of those weights."""
+    rng = np.random.default_rng(900 + mode)
+    M, K = 80, 1024
+    seg_widths = [[256], [128, 384]]
+    seg_outs = [len(w) for w in seg_widths]
+    widths = [w for ws in seg_widths for w in ws]
+    ns = [sum(ws) for ws in seg_widths]
+    x = P.synth_x(rng, M, K)
+    stored, scales = zip(*[U.make_weight(rng, mode, K, n, True) for n in ns])
+    quantised = mode != 0
+    w_scale = np.concatenate(scales) if quantised else None
+    dense = SkinnyGemm(seg_outs, widths, w_scale=w_scale)
+    passes = SkinnyGemm(seg_outs, widths, w_scale=w_scale)
+    passes.set_option("dense_rows", 0)
+    xd = to_dev(x, "bf16")
+    wd = [U.dev_weight(a, mode) for a in stored]
+    out_dense = dense(xd, *wd)
+    out_passes = passes(xd, *wd)
+    # rows at or below the threshold keep the streaming kernels: bit-identical with the branch switched off
+    small = {0: 8, 1: 16, 2: 32}[mode]
+    out_small = dense(xd[:small], *wd)
+    torch.cuda.synchronize()
+    o = 0
+    for i, n in enumerate(ns):
+        cat = lambda outs, rows: np.concatenate([bits(outs[o + j]).reshape(rows, -1) for j in range(seg_outs[i])], axis=1)
+        got, ref_passes = cat(out_dense, M), cat(out_passes, M)
+        assert np.array_equal(cat(out_small, small), ref_passes[:small])
+        w_bf16 = O.dequant_weight_bf16(mode, stored[i], n, 0, scales[i] if quantised else None)
+        _, sums, mags = C.skinny_gemm(0, x, w_bf16, n, None)
+        ok = O.gemm_within_tolerance(got, sums, mags, K)
+        assert ok.all(), f"mode {mode} weight {i}: {np.count_nonzero(~ok)} outputs outside tolerance"
+        a, b = O.bf16_to_f32(got).astype(np.float64), O.bf16_to_f32(ref_passes).astype(np.float64)
+        # the two branches round the scaled weights at different points: 2^-9 relative per weight
+        assert (np.abs(a - b) <= 2.0 ** -7 * np.abs(b) + 2.0 ** -8 * mags + 1e-30).all()
+        U.check_against_oracle(mode, x, stored[i], n, scales[i] if quantised else None, ref_passes, K, "passes")
+        o += seg_outs[i]
+
+
+def test_dense_branch_tiles_wide_outputs_and_skips_odd_widths(cuda):
+    """An output wider than one dequantisation tile (16384 columns) is produced tile by tile; widths that are
+    not multiples of eight stay on the streaming kernels at any row count."""
+    rng = np.random.default_rng(77)
+    M, K, n = 40, 128, 16384 + 4096
+    x = P.synth_x(rng, M, K)
+    w, s = U.make_weight(rng, 2, K, n, True)
+    op = SkinnyGemm([1], [n], w_scale=s)
+    out = op(to_dev(x, "bf16"), U.dev_weight(w, 2))
+    torch.cuda.synchronize()
+    w_bf16 = O.dequant_weight_bf16(2, w, n, 0, s)
+    _, sums, mags = C.skinny_gemm(0, x, w_bf16, n, None)
+    assert O.gemm_within_tolerance(bits(out[0]).reshape(M, n), sums, mags, K).all()
+    # 100 columns: not a multiple of eight -> the streaming kernels at M = 40, row by row as for one row
+    w2, _ = U.make_weight(rng, 0, K, 100)
+    op2 = SkinnyGemm([1], [100])
+    out2 = op2(to_dev(x, "bf16"), U.dev_weight(w2, 0))
+    torch.cuda.synchronize()
+    U.check_against_oracle(0, x, w2, 100, None, bits(out2[0]).reshape(M, 100), K, "odd width")
+    one = op2(to_dev(x[17:18], "bf16"), U.dev_weight(w2, 0))
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(one[0]).reshape(-1), bits(out2[0]).reshape(M, 100)[17])
