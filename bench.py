@@ -344,8 +344,17 @@ def run_ours(args):
     total_bytes = wl.weight_bytes
 
     verified = None
+    exchange_note = None
     if world > 1:
-        verified = verify_sharded(torch, dist, head, x, shard, n_local, c0, world)
+        ok = verify_sharded(torch, dist, head, x, shard, n_local, c0, world)
+        if not ok and head.peer is not None:
+            # the in-kernel exchange failed its check on this machine: fall back to the collective and say so
+            exchange_note = f"peer-memory exchange failed verification (status {head.peer.status()}); NCCL used instead"
+            head = ShardedLmHead(shard, n_local, c0, exchange="nccl")
+            ok = verify_sharded(torch, dist, head, x, shard, n_local, c0, world)
+        if not ok:
+            raise SystemExit("sharded LM head disagrees with the fold of the per-rank unfused results")
+        verified = "sharded step == fold of per-rank SkinnyGemm + ArgmaxRows"
 
     sampler = ClockSampler(local)
     if rank == 0:
@@ -410,6 +419,8 @@ def run_ours(args):
         line["verified"] = verified
         line["config"]["exchange"] = ("keys stored into the peers' memory by the fused kernel (no collective launch)"
                                       if head.peer is not None else "NCCL all-gather + fold kernel")
+        if exchange_note is not None:
+            line["config"]["exchange_note"] = exchange_note
         if head.peer is not None and head.peer.status() != 0:
             raise SystemExit("a wait for a peer's keys ran out during the run")
     if world == 1 and not args.skip_cpu:
@@ -439,7 +450,8 @@ def run_ours(args):
 
 def verify_sharded(torch, dist, head, x, shard, n_local, c0, world):
     """Untimed: the sharded step against the fold of every rank's unfused SkinnyGemm + ArgmaxRows
-    over its own columns (same Better order: larger value, then lower global index)."""
+    over its own columns (same Better order: larger value, then lower global index).  Returns the
+    verdict agreed by all ranks."""
     from qwen38_flash_ops_b200 import ArgmaxRows, SkinnyGemm
 
     m = x.shape[0]
@@ -455,9 +467,12 @@ def verify_sharded(torch, dist, head, x, shard, n_local, c0, world):
     for r in range(m):
         best = max(range(world), key=lambda w: (g[w, r, 0], -g[w, r, 1]))
         ok = ok and int(g[best, r, 1]) == int(idx[r].item()) and float(g[best, r, 0]) == float(val[r].item())
-    if not ok:
-        raise SystemExit("sharded LM head disagrees with the fold of the per-rank unfused results")
-    return "sharded step == fold of per-rank SkinnyGemm + ArgmaxRows"
+    if head.peer is not None and head.peer.status() != 0:
+        ok = False
+    # every rank takes the same decision
+    flag = torch.tensor([1 if ok else 0], device=x.device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return int(flag.item()) == 1
 
 
 _OUT_CACHE = {}
