@@ -162,9 +162,12 @@ class HostLmHead:
     """The LM head for a caller whose activations and results live in host memory.
 
     One call copies `x` (pinned host, BF16 [m, K]) to the device, runs the sharded step and copies
-    the winning index and value back.  On a single GPU the three stages are captured once into a
-    CUDA graph (the input copy and the fused kernel, which writes its results directly into the
-    pinned host buffers), so a call costs one graph launch and one stream synchronisation; with several ranks the stages are issued eagerly around the all-gather.
+    the winning index and value back.  Whenever the step is a single kernel (one GPU, or several
+    ranks exchanging their keys through peer memory inside the kernel) the stages are captured once
+    into a CUDA graph: the input copy and the fused kernel, which writes its results directly into
+    the pinned host buffers, so a call costs one graph launch and one stream synchronisation.  With
+    the NCCL exchange the stages are issued eagerly around the all-gather.  Every rank must construct
+    the object and make its calls in step with the others.
     """
 
     def __init__(self, head: ShardedLmHead, m: int, k: int):
@@ -178,7 +181,8 @@ class HostLmHead:
         self._key = torch.empty(m, dtype=torch.int64, device=dev)
         self.stream = torch.cuda.Stream(device=dev)
         self.graph = None
-        if head.world == 1:
+        self._single_kernel = head.world == 1 or head.peer is not None
+        if self._single_kernel:
             with torch.cuda.stream(self.stream):
                 self._enqueue()  # first call outside capture: one-time set-up of the kernels
                 self.stream.synchronize()
@@ -189,10 +193,14 @@ class HostLmHead:
     def _enqueue(self):
         self.x_dev.copy_(self.x_host, non_blocking=True)
         h = self.head
+        # The kernel's last CTA stores the winners straight into the pinned host buffers (pinned
+        # memory is device-addressable), which saves two device-to-host copies per call.
         if h.world == 1:
-            # The kernel's last CTA stores the winners straight into the pinned host buffers (pinned
-            # memory is device-addressable), which saves two device-to-host copies per call.
             h.head(self.x_dev, h.shard, h.n_local, col_offset=h.col_begin, out=(self.idx_host, self.val_host, self._key))
+            return
+        if h.peer is not None:
+            h.head.call_sharded(self.x_dev, h.shard, h.n_local, h.col_begin, h.peer.struct,
+                                out=(self.idx_host, self.val_host))
             return
         idx, val = h.step(self.x_dev)
         self.idx_host.copy_(idx, non_blocking=True)
