@@ -705,6 +705,7 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
         __syncthreads();
         if (tid == 0) {
           own->epoch = epoch;
+          __threadfence_system();  // release: the key stores the barrier made visible to this thread precede the flags
           for (int r = 0; r < p.xworld; ++r) *reinterpret_cast<volatile unsigned int*>(&p.xpeer[r]->flags[par][p.xrank]) = epoch;
         }
         if (tid < p.xworld) {
