@@ -1225,6 +1225,7 @@ __global__ void __launch_bounds__(kRegThreads, 1) SkinnyGemmRegKernel(const __gr
   __shared__ SharedScratch sh;
 
   if (p.trigger == 1) GridLaunchDependents();
+  Stamp(p, 0);
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int wn = warp % p.wn, wk = warp / p.wn;
@@ -1306,10 +1307,12 @@ __global__ void __launch_bounds__(kRegThreads, 1) SkinnyGemmRegKernel(const __gr
   for (int d = 0; d < D; ++d) {
     if (warp_has_cols && d < nsteps) load_step(buf[d], d);
   }
+  Stamp(p, 1);
   if (p.pdl_wait) GridDependencyWait();
 
   uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
   const bool slow = StageX<MODE>(p, tl, xs, sh);
+  Stamp(p, 2);
 
   float acc[NM][4];
 #pragma unroll
@@ -1345,9 +1348,12 @@ __global__ void __launch_bounds__(kRegThreads, 1) SkinnyGemmRegKernel(const __gr
       }
     }
   }
+  Stamp(p, 3);
   if (p.trigger == 2) GridLaunchDependents();
   __syncthreads();
+  Stamp(p, 4);
   Epilogue<MODE>(p, tl, acc, smem, sh, warp_has_cols);
+  Stamp(p, 5);
 }
 
 // ------------------------------------------------------------------------------ tcgen05 kernel
