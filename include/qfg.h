@@ -99,8 +99,8 @@ QFG_API int qfg_skinny_gemm_create(const int64_t* seg_outs, int n_seg, const int
  * N % 64 == 0.  Rows are processed eight at a time, so any m >= 1 is accepted; row r of an
  * m-row call is computed with the arithmetic of the one-row call on that row.
  *
- * Prefill-shaped calls: with more rows than the "dense_rows" option (unless set: 8 for BF16, 16 for
- * FP8, 32 for NVFP4 weights, where the branch starts to win on a B200; 0 switches it off) and every width a multiple of 8, the call dequantises the weights to BF16 in column
+ * Prefill-shaped calls: with more rows than the "dense_rows" option (unless set: 8 for BF16 and FP8,
+ * 16 for NVFP4 weights, where the branch starts to win on a B200; 0 switches it off) and every width a multiple of 8, the call dequantises the weights to BF16 in column
  * tiles (w_scale folded in before the rounding) and runs cublasGemmEx with FP32 accumulation, as
  * the reference does for M > 8 (fused_gemm.cu:365-428, dispatch at :578-583).  Like the
  * reference's, this branch allocates a handle and a buffer on first use, is not graph-capturable,

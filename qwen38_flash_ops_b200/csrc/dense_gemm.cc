@@ -13,6 +13,7 @@
 #include <dlfcn.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <stdexcept>
@@ -24,7 +25,15 @@
 namespace qfg {
 namespace {
 
-constexpr int kDenseTileCols = 16384;  // columns dequantised per GEMM call (168 MB of BF16 at K = 5120)
+// Columns dequantised per GEMM call.  QFG_DENSE_TILE overrides it (a multiple of 16).
+int DenseTileCols() {
+  static const int cols = [] {
+    const char* e = std::getenv("QFG_DENSE_TILE");
+    const int v = e != nullptr ? std::atoi(e) : 0;
+    return v >= 16 && v % 16 == 0 ? v : 16384;
+  }();
+  return cols;
+}
 
 using GemmExFn = cublasStatus_t (*)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const void*,
                                     const void*, cudaDataType, int, const void*, cudaDataType, int, const void*, void*,
@@ -114,6 +123,7 @@ void LaunchDenseGemm(int mode, const GemmParams& p, int64_t m, cudaStream_t stre
       throw std::runtime_error("SkinnyGemm(dense): cublasSetStream failed");
   }
   const float alpha = 1.f, beta = 0.f;
+  const int kDenseTileCols = DenseTileCols();
   const int K = p.K;
   const int M = static_cast<int>(m);
   size_t need = 0;

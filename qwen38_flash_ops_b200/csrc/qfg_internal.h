@@ -209,15 +209,15 @@ struct DequantParams {
   int col_begin[kMaxOut] = {};
   int width[kMaxOut] = {};
   int aligned = 1;      // vector loads are legal for every row
+  int scale_vec = 0;    // set by LaunchDequant: w_scale can be read with 16-byte loads
 };
 cudaError_t LaunchDequant(const DequantParams& p, cudaStream_t stream);
 
 // dense_gemm.cc: calls with more than `dense_rows` rows (an option of the node; 0 disables the branch).
-// The defaults are where the branch starts to win on a B200: BF16 weights need no dequantisation pass, so two
-// streaming passes already lose (K = 5120, N = 2048: 37.7 us against 16.3); FP8 pays one pass over N = 10240
-// (64 us, level from 16 to 128 rows) against 35 us per eight rows; NVFP4 pays 131 us at N = 17408, which
-// four passes (140 us) reach.
-constexpr int DenseRowsDefault(int mode) { return mode == kBf16 ? 8 : mode == kFp8 ? 16 : 32; }
+// The defaults are where the branch starts to win on a B200 (K = 5120): BF16 weights need no dequantisation
+// pass, so two streaming passes already lose (N = 2048: 37.7 us against 16.3); FP8 pays 48.5 us at N = 10240
+// against 35 us per eight rows; NVFP4 pays 89 us at N = 17408, which three passes (105 us) exceed.
+constexpr int DenseRowsDefault(int mode) { return mode == kNvfp4 ? 16 : 8; }
 bool DenseEligible(const GemmParams& p);
 void LaunchDenseGemm(int mode, const GemmParams& p, int64_t m, cudaStream_t stream);  // throws std::runtime_error
 

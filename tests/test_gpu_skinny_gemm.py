@@ -75,7 +75,8 @@ def test_ragged_shapes(cuda, mode):
     run_case(rng, mode, 5, 512, [[320]])       # more than four rows in one pass
     run_case(rng, mode, 8, 512, [[320]])
     run_case(rng, mode, 11, 512, [[320]], dense_rows=0)  # two passes of eight and three rows
-    run_case(rng, mode, 11, 512, [[320]])      # BF16 weights: the library GEMM branch (more than 8 rows)
+    if mode == 0:
+        run_case(rng, mode, 11, 512, [[320]])  # BF16 weights, more than 8 rows: the library GEMM branch, same tolerance
 
 
 @pytest.mark.parametrize("mode", [0, 1, 2])
@@ -366,7 +367,7 @@ def test_register_streaming_kernel(cuda, mode, plan):
 
 @pytest.mark.parametrize("mode", [0, 1, 2])
 def test_many_rows_take_the_dense_branch(cuda, mode):
-    """Prefill-shaped calls (more rows than the `dense_rows` option; by default 8 / 16 / 32 for BF16 / FP8 / NVFP4) dequantise the weights to
+    """Prefill-shaped calls (more rows than the `dense_rows` option; by default 8 / 8 / 16 for BF16 / FP8 / NVFP4) dequantise the weights to
     BF16 with w_scale folded in and run a library GEMM, as the reference does for M > 8 (fused_gemm.cu:365-428).
     The accumulation order of that GEMM is not pinned, so the check is the tolerance against the exact sum over
     the BF16-rounded weights, and agreement with the streaming passes within the rounding of those weights."""
@@ -388,7 +389,7 @@ def test_many_rows_take_the_dense_branch(cuda, mode):
     out_dense = dense(xd, *wd)
     out_passes = passes(xd, *wd)
     # rows at or below the threshold keep the streaming kernels: bit-identical with the branch switched off
-    small = {0: 8, 1: 16, 2: 32}[mode]
+    small = {0: 8, 1: 8, 2: 16}[mode]
     out_small = dense(xd[:small], *wd)
     torch.cuda.synchronize()
     o = 0
