@@ -243,6 +243,24 @@ QFG_API int qfg_lmhead_compute_sharded(const qfg_lmhead* op, const void* x, int6
                                        void* stream);
 /* 0 = every wait so far completed, 1 = a wait ran out.  Synchronises the device. */
 QFG_API int qfg_lmhead_exchange_status(const void* own_buffer, int* status);
+
+/* The LM head for a caller whose activations and results live in host memory (the reference's callers
+ * hand ORT host tensors for the sampled token; no counterpart in the reference library itself).
+ * qfg_lmhead_host_create records, once, a CUDA graph of two kernels on a stream of its own: the copy of
+ * `x_host` (pinned, device-addressable, BF16 [m, k]) to `x_dev`, and the fused kernel as its programmatic
+ * dependent (it streams its first weight tiles while x crosses the host link), which stores the winners
+ * straight into `idx_host` / `val_host` (pinned, device-addressable; val_host may be null).  qfg_lmhead_host_run
+ * launches the graph and waits for it: one call per decode step, after which idx_host / val_host hold
+ * the result.  `exchange` is null on one GPU, or the peer-memory exchange of the sharded head, in which
+ * case every rank must create and run in step with the others.  create runs the step once before it
+ * records it, so the workspace header must be zero at that point, as for qfg_lmhead_compute. */
+typedef struct qfg_lmhead_host qfg_lmhead_host;
+QFG_API int qfg_lmhead_host_create(const qfg_lmhead* op, int64_t m, int64_t k, const qfg_tensor2d* weight, int64_t n,
+                                   int64_t col_offset, void* workspace, const qfg_lmhead_exchange* exchange,
+                                   const void* x_host, void* x_dev, int64_t* idx_host, float* val_host,
+                                   qfg_lmhead_host** out);
+QFG_API int qfg_lmhead_host_run(qfg_lmhead_host* h);
+QFG_API void qfg_lmhead_host_destroy(qfg_lmhead_host* h);
 /* Device memory that other processes on the node can map (cudaMalloc + cudaIpcGetMemHandle; `handle`
  * receives 64 bytes), the mapping of another process's handle (peer access enabled lazily), and their
  * releases.  Set-up calls: they allocate and synchronise. */

@@ -29,6 +29,7 @@ EXPORTS = (
     "qfg_lmhead_destroy", "qfg_lmhead_combine",
     "qfg_lmhead_exchange_bytes", "qfg_lmhead_compute_sharded", "qfg_lmhead_exchange_status",
     "qfg_peer_alloc", "qfg_peer_open", "qfg_peer_close", "qfg_peer_free",
+    "qfg_lmhead_host_create", "qfg_lmhead_host_run", "qfg_lmhead_host_destroy",
 )
 
 
@@ -96,6 +97,11 @@ def load() -> ctypes.CDLL:
     lib.qfg_lmhead_compute_sharded.argtypes = [c_void_p, c_void_p, c_int64, c_int64, POINTER(Tensor2D), c_int64, c_int64,
                                                c_void_p, POINTER(LmExchange), c_void_p, c_void_p, c_void_p, c_void_p]
     lib.qfg_lmhead_exchange_status.argtypes = [c_void_p, POINTER(c_int)]
+    lib.qfg_lmhead_host_create.argtypes = [c_void_p, c_int64, c_int64, POINTER(Tensor2D), c_int64, c_int64, c_void_p,
+                                           POINTER(LmExchange), c_void_p, c_void_p, c_void_p, c_void_p, POINTER(c_void_p)]
+    lib.qfg_lmhead_host_run.argtypes = [c_void_p]
+    lib.qfg_lmhead_host_destroy.argtypes = [c_void_p]
+    lib.qfg_lmhead_host_destroy.restype = None
     lib.qfg_peer_alloc.argtypes = [c_size_t, POINTER(c_void_p), ctypes.c_char_p]
     lib.qfg_peer_open.argtypes = [ctypes.c_char_p, POINTER(c_void_p)]
     lib.qfg_peer_close.argtypes = [c_void_p]

@@ -383,6 +383,33 @@ int LmheadComputeWithWorkspace(const qfg_lmhead* op, const void* x, int64_t m, i
 
 }  // namespace qfg
 
+namespace {
+
+// The input copy of the host step as a kernel, so that the fused kernel can be its programmatic dependent:
+// it releases the dependent at once, and the dependent streams its first weight tiles while these few
+// kilobytes cross the host link, waiting (griddepcontrol.wait) only before it reads x.  `src` is pinned host
+// memory addressed by the device.
+template <typename V>
+__global__ void __launch_bounds__(256) HostRowsToDeviceKernel(const V* __restrict__ src, V* __restrict__ dst, size_t n) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    dst[i] = src[i];
+}
+
+cudaError_t LaunchHostRowsToDevice(const void* src, void* dst, size_t bytes, cudaStream_t stream) {
+  const bool v16 = bytes % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+  const size_t n = v16 ? bytes / 16 : bytes / 4;
+  const unsigned blocks = static_cast<unsigned>(std::min<size_t>(16, (n + 255) / 256));
+  if (v16) {
+    HostRowsToDeviceKernel<uint4><<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), n);
+  } else {
+    HostRowsToDeviceKernel<uint32_t><<<blocks, 256, 0, stream>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), n);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
 extern "C" {
 
 const char* qfg_last_error(void) { return g_last_error.c_str(); }
@@ -696,6 +723,74 @@ int qfg_lmhead_exchange_status(const void* own_buffer, int* status) {
   if (err != cudaSuccess) return Fail(QFG_FAIL, (std::string("LmHead: ") + cudaGetErrorString(err)).c_str());
   *status = static_cast<int>(s);
   return QFG_OK;
+}
+
+struct qfg_lmhead_host {
+  cudaStream_t stream = nullptr;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  qfg_lmhead op;  // the caller's node with pdl_wait set (shares, and does not own, its w_scale)
+};
+
+
+int qfg_lmhead_host_create(const qfg_lmhead* op, int64_t m, int64_t k, const qfg_tensor2d* weight, int64_t n,
+                           int64_t col_offset, void* workspace, const qfg_lmhead_exchange* exchange, const void* x_host,
+                           void* x_dev, int64_t* idx_host, float* val_host, qfg_lmhead_host** out) {
+  if (out == nullptr) return Fail(QFG_INVALID_ARGUMENT, "LmHead: null handle pointer");
+  *out = nullptr;
+  if (op == nullptr || weight == nullptr || x_host == nullptr || x_dev == nullptr || idx_host == nullptr || m < 1 || k < 1)
+    return Fail(QFG_INVALID_ARGUMENT, "LmHead: null or bad host-step argument");
+  if (k % 2 != 0 || reinterpret_cast<uintptr_t>(x_host) % 4 != 0 || reinterpret_cast<uintptr_t>(x_dev) % 4 != 0)
+    return Fail(QFG_INVALID_ARGUMENT, "LmHead: x must be 4-byte aligned with an even K");
+  qfg_lmhead_host* h = new qfg_lmhead_host{nullptr, nullptr, nullptr, *op};
+  h->op.gemm.pdl_wait = 1;
+  const size_t x_bytes = static_cast<size_t>(m) * static_cast<size_t>(k) * 2;
+  // one step: input copy, then the fused kernel as its programmatic dependent, results addressed to host memory
+  auto enqueue = [&]() -> int {
+    const cudaError_t err = LaunchHostRowsToDevice(x_host, x_dev, x_bytes, h->stream);
+    if (err != cudaSuccess) return Fail(QFG_FAIL, std::string("LmHead: ") + cudaGetErrorString(err));
+    return qfg::LmheadComputeWithWorkspace(&h->op, x_dev, m, k, weight, n, col_offset, workspace, qfg_lmhead_workspace_bytes(),
+                                           idx_host, val_host, nullptr, nullptr, h->stream, exchange);
+  };
+  int rc = QFG_OK;
+  cudaError_t err = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
+  if (err == cudaSuccess) {
+    // eagerly once: plans and kernel attributes are settled outside the capture
+    rc = enqueue();
+    if (rc == QFG_OK) err = cudaStreamSynchronize(h->stream);
+  }
+  if (rc == QFG_OK && err == cudaSuccess) {
+    err = cudaStreamBeginCapture(h->stream, cudaStreamCaptureModeThreadLocal);
+    if (err == cudaSuccess) {
+      rc = enqueue();
+      const cudaError_t end = cudaStreamEndCapture(h->stream, &h->graph);  // always ends the capture
+      if (rc == QFG_OK) err = end;
+    }
+  }
+  if (rc == QFG_OK && err == cudaSuccess) err = cudaGraphInstantiate(&h->exec, h->graph, 0);
+  if (rc != QFG_OK || err != cudaSuccess) {
+    if (rc == QFG_OK) rc = Fail(QFG_FAIL, std::string("LmHead: ") + cudaGetErrorString(err));
+    qfg_lmhead_host_destroy(h);
+    return rc;
+  }
+  *out = h;
+  return QFG_OK;
+}
+
+int qfg_lmhead_host_run(qfg_lmhead_host* h) {
+  if (h == nullptr || h->exec == nullptr) return Fail(QFG_INVALID_ARGUMENT, "LmHead: null host-step handle");
+  cudaError_t err = cudaGraphLaunch(h->exec, h->stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(h->stream);
+  if (err != cudaSuccess) return Fail(QFG_FAIL, std::string("LmHead: ") + cudaGetErrorString(err));
+  return QFG_OK;
+}
+
+void qfg_lmhead_host_destroy(qfg_lmhead_host* h) {
+  if (h == nullptr) return;
+  if (h->exec != nullptr) cudaGraphExecDestroy(h->exec);
+  if (h->graph != nullptr) cudaGraphDestroy(h->graph);
+  if (h->stream != nullptr) cudaStreamDestroy(h->stream);
+  delete h;
 }
 
 int qfg_peer_alloc(size_t bytes, void** ptr, unsigned char handle[64]) {

@@ -161,16 +161,22 @@ class ShardedLmHead:
 class HostLmHead:
     """The LM head for a caller whose activations and results live in host memory.
 
-    One call copies `x` (pinned host, BF16 [m, K]) to the device, runs the sharded step and copies
-    the winning index and value back.  Whenever the step is a single kernel (one GPU, or several
-    ranks exchanging their keys through peer memory inside the kernel) the stages are captured once
-    into a CUDA graph: the input copy and the fused kernel, which writes its results directly into
-    the pinned host buffers, so a call costs one graph launch and one stream synchronisation.  With
-    the NCCL exchange the stages are issued eagerly around the all-gather.  Every rank must construct
-    the object and make its calls in step with the others.
+    One call copies `x` (pinned host, BF16 [m, K]) to the device, runs the sharded step and leaves the
+    winning index and value in pinned host buffers.  Whenever the step is a single kernel (one GPU, or
+    several ranks exchanging their keys through peer memory inside the kernel) the call is
+    qfg_lmhead_host_run: a CUDA graph, recorded once by the library, of the input copy and the fused
+    kernel, which stores its results straight into the pinned host buffers; a call then costs one
+    graph launch and one stream synchronisation.  With the NCCL exchange the stages are issued eagerly
+    around the all-gather.  Every rank must construct the object and make its calls in step with the
+    others.
     """
 
     def __init__(self, head: ShardedLmHead, m: int, k: int):
+        import ctypes
+
+        from . import _lib
+        from .ops import _tensor2d
+
         torch = head._torch
         dev = head.shard.device
         self.head = head
@@ -178,44 +184,46 @@ class HostLmHead:
         self.x_dev = torch.empty((m, k), dtype=torch.bfloat16, device=dev)
         self.idx_host = torch.empty(m, dtype=torch.int64).pin_memory()
         self.val_host = torch.empty(m, dtype=torch.float32).pin_memory()
-        self._key = torch.empty(m, dtype=torch.int64, device=dev)
-        self.stream = torch.cuda.Stream(device=dev)
-        self.graph = None
-        self._single_kernel = head.world == 1 or head.peer is not None
-        if self._single_kernel:
-            with torch.cuda.stream(self.stream):
-                self._enqueue()  # first call outside capture: one-time set-up of the kernels
-                self.stream.synchronize()
-                self.graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(self.graph, stream=self.stream):
-                    self._enqueue()
-
-    def _enqueue(self):
-        self.x_dev.copy_(self.x_host, non_blocking=True)
-        h = self.head
-        # The kernel's last CTA stores the winners straight into the pinned host buffers (pinned
-        # memory is device-addressable), which saves two device-to-host copies per call.
-        if h.world == 1:
-            h.head(self.x_dev, h.shard, h.n_local, col_offset=h.col_begin, out=(self.idx_host, self.val_host, self._key))
-            return
-        if h.peer is not None:
-            h.head.call_sharded(self.x_dev, h.shard, h.n_local, h.col_begin, h.peer.struct,
-                                out=(self.idx_host, self.val_host))
-            return
-        idx, val = h.step(self.x_dev)
-        self.idx_host.copy_(idx, non_blocking=True)
-        self.val_host.copy_(val, non_blocking=True)
+        self._lib = _lib.load()
+        self._h = None
+        self.stream = None
+        if head.world == 1 or head.peer is not None:
+            t = _tensor2d(head.shard)
+            exchange = ctypes.byref(head.peer.struct) if head.peer is not None else None
+            h = ctypes.c_void_p()
+            with torch.cuda.device(dev):
+                torch.cuda.synchronize()  # the workspace clear and anything else queued by torch precedes the first step
+                _lib.check(self._lib.qfg_lmhead_host_create(
+                    head.head._h, m, k, ctypes.byref(t), head.n_local, head.col_begin, head.head.workspace.data_ptr(),
+                    exchange, self.x_host.data_ptr(), self.x_dev.data_ptr(), self.idx_host.data_ptr(),
+                    self.val_host.data_ptr(), ctypes.byref(h)))
+            self._h = h
+        else:
+            self.stream = torch.cuda.Stream(device=dev)
 
     def __call__(self, x_host=None):
         """x_host: optional BF16 [m, K] host tensor to stage first (omit when the caller wrote
         `self.x_host` in place).  Returns (idx_host, val_host), valid until the next call."""
-        torch = self.head._torch
         if x_host is not None:
             self.x_host.copy_(x_host)
+        if self._h is not None:
+            rc = self._lib.qfg_lmhead_host_run(self._h)
+            if rc != 0:
+                from . import _lib
+
+                _lib.check(rc)
+            return self.idx_host, self.val_host
+        torch = self.head._torch
         with torch.cuda.stream(self.stream):
-            if self.graph is not None:
-                self.graph.replay()
-            else:
-                self._enqueue()
+            self.x_dev.copy_(self.x_host, non_blocking=True)
+            idx, val = self.head.step(self.x_dev)
+            self.idx_host.copy_(idx, non_blocking=True)
+            self.val_host.copy_(val, non_blocking=True)
         self.stream.synchronize()
         return self.idx_host, self.val_host
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h is not None:
+            self._lib.qfg_lmhead_host_destroy(h)
+            self._h = None
