@@ -431,9 +431,12 @@ def run_ours(args):
         for mm in (1, 2, 4):
             xm = W.make_x(mm, k, seed=7)
             outm = head_out(head, mm, torch)
-            msm = time_region(torch, lambda: head.head(xm, shard, n_local, col_offset=c0, out=outm), args.steps,
-                              args.warmup)
-            usm = msm * 1000.0 / args.steps
+            if mm == m:
+                usm = us_kernel  # the roofline measurement above is this case
+            else:
+                msm = time_region(torch, lambda: head.head(xm, shard, n_local, col_offset=c0, out=outm), args.steps,
+                                  args.warmup)
+                usm = msm * 1000.0 / args.steps
             per_m[f"M{mm}"] = {"us": round(usm, 2), "GBps": round(shard_bytes / usm / 1e3, 1),
                                "frac_of_measured_hbm": round(shard_bytes / usm / 1e3 / peak, 4),
                                "frac_of_8TBps": round(shard_bytes / usm / 1e3 / 8000.0, 4)}
