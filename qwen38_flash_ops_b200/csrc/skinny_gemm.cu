@@ -557,49 +557,47 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
   // of it was measured at 1.7 us per row.
   float cur_v = 0.f;
   long long cur_i = -1;
+  // what every element needs from the parameter block, read once
+  const float* const w_scale = sg.w_scale;
+  const bool fuse = p.fuse != 0, lm = p.lm != 0;
+  const int out_begin = sg.out_begin, out_end = sg.out_end;
+  const bool store = !lm || p.out[out_begin] != nullptr;
+  const long long col_offset = p.lm_col_offset;
   auto finalize = [&](int m, int c, float v) {
     const int n = n0 + c;
-    if (sg.w_scale != nullptr) v *= sg.w_scale[n];
-    if (p.fuse) {
+    if (w_scale != nullptr) v *= w_scale[n];
+    if (fuse) {
       // SharedExpertDown: routed + bf16(bf16(sum) * gate), every step rounded to BF16 (skinny_gemm.cuh:226-240)
       const float shared = RoundBf16(RoundBf16(v) * sh.gate[m]);
       v = p.routed != nullptr ? __uint_as_float(static_cast<uint32_t>(p.routed[static_cast<size_t>(m) * sg.n + n]) << 16) + shared
                               : shared;
     }
     const __nv_bfloat16 b = __float2bfloat16(v);
-    if (!p.lm || p.out[sg.out_begin] != nullptr) {
-      int j = sg.out_begin;
-      for (int i = j + 1; i < sg.out_end; ++i) {
+    if (store) {
+      int j = out_begin;
+      for (int i = j + 1; i < out_end; ++i) {
         if (n >= p.col_begin[i]) j = i;
       }
       p.out[j][static_cast<size_t>(m) * p.width[j] + (n - p.col_begin[j])] = __bfloat16_as_ushort(b);
     }
-    if (p.lm) {
+    if (lm) {
       // a thread meets the columns of a row in increasing order: strict comparison, a NaN is never replaced
       const float f = __bfloat162float(b);
       if (cur_i < 0 || f > cur_v || (f != f && cur_v == cur_v)) {
         cur_v = f;
-        cur_i = p.lm_col_offset + n;
+        cur_i = col_offset + n;
       }
     }
   };
+  // The warp's best of row m as a key whose unsigned order is the Better order (0 = no candidate): the maximum
+  // of the high words, then the maximum of the low words among the lanes that hold that high word.
   auto flush_row = [&](int m) {
-    if (!p.lm) return;
-    float v = cur_i < 0 ? -INFINITY : cur_v;
-    long long i = cur_i < 0 ? LLONG_MAX : cur_i;
-#pragma unroll 1
-    for (int off = 16; off > 0; off >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, v, off);
-      const long long oi = __shfl_xor_sync(0xffffffffu, i, off);
-      if (Better(ov, oi, v, i)) {
-        v = ov;
-        i = oi;
-      }
-    }
-    if (lane == 0) {
-      sh.best_v[warp][m] = v;
-      sh.best_i[warp][m] = i;
-    }
+    if (!lm) return;
+    const unsigned long long key = cur_i < 0 ? 0ull : PackKey(cur_v, cur_i);
+    const uint32_t hi = static_cast<uint32_t>(key >> 32);
+    const uint32_t top = __reduce_max_sync(0xffffffffu, hi);
+    const uint32_t low = __reduce_max_sync(0xffffffffu, hi == top ? static_cast<uint32_t>(key) : 0u);
+    if (lane == 0) sh.best_i[warp][m] = static_cast<long long>((static_cast<unsigned long long>(top) << 32) | low);
     cur_v = 0.f;
     cur_i = -1;
   };
@@ -645,15 +643,12 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
     auto fold_into_keys = [&]() {
       __syncthreads();
       if (tid < M) {
-        float v = sh.best_v[0][tid];
-        long long i = sh.best_i[0][tid];
-        for (int w = 1; w < (nthreads >> 5); ++w) {
-          if (Better(sh.best_v[w][tid], sh.best_i[w][tid], v, i)) {
-            v = sh.best_v[w][tid];
-            i = sh.best_i[w][tid];
-          }
+        unsigned long long best = 0ull;
+        for (int w = 0; w < (nthreads >> 5); ++w) {
+          const unsigned long long k = static_cast<unsigned long long>(sh.best_i[w][tid]);
+          best = k > best ? k : best;
         }
-        if (i != LLONG_MAX) atomicMax(p.lm_keys + tid, PackKey(v, i));
+        if (best != 0ull) atomicMax(p.lm_keys + tid, best);
         __threadfence();
       }
       __syncthreads();
