@@ -551,6 +551,12 @@ __device__ __forceinline__ bool StageX(const GemmParams& p, const Tile& tl, uint
   return StageXImpl<MODE, 1, TC>(p, tl, xs, sh);
 }
 
+// Position of column c of row m inside a row of the partial-sum array.  An MMA accumulator fragment puts the
+// lanes of a warp 16 (or 8) columns apart in rows 2t and 2t + 1, and a row is a multiple of 32 floats long, so
+// plain indexing made the 8-byte stores of a warp collide 8- to 16-way.  The exclusive-or moves column bits
+// 5-6 and row bits 1-2 into the bank bits (1-4) and stays inside the aligned group of 32 columns.
+__device__ __forceinline__ int RedCol(int c, int m) { return c ^ ((((c >> 5) & 3) << 1) ^ (((m >> 1) & 3) << 3)); }
+
 // The part of the epilogue that starts from the partial sums in shared memory: `red` holds
 // [nparts][M][TNc] floats (part w = the sum over the k-steps of K-group w), the cluster partials
 // follow it.  Every thread of the CTA must call this after a __syncthreads() that follows the
@@ -621,7 +627,7 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
       const float inv = sh.inv_scale[m];
       for (int c = tid; c < ncols; c += nthreads) {
         float sum = 0.f;
-        for (int w = 0; w < nparts; ++w) sum += red[(w * M + m) * TNc + c];
+        for (int w = 0; w < nparts; ++w) sum += red[(w * M + m) * TNc + RedCol(c, m)];
         finalize(m, c, sum * inv);
       }
       flush_row(m);
@@ -631,7 +637,7 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
       const float inv = sh.inv_scale[m];
       for (int c = tid; c < TNc; c += nthreads) {
         float sum = 0.f;
-        for (int w = 0; w < nparts; ++w) sum += red[(w * M + m) * TNc + c];
+        for (int w = 0; w < nparts; ++w) sum += red[(w * M + m) * TNc + RedCol(c, m)];
         part[m * TNc + c] = sum * inv;
       }
     }
@@ -772,8 +778,8 @@ __device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, fl
       const int per_group = G::kMmas / W;
       const int cl = wn * cols_per_warp + (j / per_group) * 8 * G::kColsPerThread + g * G::kColsPerThread + 2 * (j % per_group);
       const int m0 = 2 * t, m1 = 2 * t + 1;
-      if (m0 < M) *reinterpret_cast<float2*>(&red[(wk * M + m0) * TNc + cl]) = make_float2(acc[j][0], acc[j][2]);
-      if (m1 < M) *reinterpret_cast<float2*>(&red[(wk * M + m1) * TNc + cl]) = make_float2(acc[j][1], acc[j][3]);
+      if (m0 < M) *reinterpret_cast<float2*>(&red[(wk * M + m0) * TNc + RedCol(cl, m0)]) = make_float2(acc[j][0], acc[j][2]);
+      if (m1 < M) *reinterpret_cast<float2*>(&red[(wk * M + m1) * TNc + RedCol(cl, m1)]) = make_float2(acc[j][1], acc[j][3]);
     }
   } else {
     for (int m = 0; m < M; ++m)
@@ -1672,7 +1678,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const __gri
         const int c = wn * 128 + (l < 8 ? 16 * l + 2 * j : 16 * (l - 8) + 2 * j + 1);
 #pragma unroll
         for (int m = 0; m < kMaxRows; ++m)
-          if (m < M) red[m * TNc + c] = __uint_as_float(d[i][m]);
+          if (m < M) red[m * TNc + RedCol(c, m)] = __uint_as_float(d[i][m]);
       }
     } else {
       for (int m = 0; m < M; ++m)
@@ -1684,8 +1690,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const __gri
       for (int j = 0; j < 8; ++j) {
         const int cl = wn * 128 + g * 16 + 2 * j;
         const int m0 = 2 * t, m1 = 2 * t + 1;
-        if (m0 < M) *reinterpret_cast<float2*>(&red[(wk * M + m0) * TNc + cl]) = make_float2(acc[j][0], acc[j][2]);
-        if (m1 < M) *reinterpret_cast<float2*>(&red[(wk * M + m1) * TNc + cl]) = make_float2(acc[j][1], acc[j][3]);
+        if (m0 < M) *reinterpret_cast<float2*>(&red[(wk * M + m0) * TNc + RedCol(cl, m0)]) = make_float2(acc[j][0], acc[j][2]);
+        if (m1 < M) *reinterpret_cast<float2*>(&red[(wk * M + m1) * TNc + RedCol(cl, m1)]) = make_float2(acc[j][1], acc[j][3]);
       }
     } else {
       for (int m = 0; m < M; ++m)
