@@ -35,7 +35,7 @@ UNIT = "TB/s"
 HEAD = "C5_nvfp4_lmhead_5120x151936"
 
 
-NCU_DRAM_BYTES_PER_WEIGHT_BYTE = 1.0129  # (439.01 MB read + 4.20 MB written) / 437.58 MB of packed weights
+NCU_DRAM_BYTES_PER_WEIGHT_BYTE = 1.0121  # (438.99 MB read + 3.89 MB written) / 437.58 MB of packed weights
 
 
 def peaks():
