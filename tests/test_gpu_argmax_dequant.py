@@ -127,6 +127,22 @@ def test_dequant_slices_and_splits(cuda, mode):
         assert [o.shape[1] for o in outs] == (widths or [n_cols])
 
 
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("K", [1, 3, 6, 97])
+def test_dequant_row_counts_off_the_thread_group(cuda, mode, K):
+    """A thread converts four consecutive rows of a column chunk: row counts that are not multiples of four
+    must not lose the last rows (the kernel guards every row of the group against the row count)."""
+    rng = np.random.default_rng(300 + 10 * mode + K)
+    N = 192
+    arr, _ = U.make_weight(rng, mode, K, N)
+    w = U.dev_weight(arr, mode)
+    s = rng.uniform(0.25, 4.0, N).astype(np.float32) if mode != 0 else None
+    outs = DequantWeightBf16(N, w_scale=s)(w)
+    torch.cuda.synchronize()
+    assert outs[0].shape == (K, N)
+    assert np.array_equal(bits(outs[0]), O.dequant_weight_bf16(mode, arr, N, 0, s))
+
+
 def test_dequant_errors(cuda):
     with pytest.raises(QfgError):
         DequantWeightBf16(100)                              # not a multiple of 8
