@@ -701,22 +701,59 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
     }
     __syncthreads();
     if (sh.last) {
+      unsigned long long tail_best = 0ull;  // thread m < M: best key of row m among the shared columns
       if (p.tail_groups > 0) {
         // the partial sums of the shared columns were stored before their CTAs counted themselves in:
         // add the K slices up in order, finish those columns and fold their best into the keys
         __threadfence();
         const int n_main = sg.n - p.tail_groups * 128;
-        for (int m = 0; m < M; ++m) {
-          for (int j = tid; j < p.tail_groups * 128; j += nthreads) {
-            const int col = j & 127, tg = j >> 7;
-            const float* src = p.lm_tail + (static_cast<size_t>(tg) * p.tail_split * kMaxRows + m) * 128 + col;
+        const int tcols = p.tail_groups * 128;
+        if (tcols <= nthreads) {
+          // This runs after every other CTA has finished, so it is all on the critical path: a thread owns one
+          // column, and the loads of all its rows and slices are issued before the first sum is used (one
+          // round trip to L2 instead of one per row).  The slices are still added in slice order.
+          float sums[kMaxRows];
+#pragma unroll
+          for (int m = 0; m < kMaxRows; ++m) {
+            float part[kMaxTailSplit];
+#pragma unroll
+            for (int c = 0; c < kMaxTailSplit; ++c) {
+              part[c] = 0.f;
+              if (m < M && tid < tcols && c < p.tail_split)
+                part[c] = __ldcg(p.lm_tail + ((static_cast<size_t>(tid >> 7) * p.tail_split + c) * kMaxRows + m) * 128 + (tid & 127));
+            }
             float sum = 0.f;
-            for (int c = 0; c < p.tail_split; ++c) sum += __ldcg(src + static_cast<size_t>(c) * kMaxRows * 128);
-            finalize(m, n_main + j - n0, sum * sh.inv_scale[m]);
+#pragma unroll
+            for (int c = 0; c < kMaxTailSplit; ++c) sum += part[c];
+            sums[m] = sum;
           }
-          flush_row(m);
+#pragma unroll
+          for (int m = 0; m < kMaxRows; ++m) {
+            if (m < M) {
+              if (tid < tcols) finalize(m, n_main + tid - n0, sums[m] * sh.inv_scale[m]);
+              flush_row(m);
+            }
+          }
+        } else {
+          for (int m = 0; m < M; ++m) {
+            for (int j = tid; j < tcols; j += nthreads) {
+              const int col = j & 127, tg = j >> 7;
+              const float* src = p.lm_tail + (static_cast<size_t>(tg) * p.tail_split * kMaxRows + m) * 128 + col;
+              float sum = 0.f;
+              for (int c = 0; c < p.tail_split; ++c) sum += __ldcg(src + static_cast<size_t>(c) * kMaxRows * 128);
+              finalize(m, n_main + j - n0, sum * sh.inv_scale[m]);
+            }
+            flush_row(m);
+          }
         }
-        fold_into_keys();
+        // no other CTA is left to see these keys: they join the global ones in registers below
+        __syncthreads();
+        if (tid < M) {
+          for (int w = 0; w < (nthreads >> 5); ++w) {
+            const unsigned long long k = static_cast<unsigned long long>(sh.best_i[w][tid]);
+            tail_best = k > tail_best ? k : tail_best;
+          }
+        }
       }
       if (p.xworld > 1) {
         // Sharded head: this rank's keys go straight into every rank's exchange buffer (peer memory), then
@@ -727,7 +764,8 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
         const int par = static_cast<int>(epoch & 1u);
         __syncthreads();
         if (tid < M) {
-          const unsigned long long mine = atomicExch(p.lm_keys + tid, 0ull);
+          unsigned long long mine = atomicExch(p.lm_keys + tid, 0ull);
+          mine = tail_best > mine ? tail_best : mine;
           for (int r = 0; r < p.xworld; ++r)
             *reinterpret_cast<volatile unsigned long long*>(&p.xpeer[r]->keys[par][p.xrank][tid]) = mine;
           __threadfence_system();
@@ -761,7 +799,8 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
         __syncthreads();
       }
       if (tid < M) {
-        const unsigned long long key = atomicExch(p.lm_keys + tid, 0ull);
+        unsigned long long key = atomicExch(p.lm_keys + tid, 0ull);
+        if (p.xworld == 1) key = tail_best > key ? tail_best : key;
         const uint32_t ord = static_cast<uint32_t>(key >> 32);
         const uint32_t bits = (ord == 0xFFFFFFFFu) ? 0x7FC00000u : ((ord & 0x80000000u) ? (ord & 0x7FFFFFFFu) : ~ord);
         if (p.lm_idx != nullptr) p.lm_idx[tid] = static_cast<long long>(0xFFFFFFFFu - static_cast<uint32_t>(key));
