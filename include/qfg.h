@@ -229,7 +229,8 @@ QFG_API void qfg_lmhead_destroy(qfg_lmhead* op);
  * every other rank can address (qfg_peer_alloc / qfg_peer_open below, or any peer-mapped memory).
  * `peers[r]` is this process's address of rank r's buffer, `peers[rank]` its own.  All ranks must make
  * the same sequence of calls.  If a peer's keys do not arrive within the wait limit the call still
- * returns (the result then lacks that peer) and qfg_lmhead_exchange_status reports 1. */
+ * returns (the result then lacks that peer) and qfg_lmhead_exchange_status reports 1; qfg_lmhead_host_run
+ * returns QFG_FAIL for such a step. */
 #define QFG_MAX_RANKS 8
 typedef struct qfg_lmhead_exchange {
   int world;
@@ -241,8 +242,13 @@ QFG_API int qfg_lmhead_compute_sharded(const qfg_lmhead* op, const void* x, int6
                                        const qfg_tensor2d* weight, int64_t n, int64_t col_offset, void* workspace,
                                        const qfg_lmhead_exchange* exchange, int64_t* idx, float* val, void* logits,
                                        void* stream);
-/* 0 = every wait so far completed, 1 = a wait ran out.  Synchronises the device. */
+/* 0 = every wait so far completed, 1 = a wait ran out.  Synchronises the device.  The wait limit is the
+ * option "exchange_spin" of qfg_lmhead_set_option (polling iterations of about 50 ns; default 4194304). */
 QFG_API int qfg_lmhead_exchange_status(const void* own_buffer, int* status);
+/* Device timer (ns) of the owner's last sharded call at three points of the exchange: own keys ready, stores
+ * to all peers issued, words of all ranks seen (or given up on).  Differences separate the cost of the stores
+ * from the wait for the slowest rank.  Synchronises the device.  No counterpart in the reference. */
+QFG_API int qfg_lmhead_exchange_times(const void* own_buffer, uint64_t out[3]);
 
 /* The LM head for a caller whose activations and results live in host memory (the reference's callers
  * hand ORT host tensors for the sampled token; no counterpart in the reference library itself).

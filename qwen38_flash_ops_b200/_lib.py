@@ -10,7 +10,8 @@ import os
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libqfg_b200.so")
+# QFG_LIBRARY names another build of the same library (a measurement build, for instance)
+LIB_PATH = os.environ.get("QFG_LIBRARY") or os.path.join(_HERE, "libqfg_b200.so")
 
 QFG_OK, QFG_FAIL, QFG_INVALID_ARGUMENT = 0, 1, 2
 QFG_FLOAT, QFG_UINT8, QFG_INT64, QFG_FLOAT16, QFG_BFLOAT16, QFG_FLOAT8E4M3FN = 1, 2, 7, 10, 16, 17
@@ -28,6 +29,7 @@ EXPORTS = (
     "qfg_lmhead_compute_static", "qfg_lmhead_set_option",
     "qfg_lmhead_destroy", "qfg_lmhead_combine",
     "qfg_lmhead_exchange_bytes", "qfg_lmhead_compute_sharded", "qfg_lmhead_exchange_status",
+    "qfg_lmhead_exchange_times",
     "qfg_peer_alloc", "qfg_peer_open", "qfg_peer_close", "qfg_peer_free",
     "qfg_lmhead_host_create", "qfg_lmhead_host_run", "qfg_lmhead_host_destroy",
 )
@@ -97,6 +99,7 @@ def load() -> ctypes.CDLL:
     lib.qfg_lmhead_compute_sharded.argtypes = [c_void_p, c_void_p, c_int64, c_int64, POINTER(Tensor2D), c_int64, c_int64,
                                                c_void_p, POINTER(LmExchange), c_void_p, c_void_p, c_void_p, c_void_p]
     lib.qfg_lmhead_exchange_status.argtypes = [c_void_p, POINTER(c_int)]
+    lib.qfg_lmhead_exchange_times.argtypes = [c_void_p, POINTER(c_uint64)]
     lib.qfg_lmhead_host_create.argtypes = [c_void_p, c_int64, c_int64, POINTER(Tensor2D), c_int64, c_int64, c_void_p,
                                            POINTER(LmExchange), c_void_p, c_void_p, c_void_p, c_void_p, POINTER(c_void_p)]
     lib.qfg_lmhead_host_run.argtypes = [c_void_p]

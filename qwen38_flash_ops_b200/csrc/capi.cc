@@ -72,7 +72,7 @@ struct qfg_skinny_gemm {
   size_t w_scale_len = 0;
   int pdl_wait = 0;
   int force_slow = 0;
-  int debug = 0;
+  int exchange_spin = qfg::kExchangeSpin;  // sharded LM head: bound of the wait for a peer's keys (iterations)
   int dense_rows = -1;  // calls with more rows take the dequantise + library GEMM branch; -1 = qfg::DenseRowsDefault(mode), 0 = never
   unsigned long long phase_times = 0;  // device address given through set_option("phase_times", ...)
   std::string plan_spec;
@@ -82,7 +82,7 @@ struct qfg_skinny_gemm {
   qfg_skinny_gemm() = default;
   qfg_skinny_gemm(const qfg_skinny_gemm& o)
       : seg_outs(o.seg_outs), widths(o.widths), trigger(o.trigger), d_w_scale(o.d_w_scale), w_scale_len(o.w_scale_len),
-        pdl_wait(o.pdl_wait), force_slow(o.force_slow), debug(o.debug), dense_rows(o.dense_rows), phase_times(o.phase_times),
+        pdl_wait(o.pdl_wait), force_slow(o.force_slow), exchange_spin(o.exchange_spin), dense_rows(o.dense_rows), phase_times(o.phase_times),
         plan_spec(o.plan_spec) {}
 };
 
@@ -137,7 +137,6 @@ Prepared Prepare(const qfg_skinny_gemm& op, const void* x, int64_t m, int64_t k,
   p.trigger = op.trigger;
   p.pdl_wait = op.pdl_wait;
   p.force_slow = op.force_slow;
-  p.debug = op.debug;
   p.phase_times = reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(op.phase_times));
   int o = 0;
   size_t scale_off = 0;
@@ -314,9 +313,11 @@ int SetGemmOption(qfg_skinny_gemm* op, const char* key, const char* value) {
   const std::string k = key;
   if (k == "pdl_wait") op->pdl_wait = std::atoi(value);
   else if (k == "force_slow") op->force_slow = std::atoi(value);
-  else if (k == "debug") op->debug = std::atoi(value);
   else if (k == "dense_rows") op->dense_rows = std::atoi(value);
-  else if (k == "phase_times") op->phase_times = std::strtoull(value, nullptr, 10);
+  else if (k == "exchange_spin") op->exchange_spin = std::max(0, std::atoi(value));
+#ifdef QFG_PHASE_TIMES
+  else if (k == "phase_times") op->phase_times = std::strtoull(value, nullptr, 10);  // measurement builds only
+#endif
   else if (k == "plan") op->plan_spec = value;
   else if (k == "trigger") op->trigger = std::atoi(value);
   else return Fail(QFG_INVALID_ARGUMENT, "set_option: unknown key " + k);
@@ -332,7 +333,8 @@ int SetLastError(int code, const char* message) { return Fail(code, message); }
 // The fused LM head on a caller-chosen scratch area (see qfg_lmhead_compute).
 int LmheadComputeWithWorkspace(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
                        int64_t n, int64_t col_offset, void* workspace, size_t workspace_bytes, int64_t* idx, float* val,
-                       uint64_t* key, void* logits, void* stream, const qfg_lmhead_exchange* exchange) {
+                       uint64_t* key, void* logits, void* stream, const qfg_lmhead_exchange* exchange,
+                       unsigned int* status_out) {
   if (op == nullptr || weight == nullptr) return Fail(QFG_FAIL, "LmHead: null argument");
   try {
     if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 8 != 0)
@@ -366,6 +368,8 @@ int LmheadComputeWithWorkspace(const qfg_lmhead* op, const void* x, int64_t m, i
         throw InvalidArgument("LmHead: bad exchange (1 <= world <= 8, 0 <= rank < world)");
       pr.params.xworld = exchange->world;
       pr.params.xrank = exchange->rank;
+      pr.params.xspin = call.exchange_spin;
+      pr.params.lm_status_out = status_out;
       for (int r = 0; r < exchange->world; ++r) {
         if (exchange->peers[r] == nullptr || reinterpret_cast<uintptr_t>(exchange->peers[r]) % 8 != 0)
           throw InvalidArgument("LmHead: exchange buffers must be 8-byte aligned device pointers");
@@ -456,7 +460,7 @@ int qfg_skinny_gemm_describe(const qfg_skinny_gemm* op, int64_t k, const qfg_ten
   try {
     Prepared pr = Prepare(*op, nullptr, 1, k, weights, n_weights, nullptr, 0, false);
     const qfg::Plan plan = PlanFor(*op, pr.plan_in, qfg::kMaxRows);
-    const std::string d = qfg::DescribePlan(plan, pr.plan_in);
+    const std::string d = qfg::DescribePlan(plan, pr.plan_in) + ",trigger=" + std::to_string(op->trigger);
     std::snprintf(buf, buf_len, "%s", d.c_str());
     return QFG_OK;
   } catch (const std::exception& e) {
@@ -725,11 +729,22 @@ int qfg_lmhead_exchange_status(const void* own_buffer, int* status) {
   return QFG_OK;
 }
 
+int qfg_lmhead_exchange_times(const void* own_buffer, uint64_t out[3]) {
+  if (own_buffer == nullptr || out == nullptr) return Fail(QFG_INVALID_ARGUMENT, "LmHead: null argument");
+  const qfg::LmExchange* e = static_cast<const qfg::LmExchange*>(own_buffer);
+  unsigned long long t[3] = {0, 0, 0};
+  const cudaError_t err = cudaMemcpy(t, &e->t_ready, sizeof(t), cudaMemcpyDeviceToHost);
+  if (err != cudaSuccess) return Fail(QFG_FAIL, (std::string("LmHead: ") + cudaGetErrorString(err)).c_str());
+  for (int i = 0; i < 3; ++i) out[i] = t[i];
+  return QFG_OK;
+}
+
 struct qfg_lmhead_host {
   cudaStream_t stream = nullptr;
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
   qfg_lmhead op;  // the caller's node with pdl_wait set (shares, and does not own, its w_scale)
+  unsigned int* status_host = nullptr;  // pinned, device-addressable: 1 if the step's wait for a peer ran out
 };
 
 
@@ -742,15 +757,24 @@ int qfg_lmhead_host_create(const qfg_lmhead* op, int64_t m, int64_t k, const qfg
     return Fail(QFG_INVALID_ARGUMENT, "LmHead: null or bad host-step argument");
   if (k % 2 != 0 || reinterpret_cast<uintptr_t>(x_host) % 4 != 0 || reinterpret_cast<uintptr_t>(x_dev) % 4 != 0)
     return Fail(QFG_INVALID_ARGUMENT, "LmHead: x must be 4-byte aligned with an even K");
-  qfg_lmhead_host* h = new qfg_lmhead_host{nullptr, nullptr, nullptr, *op};
+  qfg_lmhead_host* h = new qfg_lmhead_host{nullptr, nullptr, nullptr, *op, nullptr};
   h->op.gemm.pdl_wait = 1;
+  if (exchange != nullptr && exchange->world > 1) {
+    // the sharded step reports a wait that ran out through one word of pinned memory, read after the synchronise
+    if (cudaHostAlloc(reinterpret_cast<void**>(&h->status_host), sizeof(unsigned int), cudaHostAllocMapped) != cudaSuccess) {
+      cudaGetLastError();
+      delete h;
+      return Fail(QFG_FAIL, "LmHead: cannot allocate the pinned status word");
+    }
+    *h->status_host = 0;
+  }
   const size_t x_bytes = static_cast<size_t>(m) * static_cast<size_t>(k) * 2;
   // one step: input copy, then the fused kernel as its programmatic dependent, results addressed to host memory
   auto enqueue = [&]() -> int {
     const cudaError_t err = LaunchHostRowsToDevice(x_host, x_dev, x_bytes, h->stream);
     if (err != cudaSuccess) return Fail(QFG_FAIL, std::string("LmHead: ") + cudaGetErrorString(err));
     return qfg::LmheadComputeWithWorkspace(&h->op, x_dev, m, k, weight, n, col_offset, workspace, qfg_lmhead_workspace_bytes(),
-                                           idx_host, val_host, nullptr, nullptr, h->stream, exchange);
+                                           idx_host, val_host, nullptr, nullptr, h->stream, exchange, h->status_host);
   };
   int rc = QFG_OK;
   cudaError_t err = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
@@ -782,11 +806,14 @@ int qfg_lmhead_host_run(qfg_lmhead_host* h) {
   cudaError_t err = cudaGraphLaunch(h->exec, h->stream);
   if (err == cudaSuccess) err = cudaStreamSynchronize(h->stream);
   if (err != cudaSuccess) return Fail(QFG_FAIL, std::string("LmHead: ") + cudaGetErrorString(err));
+  if (h->status_host != nullptr && *h->status_host != 0)
+    return Fail(QFG_FAIL, "LmHead: the wait for a peer's keys ran out; the result lacks that peer");
   return QFG_OK;
 }
 
 void qfg_lmhead_host_destroy(qfg_lmhead_host* h) {
   if (h == nullptr) return;
+  if (h->status_host != nullptr) cudaFreeHost(h->status_host);
   if (h->exec != nullptr) cudaGraphExecDestroy(h->exec);
   if (h->graph != nullptr) cudaGraphDestroy(h->graph);
   if (h->stream != nullptr) cudaStreamDestroy(h->stream);

@@ -14,8 +14,16 @@
 //     race; calls on one stream are ordered and safe;
 //   * it keeps what the last call left in it.  The kernel leaves the keys and the counter at
 //     zero when it finishes, and the first call on a device clears the array before use.
-// The first call on each device does that set-up (address look-up and a synchronous clear), so
-// it should be made before any stream capture begins.  No call allocates or frees anything.
+// The first call on each device does that set-up: the address look-up, a clear, and a device-wide
+// synchronisation so that the clear has finished before any kernel - on whatever stream, blocking or
+// not - can touch the array.  That first call therefore belongs before any stream capture begins.
+// No call allocates or frees anything.
+//
+// Without a caller workspace there is no room for the partial sums of the "shared tail" launch shape
+// that qfg_lmhead_compute uses for vocabularies whose 128-column groups do not divide by the SM count,
+// so this entry point runs the plain launch shape: about a tenth slower on such vocabularies, and the
+// columns the shared tail would cover are summed over K in the plain kernel's order (their logits can
+// differ from qfg_lmhead_compute's by one BF16 unit; each entry point's argmax is exact on its own logits).
 #include <cuda_runtime.h>
 
 #include <mutex>
@@ -47,6 +55,8 @@ void* ScratchForCurrentDevice() {
   void* ptr = nullptr;
   err = cudaGetSymbolAddress(&ptr, g_lmhead_static_scratch);
   if (err == cudaSuccess) err = cudaMemset(ptr, 0, kStaticScratchBytes);
+  // the clear runs on the legacy stream, which non-blocking streams do not wait for: finish it here
+  if (err == cudaSuccess) err = cudaDeviceSynchronize();
   if (err != cudaSuccess || ptr == nullptr) {
     const std::string msg = std::string("LmHead(static): scratch set-up failed: ") + cudaGetErrorString(err);
     qfg::SetLastError(QFG_FAIL, msg.c_str());

@@ -21,7 +21,8 @@ double BytesPerCol(int mode) { return mode == kBf16 ? 2.0 : mode == kFp8 ? 1.0 :
 
 int Granule(int mode, int row_align, bool direct, int wide = 1) {
   const ModeGeom g = GeomOf(mode, direct ? wide : 1);
-  if (direct) return g.cols_per_thread;  // tiles are whole thread chunks
+  if (direct && mode == kNvfp4) return 128;  // tiles are whole warp columns: aligned nibble chunks, scales in one 16-byte piece
+  if (direct) return g.cols_per_thread;      // tiles are whole thread chunks
   const int cols_per_vec = static_cast<int>(row_align / BytesPerCol(mode));
   return std::max(g.cols_per_thread, cols_per_vec);
 }
@@ -32,8 +33,9 @@ bool DirectEligible(const PlanInput& in, int wide = 1) {
   // BF16 / FP8 lanes copy their own 16 bytes; NVFP4 rows are copied as aligned 16-byte pieces
   // around chunks that may start 8 bytes off
   if (in.row_align < (in.mode == kNvfp4 ? 8 : 16)) return false;
+  if (wide != 1) return false;  // the warp-ring kernel has one thread width
   for (int s = 0; s < in.nseg; ++s) {
-    if (in.n[s] % g.cols_per_thread != 0) return false;
+    if (in.n[s] % (in.mode == kNvfp4 ? 128 : g.cols_per_thread) != 0) return false;
   }
   return true;
 }
@@ -59,13 +61,13 @@ void FitRing(const PlanInput& in, int rows, Plan* p) {
   if (p->direct) {
     // warp-private rings: as deep as the CTA's share of shared memory allows, at most 8 k-steps
     const int warps = p->warps();
-    const int per_sm = p->tc ? 1 : std::max(1, (p->wide == 2 ? 16 : 20) / warps);
+    const int per_sm = p->tc ? 1 : std::max(1, (p->wide == 2 ? 16 : kMaxWarps) / warps);
     const size_t budget = static_cast<size_t>(220 * 1024) / per_sm;
     p->ks = 1;
-    // the kernel is compiled for ring depths 8, 6, 4 and 3
+    // the warp-ring kernel is compiled for rings of 8, 6 and 4 k-steps, the tcgen05 kernel for 6, 4 and 3
     static const int kDepths[] = {8, 6, 4, 3};
     for (int d : kDepths) {
-      if (p->tc && d == 8) continue;  // the tcgen05 kernel is compiled for 6, 4 and 3
+      if (p->tc ? d == 8 : d == 3) continue;
       p->stages = d;
       if (SmemBytes(*p, in.mode, rows, in.K) <= budget) break;
     }
@@ -100,7 +102,7 @@ size_t SmemBytes(const Plan& plan, int mode, int rows, int K) {
   const int stage = (plan.rows_per_stage() * (tb + srb) + 127) & ~127;
   const int tnc = plan.wn * g.cols_per_warp;
   const int red = (plan.wk + (plan.cluster > 1 ? 1 : 0)) * rows * tnc * 4;
-  const int direct_slot = DirectSlotBytes(mode, plan.wide);
+  const int direct_slot = RingSlotBytes(mode);
   const int ring_raw = plan.direct == 2 ? 0 : plan.direct ? plan.wn * plan.wk * plan.stages * direct_slot : plan.stages * stage;
   const int ring = (std::max(ring_raw, red) + 127) & ~127;
   const int xpitch = ((kslice + 63) & ~63) + 16;
@@ -164,7 +166,7 @@ struct TunedShape {
 const TunedShape kTunedB200[] = {
     {kBf16, 5120, 1, {5120, 0, 0, 0}, "direct=2,wn=1,wk=16,cluster=1,waves=1"},
     {kFp8, 5120, 3, {8192, 1024, 1024, 0}, "direct=1,wn=1,wk=6,cluster=4,waves=1"},
-    {kNvfp4, 5120, 2, {17408, 17408, 0, 0}, "direct=1,wide=2,wn=1,wk=8,cluster=2,waves=1"},
+    {kNvfp4, 5120, 2, {17408, 17408, 0, 0}, "direct=1,wide=1,wn=2,wk=8,cluster=1,ctas=136"},
     {kNvfp4, 17408, 1, {5120, 0, 0, 0}, "direct=1,wide=1,wn=2,wk=8,cluster=6,ctas=120"},
     {kNvfp4, 5120, 1, {151936, 0, 0, 0}, "direct=1,wide=1,wn=9,wk=2,cluster=1,waves=1"},
     // one eighth of that head where the split leaves 149 column groups: 30 tiles of five groups (one of four)
@@ -180,7 +182,7 @@ Plan ChoosePlan(const PlanInput& in) {
     const int groups = in.n[0] / 128, per = groups / in.sm_count;
     if (per >= 4 && per + 1 <= 10 && groups - per * in.sm_count <= kMaxTailGroups) {
       char spec[96];
-      std::snprintf(spec, sizeof(spec), "direct=1,wide=1,wn=%d,wk=%d,cluster=1,ctas=%d", per + 1, 20 / (per + 1), in.sm_count);
+      std::snprintf(spec, sizeof(spec), "direct=1,wide=1,wn=%d,wk=%d,cluster=1,ctas=%d", per + 1, kMaxWarps / (per + 1), in.sm_count);
       Plan shared;
       if (ApplyPlanOverrides(spec, in, &shared)) return shared;
     }
@@ -207,7 +209,7 @@ Plan ChoosePlan(const PlanInput& in) {
   const int gran = Granule(in.mode, in.row_align, direct, wide);
   long long granules = 0;
   for (int s = 0; s < in.nseg; ++s) granules += (in.n[s] + gran - 1) / gran;
-  const int max_warps = direct ? (wide == 2 ? 16 : 20) : 8;
+  const int max_warps = direct ? (wide == 2 ? 16 : kMaxWarps) : 8;
   const int max_wn = direct ? 10 : 8;
   for (int c = 1; c <= 8; c *= 2) {
     if (c > 1 && in.K / c < 256) continue;
@@ -281,7 +283,7 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
   std::stringstream ss(spec);
   std::string item;
   int ctas = -1, waves = -1;
-  bool ring_given = false, wide_given = false, shape_given = false;
+  bool ring_given = false, wide_given = false, shape_given = false, gran_given = false;
   while (std::getline(ss, item, ',')) {
     const size_t eq = item.find('=');
     if (eq == std::string::npos) return false;
@@ -294,7 +296,7 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
     else if (key == "cluster") plan->cluster = val;
     else if (key == "ctas") ctas = val;
     else if (key == "waves") waves = val;
-    else if (key == "gran") plan->gran = val;
+    else if (key == "gran") { plan->gran = val; gran_given = true; }
     else if (key == "direct") plan->direct = val;
     else if (key == "wide") { plan->wide = val; wide_given = true; }
     else if (key == "tc") plan->tc = val != 0 ? 1 : 0;
@@ -313,20 +315,22 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
       return false;
     }
   }
-  if (plan->direct != 0 && ring_given && plan->stages != 3 && plan->stages != 4 && plan->stages != 6 &&
-      (plan->stages != 8 || plan->tc != 0)) {
-    return false;
+  if (plan->direct != 0 && ring_given) {
+    const int d = plan->stages;
+    if (plan->tc != 0 ? (d != 3 && d != 4 && d != 6) : (d != 4 && d != 6 && d != 8)) return false;
   }
   // 2 = register streaming (BF16 / FP8, at most 16 warps)
   if (plan->direct == 2 && (in.mode == kNvfp4 || plan->wn * plan->wk > 16)) return false;
   plan->direct = plan->direct == 2 ? 2 : plan->direct != 0 ? 1 : 0;
   if (plan->direct == 0 && plan->gran < Granule(in.mode, in.row_align, false)) plan->gran = Granule(in.mode, in.row_align, false);
   if ((plan->direct == 0 && (!pow2(plan->wn) || !pow2(plan->wk) || plan->wn * plan->wk > 8)) || plan->wn < 1 || plan->wk < 1 ||
-      plan->warps() > (plan->wide == 2 ? 16 : 20) || plan->wn > 12 || plan->ks < 1 || plan->ks > 8 ||
+      plan->warps() > (plan->wide == 2 ? 16 : kMaxWarps) || plan->wn > 12 || plan->ks < 1 || plan->ks > 8 ||
       plan->stages < 2 || plan->stages > 8 || plan->cluster < 1 || plan->cluster > 8) {
     return false;
   }
-  if (plan->gran % Granule(in.mode, in.row_align, plan->direct != 0, plan->wide) != 0) plan->gran = Granule(in.mode, in.row_align, plan->direct != 0, plan->wide);
+  // the column granule belongs to the kernel: an override that changes the kernel takes that kernel's granule
+  if (!gran_given || plan->gran % Granule(in.mode, in.row_align, plan->direct != 0, plan->wide) != 0)
+    plan->gran = Granule(in.mode, in.row_align, plan->direct != 0, plan->wide);
   if (!ring_given) FitRing(in, in.max_rows, plan);
   const ModeGeom g = GeomOf(in.mode, plan->direct ? plan->wide : 1);
   int total = ctas > 0 ? std::max(1, ctas / plan->cluster) : 0;
@@ -336,7 +340,7 @@ bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan
     Plan full = *plan;
     if (!ring_given) FitRing(in, kMaxRows, &full);
     const size_t smem = SmemBytes(full, in.mode, kMaxRows, in.K);
-    const int per_sm = std::max(1, std::min(20 / (plan->wn * plan->wk), static_cast<int>((220 * 1024) / std::max<size_t>(smem, 1))));
+    const int per_sm = std::max(1, std::min(kMaxWarps / (plan->wn * plan->wk), static_cast<int>((220 * 1024) / std::max<size_t>(smem, 1))));
     int cluster_slots;
     if (in.max_clusters != nullptr) {
       cluster_slots = in.max_clusters(in.mode, plan->tc ? 3 : plan->direct == 2 ? 4 : plan->direct * plan->wide, plan->threads(), smem,

@@ -14,6 +14,10 @@ namespace qfg {
 constexpr int kMaxSeg = QFG_MAX_WEIGHTS;
 constexpr int kMaxOut = QFG_MAX_OUTPUTS;
 constexpr int kMaxRows = 8;  // rows of x one launch handles (the n = 8 side of m16n8k16)
+#ifndef QFG_MAX_WARPS
+#define QFG_MAX_WARPS 20
+#endif
+constexpr int kMaxWarps = QFG_MAX_WARPS;  // warps per CTA of the warp-ring kernel (sets its register budget)
 
 enum WeightMode : int { kBf16 = 0, kFp8 = 1, kNvfp4 = 2 };
 
@@ -34,7 +38,9 @@ inline ModeGeom GeomOf(int mode, int wide = 1) {
     default: return wide == 2 ? ModeGeom{16, 8, 256, 128} : ModeGeom{16, 8, 128, 64};
   }
 }
-// Bytes of one warp's ring slot (one k-step) in the direct kernel.
+// Bytes of one k-step of one warp in the ring of the direct kernel.
+inline int RingSlotBytes(int mode) { return mode == kNvfp4 ? 1584 : 2048; }
+// The same for the tcgen05 kernel, which keeps the older slot layout.
 inline int DirectSlotBytes(int mode, int wide) {
   if (mode != kNvfp4) return 4 * 32 * 16;
   const int w = wide == 2 ? 2 : 1;
@@ -84,6 +90,8 @@ struct Segment {
   int svec = 4;   // cp.async width for the NVFP4 scale bytes of a row
 };
 
+constexpr int kExchangeSpin = 1 << 22;  // default bound of the wait for a peer's words (iterations of about 50 ns)
+
 struct GemmParams {
   const uint16_t* x = nullptr;  // BF16 [M, K]
   int M = 0;
@@ -96,8 +104,7 @@ struct GemmParams {
   int trigger = 0;
   int pdl_wait = 0;
   int force_slow = 0;  // testing: always take the BF16-MMA path of the quantised modes
-  int debug = 0;       // unused by the kernels (kept for option compatibility)
-  unsigned long long* phase_times = nullptr;  // measurement aid: [CTA][16] timer stamps and cycle counts of the direct / tcgen05 kernels
+  unsigned long long* phase_times = nullptr;  // [CTA][16] timer stamps; written only by builds with -DQFG_PHASE_TIMES
   // plan
   int wn = 4, wk = 2, ks = 1, stages = 4, cluster = 1, gran = 16;
   int xpitch = 0;       // elements per x row in shared memory
@@ -134,18 +141,20 @@ struct GemmParams {
   // Key exchange of the N-sharded LM head through peer memory (world > 1): xpeer[r] is rank r's buffer.
   int xworld = 1;
   int xrank = 0;
+  int xspin = kExchangeSpin;              // iterations a thread waits for one word of a peer
+  unsigned int* lm_status_out = nullptr;  // optional (host-mapped) word: 1 if a wait ran out in this call, else 0
   struct LmExchange* xpeer[8] = {};
 };
 
-// One rank's exchange buffer.  Slots alternate with the parity of the call count, so a rank that is one
-// call ahead never overwrites keys a slower rank has not read yet.
+// One rank's exchange buffer.  A word is (upper or lower half of a key) << 32 | call count of the writer, so
+// its arrival validates itself.  Slots alternate with the parity of the call count, so a rank that is one
+// call ahead never overwrites words a slower rank has not read yet.
 struct LmExchange {
-  unsigned long long keys[2][8][kMaxRows];  // [parity][source rank][row]
-  unsigned int flags[2][8];                 // [parity][source rank] = call count of the writer
-  unsigned int epoch;                       // calls made by the owner
-  unsigned int status;                      // 1 after a wait that ran out
+  unsigned long long words[2][8][kMaxRows][2];  // [parity][source rank][row][half]
+  unsigned int epoch;                           // calls made by the owner
+  unsigned int status;                          // 1 after a wait that ran out (until the host clears it)
+  unsigned long long t_ready, t_sent, t_done;   // %globaltimer of the owner's last call: keys ready, stores issued, all words seen
 };
-constexpr int kExchangeSpin = 1 << 22;
 
 constexpr int kMaxTailGroups = 8;
 constexpr int kMaxTailSplit = 8;
@@ -192,7 +201,7 @@ cudaError_t LaunchLmheadCombine(const uint64_t* keys, int ranks, int64_t m, int6
 int LmheadComputeWithWorkspace(const qfg_lmhead* op, const void* x, int64_t m, int64_t k, const qfg_tensor2d* weight,
                                int64_t n, int64_t col_offset, void* workspace, size_t workspace_bytes, int64_t* idx,
                                float* val, uint64_t* key, void* logits, void* stream,
-                               const qfg_lmhead_exchange* exchange = nullptr);
+                               const qfg_lmhead_exchange* exchange = nullptr, unsigned int* status_out = nullptr);
 int SetLastError(int code, const char* message);
 
 // dequant_bf16.cu

@@ -37,6 +37,8 @@
 #include <map>
 #include <mutex>
 #include <tuple>
+#include <type_traits>
+#include <utility>
 
 #include "qfg_internal.h"
 
@@ -45,8 +47,7 @@ namespace {
 
 namespace cg = cooperative_groups;
 
-constexpr int kMaxThreads = 640;      // direct kernel: up to 20 warps (at most 102 registers per thread)
-constexpr int kMaxThreadsWide = 512;  // its 32-columns-per-thread NVFP4 variant: up to 16 warps (128 registers)
+constexpr int kMaxThreads = 32 * kMaxWarps;  // warp-ring and tcgen05 kernels (20 warps: at most 102 registers per thread)
 constexpr int kRingThreads = 256;  // ring kernel: up to 8 warps
 
 // ------------------------------------------------------------------------------ PTX helpers
@@ -89,6 +90,38 @@ __device__ __forceinline__ uint32_t Lds8(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
+}
+// shared-memory loads at a register address plus a compile-time offset (folded into the instruction)
+template <int OFF>
+__device__ __forceinline__ uint4 Lds128At(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint2 Lds64At(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t Lds8At(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+// 16 bytes from `base + off` to shared memory at `dst + OFF`; CACHED keeps the line in L1 (.ca) for neighbours
+template <int OFF, bool CACHED>
+__device__ __forceinline__ void CpAsync16At(uint32_t dst, const uint8_t* base, uint32_t off) {
+  if constexpr (CACHED) {
+    asm volatile("{ .reg .u64 a;\n mad.wide.u32 a, %2, 1, %1;\n cp.async.ca.shared.global [%0+%3], [a], 16;\n}" ::"r"(dst), "l"(base),
+                 "r"(off), "n"(OFF)
+                 : "memory");
+  } else {
+    asm volatile("{ .reg .u64 a;\n mad.wide.u32 a, %2, 1, %1;\n cp.async.cg.shared.global [%0+%3], [a], 16;\n}" ::"r"(dst), "l"(base),
+                 "r"(off), "n"(OFF)
+                 : "memory");
+  }
 }
 __device__ __forceinline__ uint4 Ldg128(const void* p) {
   uint4 v;
@@ -137,6 +170,12 @@ __device__ __forceinline__ uint32_t CvtE4m3x2(uint32_t pair16) {
   asm("{ .reg .b16 h0;\n cvt.u16.u32 h0, %1;\n cvt.rn.f16x2.e4m3x2 %0, h0;\n}" : "=r"(r) : "r"(pair16));
   return r;
 }
+// (a & mask) | (b & ~mask) in one instruction
+__device__ __forceinline__ uint32_t BitSelect(uint32_t a, uint32_t b, uint32_t mask) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xE4;" : "=r"(r) : "r"(a), "r"(b), "r"(mask));
+  return r;
+}
 __device__ __forceinline__ uint32_t Hmul2(uint32_t a, uint32_t b) {
   uint32_t r;
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
@@ -152,17 +191,13 @@ __device__ __forceinline__ uint32_t HalfPairToBf16Pair(uint32_t h) {
 template <bool BF16>
 __device__ __forceinline__ void Mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                     uint32_t b1) {
-#ifdef QFG_EXPERIMENT_NO_MMA
-  asm volatile("" ::"r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-  return;
-#endif
   if constexpr (BF16) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
   } else {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -270,10 +305,10 @@ __device__ __forceinline__ void ComputeStep(float (&acc)[Geom<MODE, W>::kMmas][4
       for (int i = 0; i < 2; ++i) {
         // byte q of `e_*`: (row A nibble, row B nibble) of column 8i + 2q; of `o_*`: column 8i + 2q + 1
         uint32_t e_ab[4], o_ab[4], e_cd[4], o_cd[4];
-        CvtE2m1x8((a[i] & 0x0F0F0F0Fu) | ((b[i] << 4) & 0xF0F0F0F0u), e_ab);
-        CvtE2m1x8(((a[i] >> 4) & 0x0F0F0F0Fu) | (b[i] & 0xF0F0F0F0u), o_ab);
-        CvtE2m1x8((c[i] & 0x0F0F0F0Fu) | ((d[i] << 4) & 0xF0F0F0F0u), e_cd);
-        CvtE2m1x8(((c[i] >> 4) & 0x0F0F0F0Fu) | (d[i] & 0xF0F0F0F0u), o_cd);
+        CvtE2m1x8(BitSelect(a[i], b[i] << 4, 0x0F0F0F0Fu), e_ab);
+        CvtE2m1x8(BitSelect(a[i] >> 4, b[i], 0x0F0F0F0Fu), o_ab);
+        CvtE2m1x8(BitSelect(c[i], d[i] << 4, 0x0F0F0F0Fu), e_cd);
+        CvtE2m1x8(BitSelect(c[i] >> 4, d[i], 0x0F0F0F0Fu), o_cd);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint32_t a0 = Hmul2(e_ab[q], s_ab), a1 = Hmul2(o_ab[q], s_ab);
@@ -324,6 +359,7 @@ struct SharedScratch {
   long long best_i[kMaxThreads / 32][kMaxRows];
   float gate[kMaxRows];  // SharedExpertDown: the BF16 sigmoid gate of every row (best_v holds its partial sums first)
   int last;
+  int xfail;  // sharded LM head: a wait for a peer's keys ran out in this call
 };
 
 // The BF16 arithmetic of SharedExpertDown (src/common/sigmoid_acc.cuh:12-21, skinny_gemm.cuh:73-80): sigmoid
@@ -379,6 +415,8 @@ template <int MODE, int WORDS, bool TC = false, bool FUSE = false, bool WALK = t
 __device__ __forceinline__ bool StageXImpl(const GemmParams& p, const Tile& tl, uint16_t* xs, SharedScratch& sh) {
   constexpr int kElems = 2 * WORDS;
   constexpr int kBatch = 4;
+  // a CTA whose K slice is empty (more cluster ranks than k-steps) stages nothing and adds nothing
+  if (tl.kslice <= 0) return false;
   const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31;
   const int M = p.M, xpitch = p.xpitch;
   const int kpad = (tl.kslice + 15) & ~15;
@@ -755,52 +793,74 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
           }
         }
       }
+      unsigned long long key = 0ull;  // thread m < M: the winning key of row m
       if (p.xworld > 1) {
-        // Sharded head: this rank's keys go straight into every rank's exchange buffer (peer memory), then
-        // the keys of all ranks are awaited - bounded - in the own buffer and folded; the maximum of the
-        // order-preserving keys is the Better order, so every rank ends with the same winner.
+        // Sharded head: this rank's keys go straight into every rank's exchange buffer (peer memory) as
+        // self-validating words - (upper or lower half of the key) << 32 | call count - so that one round of
+        // 8-byte stores carries both the data and the signal that it has arrived: no fence, no separate flag.
+        // Slots alternate with the parity of the call count: a rank that is one call ahead writes the other
+        // slot.  Every rank then awaits - bounded - the words of all ranks in its own buffer and folds them;
+        // the maximum of the order-preserving keys is the Better order, so every rank ends with the same
+        // winner.  A wait that runs out sets the buffer's status and the row is folded without that peer.
         LmExchange* own = p.xpeer[p.xrank];
         const unsigned int epoch = own->epoch + 1;  // every thread reads it before thread 0 advances it below
         const int par = static_cast<int>(epoch & 1u);
-        __syncthreads();
         if (tid < M) {
           unsigned long long mine = atomicExch(p.lm_keys + tid, 0ull);
-          mine = tail_best > mine ? tail_best : mine;
-          for (int r = 0; r < p.xworld; ++r)
-            *reinterpret_cast<volatile unsigned long long*>(&p.xpeer[r]->keys[par][p.xrank][tid]) = mine;
-          __threadfence_system();
+          sh.best_i[0][tid] = static_cast<long long>(tail_best > mine ? tail_best : mine);
         }
+        if (tid == 0) sh.xfail = 0;
         __syncthreads();
+        unsigned long long t_ready = 0, t_sent = 0;
+        if (tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_ready));
+        const int nwords = 2 * M * p.xworld;
+        for (int w = tid; w < nwords; w += nthreads) {
+          const int r = w / (2 * M), rem = w - r * 2 * M, row = rem >> 1, half = rem & 1;
+          const unsigned long long k = static_cast<unsigned long long>(sh.best_i[0][row]);
+          const unsigned long long payload = half ? (k & 0xFFFFFFFFull) : (k >> 32);
+          *reinterpret_cast<volatile unsigned long long*>(&p.xpeer[r]->words[par][p.xrank][row][half]) = (payload << 32) | epoch;
+        }
         if (tid == 0) {
           own->epoch = epoch;
-          __threadfence_system();  // release: the key stores the barrier made visible to this thread precede the flags
-          for (int r = 0; r < p.xworld; ++r) *reinterpret_cast<volatile unsigned int*>(&p.xpeer[r]->flags[par][p.xrank]) = epoch;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_sent));
         }
-        if (tid < p.xworld) {
-          const volatile unsigned int* flag = &own->flags[par][tid];
+        for (int w = tid; w < nwords; w += nthreads) {
+          const int r = w / (2 * M), rem = w - r * 2 * M, row = rem >> 1, half = rem & 1;
+          const volatile unsigned long long* word = &own->words[par][r][row][half];
           int spin = 0;
-          while (*flag != epoch && spin < kExchangeSpin) {
+          while (static_cast<unsigned int>(*word) != epoch && spin < p.xspin) {
             ++spin;
-            __nanosleep(64);
+            __nanosleep(32);
           }
-          if (*flag != epoch) own->status = 1;
-          __threadfence_system();
+          if (static_cast<unsigned int>(*word) != epoch) {
+            own->status = 1;
+            sh.xfail = 1;
+          }
         }
         __syncthreads();
         if (tid < M) {
-          unsigned long long best = 0ull;
           for (int r = 0; r < p.xworld; ++r) {
-            const bool arrived = *reinterpret_cast<const volatile unsigned int*>(&own->flags[par][r]) == epoch;
-            const unsigned long long k = *reinterpret_cast<const volatile unsigned long long*>(&own->keys[par][r][tid]);
-            if (arrived && k > best) best = k;
+            const unsigned long long w0 = *reinterpret_cast<const volatile unsigned long long*>(&own->words[par][r][tid][0]);
+            const unsigned long long w1 = *reinterpret_cast<const volatile unsigned long long*>(&own->words[par][r][tid][1]);
+            const bool arrived = static_cast<unsigned int>(w0) == epoch && static_cast<unsigned int>(w1) == epoch;
+            const unsigned long long k = (w0 & 0xFFFFFFFF00000000ull) | (w1 >> 32);
+            if (arrived && k > key) key = k;
           }
-          p.lm_keys[tid] = best;  // decoded and cleared right below
         }
-        __syncthreads();
+        if (tid == 0) {
+          // telemetry of the owner's last call: keys ready, stores issued, all words seen (or given up on)
+          unsigned long long t_done;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_done));
+          own->t_ready = t_ready;
+          own->t_sent = t_sent;
+          own->t_done = t_done;
+          if (p.lm_status_out != nullptr) *p.lm_status_out = static_cast<unsigned int>(sh.xfail);
+        }
+      } else if (tid < M) {
+        key = atomicExch(p.lm_keys + tid, 0ull);
+        key = tail_best > key ? tail_best : key;
       }
       if (tid < M) {
-        unsigned long long key = atomicExch(p.lm_keys + tid, 0ull);
-        if (p.xworld == 1) key = tail_best > key ? tail_best : key;
         const uint32_t ord = static_cast<uint32_t>(key >> 32);
         const uint32_t bits = (ord == 0xFFFFFFFFu) ? 0x7FC00000u : ((ord & 0x80000000u) ? (ord & 0x7FFFFFFFu) : ~ord);
         if (p.lm_idx != nullptr) p.lm_idx[tid] = static_cast<long long>(0xFFFFFFFFu - static_cast<uint32_t>(key));
@@ -866,7 +926,9 @@ __device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, fl
 //     groups a warp-wide shared-memory load touches into distinct banks.
 // A lane owns up to kPieces pieces; their sources are one 64-bit base, advanced by a k-step
 // stride per step, plus a 32-bit offset each.
-// Measurement aid: thread 0 of every CTA records the global timer at the phase boundaries.
+// Measurement aid, compiled in only with -DQFG_PHASE_TIMES: thread 0 of every CTA records the global timer
+// at the phase boundaries into GemmParams::phase_times ([CTA][16]).
+#ifdef QFG_PHASE_TIMES
 __device__ __forceinline__ void Stamp(const GemmParams& p, int slot) {
   if (p.phase_times != nullptr && threadIdx.x == 0) {
     unsigned long long t;
@@ -874,6 +936,9 @@ __device__ __forceinline__ void Stamp(const GemmParams& p, int slot) {
     p.phase_times[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16 + slot] = t;
   }
 }
+#else
+__device__ __forceinline__ void Stamp(const GemmParams&, int) {}
+#endif
 template <typename T>
 __device__ __forceinline__ void Pin(T& v) {
   asm volatile("" : "+r"(v));  // keeps a loop invariant in its register instead of being recomputed
@@ -1035,14 +1100,212 @@ struct Nvfp4Stream {
   }
 };
 
+// One warp's stream through its shared-memory ring: copy plan, read offsets and the K loop.
+//
+// A loop iteration handles a PAIR of the warp's k-steps (2 x 16 weight rows): one cp.async wait, one warp
+// barrier, the copies of the pair DEPTH - 1 pairs ahead, then all shared-memory loads of both steps and
+// their dequantisation and MMAs, which the compiler interleaves.  The body is not unrolled over the ring -
+// the ring position is one register added to the few per-lane address registers - because the K loop runs
+// out of the instruction cache of an SM sub-partition: a body over about 8 KB was measured 5-25 % slower.
+//
+// Slot of one k-step (RingSlot).  NVFP4 (column tiles start on multiples of 128 columns): 16 rows of
+// 5 aligned 16-byte pieces around the row's 64 nibble bytes - the fifth is needed only where the chunk
+// starts 8 bytes off a 16-byte boundary (odd rows of a weight whose packed pitch is 8 mod 16, like the
+// 151936-column LM head) - then 16 rows of the one aligned piece that holds the row's 8 scale bytes:
+// 96 pieces, three per lane (piece index lane + 32 j).  A lane whose index names an unneeded piece repeats
+// piece 0 of that row (same source, same destination), so no copy is predicated.  Rows 8..15 of both
+// areas are displaced (32 / 16 bytes), which puts the four rows a warp-wide load touches into distinct
+// banks.  BF16 / FP8: [4 rows][32 lanes][16 bytes], a lane copies exactly the bytes it consumes.
+// The last k-step of a K slice is copied by a careful path (rows past K read as zero, pieces clamped to
+// the end of the tensor); a pair that contains it, or has no second step, takes that path for both steps.
+template <int MODE>
+struct RingSlot {
+  static constexpr int kNibPitch = 80;
+  static constexpr int kNibBytes = MODE == kNvfp4 ? 16 * kNibPitch + 32 : 4 * 32 * 16;
+  static constexpr int kSclPitch = 16;
+  static constexpr int kSclBytes = MODE == kNvfp4 ? 16 * kSclPitch + 16 : 0;
+  static constexpr int kBytes = kNibBytes + kSclBytes;
+  static constexpr int NP = MODE == kNvfp4 ? 3 : 4;
+  __device__ static constexpr int NibRow(int r) { return r * kNibPitch + ((r >> 3) & 1) * 32; }
+  __device__ static constexpr int SclRow(int r) { return kNibBytes + r * kSclPitch + ((r >> 3) & 1) * 16; }
+};
+static_assert(RingSlot<kNvfp4>::kBytes == 1584 && RingSlot<kBf16>::kBytes == 2048, "keep RingSlotBytes() in step");
 
-template <int MODE, int DEPTH, int W>
-__global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) SkinnyGemmDirectKernel(const __grid_constant__ GemmParams p) {
-  using G = Geom<MODE, W>;
-  using S = DirectSlot<MODE, W>;
+template <int NP>
+struct CopyPieces {
+  uint32_t off[NP], dst[NP];
+};
+// Copies up to two consecutive local steps (those below `nsteps`) piece by piece with clamped sizes.
+template <int NP>
+__device__ __noinline__ void IssueCareful(const uint8_t* w, long long total_bytes, const uint8_t* gbase, long long step_stride,
+                                          int kend, int row0, int row_step, uint32_t rows, CopyPieces<NP> pc, uint32_t slot_off,
+                                          uint32_t slot_bytes, int s0, int nsteps) {
+  for (int e = 0; e < 2; ++e) {
+    if (s0 + e < nsteps) {
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const int r = static_cast<int>((rows >> (4 * j)) & 15u);
+        const uint8_t* src = gbase + pc.off[j];
+        const long long room = total_bytes - (src - w);
+        const int bytes = (row0 + r >= kend) ? 0 : room >= 16 ? 16 : room > 0 ? static_cast<int>(room) : 0;
+        CpAsync16(pc.dst[j] + slot_off, bytes > 0 ? src : w, bytes);
+      }
+    }
+    gbase += step_stride;
+    row0 += row_step;
+    slot_off += slot_bytes;
+  }
+}
+
+template <int MODE, int DEPTH>
+struct WarpRing {
+  using S = RingSlot<MODE>;
+  static constexpr int NP = S::NP;
+  static constexpr int kPairBytes = 2 * S::kBytes;
+  static_assert(DEPTH >= 2 && DEPTH <= 4, "ring depth in pairs of k-steps");
+
+  const uint8_t* gbase;  // next step to copy, less 16 bytes (piece offsets are unsigned)
+  long long step_stride;
+  CopyPieces<NP> pc;     // dst includes the ring's address
+  uint32_t off2[NP];     // pc.off + step_stride: the second step of a pair
+  uint32_t rd_w[2], rd_s[2], rows;
+  int nsteps, nfast, row_next, row_step;
+
+  // Local step s is k-step k_first + s * k_stride of the CTA's K slice, k_count steps in all.  `colwarp`:
+  // first column of the warp; `lane_cols_ok`: the lane's own columns exist (BF16 / FP8 lanes past the
+  // tile's last column copy the warp's first chunk instead; their sums are never stored).
+  __device__ __forceinline__ void Setup(const Tile& tl, const Segment& sg, int colwarp, bool lane_cols_ok, int k_first,
+                                        int k_count, int k_stride, uint32_t ring) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const long long pitch = sg.pitch;
+    const int ksteps = (tl.kslice + 15) >> 4;
+    nsteps = k_count;
+    const int last = ksteps - 1 - k_first;
+    const bool has_last = k_count > 0 && last >= 0 && last % k_stride == 0 && last / k_stride < k_count;
+    nfast = has_last ? last / k_stride : nsteps;
+    row_next = tl.kbeg + k_first * 16;
+    row_step = k_stride * 16;
+    step_stride = static_cast<long long>(k_stride) * 16 * pitch;
+    rows = 0;
+    if constexpr (MODE == kNvfp4) {
+      const long long warp_col_byte = colwarp / 2;  // a multiple of 64
+      gbase = sg.w + static_cast<long long>(row_next) * pitch + warp_col_byte - 16;
+      const int mis = static_cast<int>(pitch & 8);  // odd rows start 8 bytes off a 16-byte boundary
+      const long long sabs = static_cast<long long>(sg.n >> 1) + (colwarp >> 4);  // scale bytes within the row: 0 or 8 mod 16
+      const int so_even = static_cast<int>(sabs & 15), so_odd = static_cast<int>((sabs + mis) & 15);
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const int q = lane + 32 * j;
+        if (q < 80) {
+          const int r = q / 5;
+          int c = q - r * 5;
+          const int shift = (r & 1) ? mis : 0;
+          if (c == 4 && shift == 0) c = 0;
+          pc.off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (c * 16 - shift) + 16);
+          pc.dst[j] = ring + static_cast<uint32_t>(S::NibRow(r) + c * 16);
+          rows |= static_cast<uint32_t>(r) << (4 * j);
+        } else {
+          const int r = q - 80;
+          const int o = (r & 1) ? so_odd : so_even;
+          pc.off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (sabs - o - warp_col_byte) + 16);
+          pc.dst[j] = ring + static_cast<uint32_t>(S::SclRow(r));
+          rows |= static_cast<uint32_t>(r) << (4 * j);
+        }
+      }
+      const int rbase = S::NibRow(4 * t) + g * 8, sbase = S::SclRow(4 * t) + g;
+      rd_w[0] = ring + static_cast<uint32_t>(rbase);
+      rd_w[1] = ring + static_cast<uint32_t>(rbase + mis);
+      rd_s[0] = ring + static_cast<uint32_t>(sbase + so_even);
+      rd_s[1] = ring + static_cast<uint32_t>(sbase + so_odd);
+    } else {
+      const long long warp_col_byte = MODE == kBf16 ? static_cast<long long>(colwarp) * 2 : colwarp;
+      gbase = sg.w + static_cast<long long>(row_next) * pitch + warp_col_byte - 16;
+      const int gsrc = lane_cols_ok ? g : 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        pc.off[i] = static_cast<uint32_t>(static_cast<long long>(4 * t + i) * pitch + gsrc * 16 + 16);
+        pc.dst[i] = ring + static_cast<uint32_t>(i * 512 + lane * 16);
+        rows |= static_cast<uint32_t>(4 * t + i) << (4 * i);
+      }
+      rd_w[0] = rd_w[1] = ring + static_cast<uint32_t>(lane * 16);
+      rd_s[0] = rd_s[1] = 0;
+    }
+#pragma unroll
+    for (int j = 0; j < NP; ++j) off2[j] = pc.off[j] + static_cast<uint32_t>(step_stride);
+  }
+
+  // copies the pair of local steps (s0, s0 + 1) - the next ones in order - into the slots at `slot_off`
+  __device__ __forceinline__ void IssuePair(const Tile& tl, const Segment& sg, int s0, uint32_t slot_off) {
+    if (s0 + 1 < nfast) {
+#pragma unroll
+      for (int j = 0; j < NP; ++j) CpAsync16At<0, false>(pc.dst[j] + slot_off, gbase, pc.off[j]);
+#pragma unroll
+      for (int j = 0; j < NP; ++j) CpAsync16At<S::kBytes, false>(pc.dst[j] + slot_off, gbase, off2[j]);
+    } else if (s0 < nsteps) {
+      IssueCareful<NP>(sg.w, sg.total_bytes, gbase, step_stride, tl.kend, row_next, row_step, rows, pc, slot_off,
+                       static_cast<uint32_t>(S::kBytes), s0, nsteps);
+    }
+    gbase += 2 * step_stride;
+    row_next += 2 * row_step;
+  }
+
+  // the first DEPTH - 1 pairs in flight
+  __device__ __forceinline__ void Prologue(const Tile& tl, const Segment& sg) {
+#pragma unroll
+    for (int d = 0; d < DEPTH - 1; ++d) {
+      IssuePair(tl, sg, 2 * d, static_cast<uint32_t>(d * kPairBytes));
+      CpAsyncCommit();
+    }
+  }
+
+  template <int OFF>
+  __device__ __forceinline__ void LoadStep(Raw<MODE, 1>& raw, uint32_t w0, uint32_t w1, uint32_t s0, uint32_t s1) const {
+    if constexpr (MODE == kNvfp4) {
+      raw.r[0][0] = Lds64At<OFF>(w0);
+      raw.r[0][1] = Lds64At<OFF + S::kNibPitch>(w1);
+      raw.r[0][2] = Lds64At<OFF + 2 * S::kNibPitch>(w0);
+      raw.r[0][3] = Lds64At<OFF + 3 * S::kNibPitch>(w1);
+      raw.s[0][0] = Lds8At<OFF>(s0);
+      raw.s[0][1] = Lds8At<OFF + S::kSclPitch>(s1);
+      raw.s[0][2] = Lds8At<OFF + 2 * S::kSclPitch>(s0);
+      raw.s[0][3] = Lds8At<OFF + 3 * S::kSclPitch>(s1);
+    } else {
+      raw.r[0] = Lds128At<OFF>(w0);
+      raw.r[1] = Lds128At<OFF + 512>(w0);
+      raw.r[2] = Lds128At<OFF + 1024>(w0);
+      raw.r[3] = Lds128At<OFF + 1536>(w0);
+    }
+  }
+
+  // consume(raw_a, raw_b, has_b) for every pair of local steps in order, DEPTH - 1 pairs behind the copies
+  template <class F>
+  __device__ __forceinline__ void Run(const Tile& tl, const Segment& sg, F&& consume) {
+    const int npairs = (nsteps + 1) >> 1;
+    uint32_t rd_off = 0, wr_off = static_cast<uint32_t>((DEPTH - 1) * kPairBytes);
+    for (int i = 0; i < npairs; ++i) {
+      asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 2) : "memory");
+      __syncwarp();  // every lane's copies of this pair are visible, and every lane is done reading the previous pair
+      IssuePair(tl, sg, 2 * (i + DEPTH - 1), wr_off);
+      CpAsyncCommit();
+      Raw<MODE, 1> raw_a, raw_b;
+      const uint32_t w0 = rd_w[0] + rd_off, w1 = rd_w[1] + rd_off, s0 = rd_s[0] + rd_off, s1 = rd_s[1] + rd_off;
+      LoadStep<0>(raw_a, w0, w1, s0, s1);
+      LoadStep<S::kBytes>(raw_b, w0, w1, s0, s1);
+      consume(raw_a, raw_b, 2 * i + 1 < nsteps);
+      wr_off = rd_off;
+      rd_off += kPairBytes;
+      if (rd_off == static_cast<uint32_t>(DEPTH * kPairBytes)) rd_off = 0;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  }
+};
+
+// DEPTH: pairs of k-steps in every warp's ring (2, 3 or 4)
+template <int MODE, int DEPTH>
+__global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const __grid_constant__ GemmParams p) {
+  using G = Geom<MODE, 1>;
+  using S = RingSlot<MODE>;
   constexpr int NM = G::kMmas;
-  constexpr int CB = G::kBytesPerThread;
-  constexpr int NP = S::kPieces;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ SharedScratch sh;
 
@@ -1053,120 +1316,38 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
   const int wn = warp % p.wn, wk = warp / p.wn;
   const Tile tl = LocateTile(p);
   const Segment& sg = p.seg[tl.seg];
-  const long long pitch = sg.pitch;
 
   // this thread's columns and this warp's k-steps (local step s is k-step wk + s * p.wk of the slice)
-  const int cols_per_warp = 8 * G::kColsPerThread * W;
+  constexpr int cols_per_warp = 8 * G::kColsPerThread;
   const int colwarp = tl.n0 + wn * cols_per_warp;
-  const int colbase = colwarp + g * G::kColsPerThread;
   const bool warp_has_cols = colwarp < tl.n1;
-  const bool cvalid = colbase < tl.n1;
+  const bool cvalid = colwarp + g * G::kColsPerThread < tl.n1;
   const int ksteps = (tl.kslice + 15) >> 4;
-  const int nsteps = (warp_has_cols && ksteps > wk) ? (ksteps - wk + p.wk - 1) / p.wk : 0;
-  // The last k-step of the slice is copied by a careful path: rows past K (K not a multiple of
-  // 16) must read as zero and aligned pieces must not run past the end of the tensor.
-  const int careful_step = (((ksteps - 1) % p.wk) == wk) ? nsteps - 1 : -1;
-  const int row0 = tl.kbeg + wk * 16;  // first weight row of this warp's local step 0 (a multiple of 16)
-  const long long step_stride = static_cast<long long>(p.wk) * 16 * pitch;
-  const uint32_t ring = SmemAddr(smem) + static_cast<uint32_t>(warp) * (DEPTH * S::kBytes);
+  const uint32_t ring_addr = SmemAddr(smem) + static_cast<uint32_t>(warp) * (DEPTH * 2 * S::kBytes);
 
-  // ---- copy plan of this lane: source offset from `gbase`, destination offset in the slot
-  const long long warp_col_byte = MODE == kBf16 ? static_cast<long long>(colwarp) * 2 : MODE == kFp8 ? colwarp : colwarp / 2;
-  const uint8_t* gbase = sg.w + static_cast<long long>(row0) * pitch + warp_col_byte - 16;
-  uint32_t off[NP], dst[NP], pmask = 0;
-  uint32_t rd_w[2], rd_s[2];  // read offsets of the even and the odd rows of this lane
+  // Shared tail of the fused LM head: a warp without columns of the tile (the last warp column of the CTA)
+  // streams one K slice of one left-over column group through the same loop and stores FP32 partial sums.
+  bool tail_worker = false;
+  int tail_index = 0, first_step = wk, step_stride = p.wk, step_count = (warp_has_cols && ksteps > wk) ? (ksteps - wk + p.wk - 1) / p.wk : 0;
+  int stream_col = colwarp;
   if constexpr (MODE == kNvfp4) {
-    const int mis = static_cast<int>(pitch & 8);              // odd rows start 8 bytes off a 16-byte boundary
-    const int cshift = static_cast<int>(warp_col_byte & 8);   // so does a chunk whose first column is 16 mod 32
-    const long long sabs = static_cast<long long>(sg.n >> 1) + (colwarp >> 4);  // scale bytes within the row
-    const int so_even = static_cast<int>(sabs & 15), so_odd = static_cast<int>((sabs + mis) & 15);
-    const int sh_even = cshift, sh_odd = (mis + cshift) & 15;
-#pragma unroll
-    for (int j = 0; j < NP; ++j) {
-      const int slot = lane + 32 * j;
-      const int r = slot / S::kPiecesPerRow, c = slot - r * S::kPiecesPerRow;
-      off[j] = 0;
-      dst[j] = 0;
-      if (r < 16) {
-        if (c < 4 * W + 1) {  // nibble piece c of row r
-          const int shift = (r & 1) ? sh_odd : sh_even;
-          if (c < 4 * W || shift != 0) pmask |= 1u << j;
-          off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (c * 16 - shift) + 16);
-          dst[j] = static_cast<uint32_t>(S::NibRow(r) + c * 16);
-        } else {  // the aligned 16 bytes that hold (c2 = 0) or follow (c2 = 1) the first scale byte
-          const int c2 = c - (4 * W + 1);
-          const int o = (r & 1) ? so_odd : so_even;
-          if (c2 == 0 || o + 8 * W > 16) pmask |= 1u << j;
-          off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (sabs - o + c2 * 16 - warp_col_byte) + 16);
-          dst[j] = static_cast<uint32_t>(S::SclRow(r) + c2 * 16);
-        }
+    if (p.tail_groups > 0 && !warp_has_cols && wn == p.wn - 1) {
+      tail_index = static_cast<int>(blockIdx.x) * p.wk + wk;  // one (group, K slice) per idle warp
+      if (tail_index < p.tail_groups * p.tail_split) {
+        tail_worker = true;
+        const int tg = tail_index / p.tail_split, slice = tail_index - tg * p.tail_split;
+        first_step = static_cast<int>(static_cast<long long>(slice) * ksteps / p.tail_split);
+        step_count = static_cast<int>(static_cast<long long>(slice + 1) * ksteps / p.tail_split) - first_step;
+        step_stride = 1;
+        stream_col = sg.n - p.tail_groups * 128 + tg * 128;
       }
     }
-    const int rbase = S::NibRow(4 * t) + g * CB, sbase = S::SclRow(4 * t) + g;
-    rd_w[0] = static_cast<uint32_t>(rbase + sh_even);
-    rd_w[1] = static_cast<uint32_t>(rbase + sh_odd);
-    rd_s[0] = static_cast<uint32_t>(sbase + so_even);
-    rd_s[1] = static_cast<uint32_t>(sbase + so_odd);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      off[i] = static_cast<uint32_t>(static_cast<long long>(4 * t + i) * pitch + g * CB + 16);
-      dst[i] = static_cast<uint32_t>(i * (32 * CB) + lane * CB);
-    }
-    if (cvalid) pmask = 0xF;
-    rd_w[0] = rd_w[1] = static_cast<uint32_t>(lane * CB);
-    rd_s[0] = rd_s[1] = 0;
-    if (!cvalid && warp_has_cols) {
-      // lanes past the tile's last column copy nothing: their share of the ring reads as zero
-      for (int d = 0; d < DEPTH; ++d)
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(ring + d * S::kBytes + dst[i]), "r"(0) : "memory");
-    }
   }
-#pragma unroll
-  for (int j = 0; j < NP; ++j) {
-    Pin(off[j]);
-    Pin(dst[j]);
-  }
-  Pin(pmask);
-  Pin(rd_w[0]);
-  Pin(rd_w[1]);
-  Pin(rd_s[0]);
-  Pin(rd_s[1]);
-
-  // copies local step s into the slot at `slot_addr`
-  auto issue_step = [&](int s, uint32_t slot_addr) {
-    if (s != careful_step) {
-#pragma unroll
-      for (int j = 0; j < NP; ++j) CpAsync16If(pmask & (1u << j), slot_addr + dst[j], gbase, off[j]);
-    } else {
-      const int r0 = row0 + s * p.wk * 16;
-#pragma unroll
-      for (int j = 0; j < NP; ++j) {
-        if (pmask & (1u << j)) {
-          int r;  // row of the step this piece belongs to
-          if constexpr (MODE == kNvfp4) {
-            r = (lane + 32 * j) / S::kPiecesPerRow;
-          } else {
-            r = 4 * t + j;
-          }
-          const uint8_t* src = gbase + off[j];
-          const long long room = sg.total_bytes - (src - sg.w);
-          const int bytes = (r0 + r >= tl.kend) ? 0 : room >= 16 ? 16 : room > 0 ? static_cast<int>(room) : 0;
-          CpAsync16(slot_addr + dst[j], bytes > 0 ? src : sg.w, bytes);
-        }
-      }
-    }
-    gbase += step_stride;
-  };
 
   // weights do not depend on the predecessor kernel: get the first k-steps in flight, then wait
-#pragma unroll
-  for (int d = 0; d < DEPTH - 1; ++d) {
-    if (d < nsteps) issue_step(d, ring + d * S::kBytes);
-    CpAsyncCommit();
-  }
+  WarpRing<MODE, DEPTH> ring;
+  ring.Setup(tl, sg, stream_col, cvalid, first_step, step_count, step_stride, ring_addr);
+  ring.Prologue(tl, sg);
   if (p.pdl_wait) GridDependencyWait();
   Stamp(p, 1);
 
@@ -1181,43 +1362,20 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
     for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
 
   // lanes whose x row does not exist read row 0; their accumulators are never stored
-  uint32_t x_rd = SmemAddr(xs) + static_cast<uint32_t>(((g < p.M ? g : 0) * p.xpitch + 4 * t + wk * 16) * 2);
-  uint32_t x_step = static_cast<uint32_t>(p.wk) * 32u;
-  Pin(x_step);
-  const uint32_t ring_end = ring + DEPTH * S::kBytes;
-  uint32_t rd_slot = ring;                               // slot of step s
-  uint32_t wr_slot = ring + (DEPTH - 1) * S::kBytes;     // slot of step s - 1, refilled with step s + DEPTH - 1
-  // One copy of the loop per operand path: the loop body then holds a single dequantisation and stays
-  // half as large (the loop's speed was seen to depend on its code footprint).
+  uint32_t x_rd = SmemAddr(xs) + static_cast<uint32_t>(((g < p.M ? g : 0) * p.xpitch + 4 * t + first_step * 16) * 2);
+  const uint32_t x_step = static_cast<uint32_t>(step_stride) * 32u;
+  // One copy of the loop per operand path: the loop body then holds a single dequantisation.
   auto k_loop = [&](auto slow_tag) {
-    for (int s = 0; s < nsteps; ++s) {
-      __syncwarp();
-      if (s + DEPTH - 1 < nsteps) issue_step(s + DEPTH - 1, wr_slot);
-      CpAsyncCommit();
-      asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
-      __syncwarp();
-      Raw<MODE, W> raw;
-  #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        if constexpr (MODE == kNvfp4) {
-          const uint32_t wa = rd_slot + rd_w[i & 1] + i * S::kNibPitch;
-          const uint32_t sa = rd_slot + rd_s[i & 1] + i * S::kSclPitch;
-  #pragma unroll
-          for (int h = 0; h < W; ++h) {
-            raw.r[h][i] = Lds64(wa + h * 64);
-            raw.s[h][i] = Lds8(sa + h * 8);
-          }
-        } else {
-          raw.r[i] = Lds128(rd_slot + rd_w[0] + i * (32 * CB));
-        }
+    constexpr bool kSlow = decltype(slow_tag)::value;
+    ring.Run(tl, sg, [&](const Raw<MODE, 1>& raw_a, const Raw<MODE, 1>& raw_b, bool has_b) {
+      const uint2 xa = Lds64(x_rd);
+      ComputeStep<MODE, kSlow, 1>(acc, raw_a, xa.x, xa.y);
+      if (has_b) {  // warp-uniform
+        const uint2 xb = Lds64(x_rd + x_step);
+        ComputeStep<MODE, kSlow, 1>(acc, raw_b, xb.x, xb.y);
       }
-      const uint2 xv = Lds64(x_rd);
-      x_rd += x_step;
-      wr_slot = rd_slot;
-      rd_slot += S::kBytes;
-      if (rd_slot == ring_end) rd_slot = ring;
-      ComputeStep<MODE, decltype(slow_tag)::value, W>(acc, raw, xv.x, xv.y);
-    }
+      x_rd += 2 * x_step;
+    });
   };
   if constexpr (MODE == kBf16) {
     k_loop(std::false_type{});
@@ -1228,44 +1386,15 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
       k_loop(std::false_type{});
     }
   }
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
-  if constexpr (MODE == kNvfp4 && W == 1) {
-    if (p.tail_groups > 0 && !warp_has_cols && wn == p.wn - 1) {
-      // Shared tail of the fused LM head: this warp has no columns of the tile, so it computes this CTA's
-      // share of the K range of the left-over column groups and stores the partial sums.
-      const int worker = static_cast<int>(blockIdx.x) * p.wk + wk;  // one (group, K slice) per idle warp
-      const int n_main = sg.n - p.tail_groups * 128;
-      const int x_row = g < p.M ? g : 0;
-      if (worker < p.tail_groups * p.tail_split) {
-        const int tg = worker / p.tail_split, slice = worker - tg * p.tail_split;
-        const int k0 = static_cast<int>(static_cast<long long>(slice) * ksteps / p.tail_split);
-        const int k1 = static_cast<int>(static_cast<long long>(slice + 1) * ksteps / p.tail_split);
-        Nvfp4Stream<DEPTH> ts;
-        ts.SetupRange(tl, sg, n_main + tg * 128, k0, k1 - k0, 1, ring);
-        ts.Prologue(p, tl, sg);
-        // this warp's own accumulators are unused (it has no columns): accumulate the tail in them
+  if constexpr (MODE == kNvfp4) {
+    if (tail_worker) {
+      float* dstp = p.lm_tail + static_cast<size_t>(tail_index) * kMaxRows * 128;
 #pragma unroll
-        for (int j = 0; j < NM; ++j)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
-        uint32_t xr = SmemAddr(xs) + static_cast<uint32_t>((x_row * p.xpitch + 4 * t + k0 * 16) * 2);
-        ts.Run(p, tl, sg, [&](const Raw<kNvfp4, 1>& raw, int) {
-          const uint2 xv = Lds64(xr);
-          xr += 32;
-          if (slow) {
-            ComputeStep<kNvfp4, true, 1>(acc, raw, xv.x, xv.y);
-          } else {
-            ComputeStep<kNvfp4, false, 1>(acc, raw, xv.x, xv.y);
-          }
-        });
-        float* dstp = p.lm_tail + static_cast<size_t>(worker) * kMaxRows * 128;
-#pragma unroll
-        for (int j = 0; j < NM; ++j) {
-          const int cl = g * 16 + 2 * j;
-          const int m0 = 2 * t, m1 = 2 * t + 1;
-          if (m0 < p.M) *reinterpret_cast<float2*>(&dstp[m0 * 128 + cl]) = make_float2(acc[j][0], acc[j][2]);
-          if (m1 < p.M) *reinterpret_cast<float2*>(&dstp[m1 * 128 + cl]) = make_float2(acc[j][1], acc[j][3]);
-        }
+      for (int j = 0; j < NM; ++j) {
+        const int cl = g * 16 + 2 * j;
+        const int m0 = 2 * t, m1 = 2 * t + 1;
+        if (m0 < p.M) *reinterpret_cast<float2*>(&dstp[m0 * 128 + cl]) = make_float2(acc[j][0], acc[j][2]);
+        if (m1 < p.M) *reinterpret_cast<float2*>(&dstp[m1 * 128 + cl]) = make_float2(acc[j][1], acc[j][3]);
       }
       __threadfence();
     }
@@ -1274,9 +1403,10 @@ __global__ void __launch_bounds__(W == 2 ? kMaxThreadsWide : kMaxThreads, 1) Ski
   if (p.trigger == 2) GridLaunchDependents();
   __syncthreads();
   Stamp(p, 4);
-  Epilogue<MODE, W>(p, tl, acc, smem, sh, warp_has_cols);
+  Epilogue<MODE, 1>(p, tl, acc, smem, sh, warp_has_cols);
   Stamp(p, 5);
 }
+
 
 // ------------------------------------------------------------------------------ register-streaming kernel
 // BF16 / FP8 only.  Every warp loads its rows straight into registers with 128-bit non-allocating
@@ -1487,10 +1617,10 @@ __device__ __forceinline__ void Nvfp4Fragments(const Raw<kNvfp4, 1>& w, uint32_t
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     uint32_t e_ab[4], o_ab[4], e_cd[4], o_cd[4];
-    CvtE2m1x8((a[i] & 0x0F0F0F0Fu) | ((b[i] << 4) & 0xF0F0F0F0u), e_ab);
-    CvtE2m1x8(((a[i] >> 4) & 0x0F0F0F0Fu) | (b[i] & 0xF0F0F0F0u), o_ab);
-    CvtE2m1x8((c[i] & 0x0F0F0F0Fu) | ((d[i] << 4) & 0xF0F0F0F0u), e_cd);
-    CvtE2m1x8(((c[i] >> 4) & 0x0F0F0F0Fu) | (d[i] & 0xF0F0F0F0u), o_cd);
+    CvtE2m1x8(BitSelect(a[i], b[i] << 4, 0x0F0F0F0Fu), e_ab);
+    CvtE2m1x8(BitSelect(a[i] >> 4, b[i], 0x0F0F0F0Fu), o_ab);
+    CvtE2m1x8(BitSelect(c[i], d[i] << 4, 0x0F0F0F0Fu), e_cd);
+    CvtE2m1x8(BitSelect(c[i] >> 4, d[i], 0x0F0F0F0Fu), o_cd);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       uint32_t a0 = Hmul2(e_ab[q], s_ab), a1 = Hmul2(o_ab[q], s_ab);
@@ -1593,8 +1723,6 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const __gri
     const uint32_t a_base = tmem + static_cast<uint32_t>(d_cols + unit * kTcBuffers * 32) + (static_cast<uint32_t>(32 * q) << 16);
     const uint32_t full0 = SmemAddr(&tc.full[unit][0]), empty0 = SmemAddr(&tc.empty[unit][0]);
     int b = 0, round = 0;  // buffer of step s and how many times the buffers were cycled
-    long long t_empty = 0, t_store = 0;
-    const bool probe = p.phase_times != nullptr && warp == 0 && lane == 0;
     auto publish = [&](const Raw<kNvfp4, 1>* raw) {
       uint32_t fr[8][4];
       if (raw != nullptr) {
@@ -1604,9 +1732,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const __gri
           Nvfp4Fragments<false>(*raw, fr);
         }
       }
-      const long long c0 = probe ? clock64() : 0;
       if (round > 0 && !MbarWait(empty0 + b * 8, static_cast<uint32_t>((round - 1) & 1))) tc.fault = 1;
-      const long long c1 = probe ? clock64() : 0;
       if (raw != nullptr) {
         TcFenceAfter();
         const uint32_t ta = a_base + static_cast<uint32_t>(b * 32);
@@ -1617,10 +1743,6 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const __gri
       }
       __syncwarp();
       if (lane == 0) MbarArrive(full0 + b * 8);
-      if (probe) {
-        t_empty += c1 - c0;
-        t_store += clock64() - c1;
-      }
       if (++b == kTcBuffers) {
         b = 0;
         ++round;
@@ -1631,19 +1753,12 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const __gri
     } else {
       for (int s = 0; s < proto_steps; ++s) publish(nullptr);
     }
-    if (probe) {
-      unsigned long long* o = p.phase_times + (static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16;
-      o[6] = static_cast<unsigned long long>(t_empty);
-      o[7] = static_cast<unsigned long long>(t_store);
-    }
   } else if (is_issuer) {
     if (lane == 0) {
       const uint32_t idesc = 0x10u | (2u << 17) | (8u << 24) | (slow ? ((1u << 7) | (1u << 10)) : 0u);
       const uint32_t xa = SmemAddr(xs);
       const int max_steps = (ksteps + p.wk - 1) / p.wk;
       int b = 0, round = 0;
-      long long t_full = 0, t_issue = 0;
-      const bool probe = p.phase_times != nullptr;
       for (int s = 0; s < max_steps; ++s) {
         for (int wkI = 0; wkI < p.wk; ++wkI) {
           const int kk = wkI + s * p.wk;
@@ -1654,9 +1769,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const __gri
                                           (static_cast<unsigned long long>(256 >> 4) << 32) | (1ull << 46);
           for (int gi = 0; gi < ngroups; ++gi) {
             const int u = wkI * ngroups + gi;
-            const long long c0 = probe ? clock64() : 0;
             if (!MbarWait(SmemAddr(&tc.full[u][b]), static_cast<uint32_t>(round & 1))) tc.fault = 1;
-            const long long c1 = probe ? clock64() : 0;
             TcFenceAfter();
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -1671,10 +1784,6 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const __gri
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                              SmemAddr(&tc.empty[u][b]))
                          : "memory");
-            if (probe) {
-              t_full += c1 - c0;
-              t_issue += clock64() - c1;
-            }
           }
         }
         if (++b == kTcBuffers) {
@@ -1684,11 +1793,6 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const __gri
       }
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(SmemAddr(&tc.done))
                    : "memory");
-      if (probe) {
-        unsigned long long* o = p.phase_times + (static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16;
-        o[8] = static_cast<unsigned long long>(t_full);
-        o[9] = static_cast<unsigned long long>(t_issue);
-      }
     }
     __syncwarp();
   } else {
@@ -1958,23 +2062,21 @@ cudaError_t ConfigureKernel(K kernel) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn);
 }
 
-template <int MODE, int W>
+template <int MODE>
 cudaError_t ConfigureDirect() {
-  cudaError_t err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 3, W>);
-  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 4, W>);
-  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 6, W>);
-  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 8, W>);
+  cudaError_t err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 2>);
+  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 3>);
+  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 4>);
   return err;
 }
 
-// the direct kernel is compiled for ring depths 3, 4, 6 and 8
-template <int MODE, int W>
-cudaError_t LaunchDirect(const cudaLaunchConfig_t* cfg, int depth, const GemmParams& p) {
-  switch (depth) {
-    case 3: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 3, W>, p);
-    case 4: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 4, W>, p);
-    case 6: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 6, W>, p);
-    case 8: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 8, W>, p);
+// the direct kernel is compiled for rings of 4, 6 and 8 k-steps (2, 3, 4 pairs)
+template <int MODE>
+cudaError_t LaunchDirect(const cudaLaunchConfig_t* cfg, int stages, const GemmParams& p) {
+  switch (stages) {
+    case 4: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 2>, p);
+    case 6: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 3>, p);
+    case 8: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 4>, p);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -2016,9 +2118,8 @@ cudaError_t LaunchMode(const GemmParams& p, const Plan& plan, size_t smem, cudaS
           default: return cudaErrorInvalidValue;
         }
       }
-      if (plan.wide == 2) return LaunchDirect<MODE, 2>(&cfg, plan.stages, p);
     }
-    return LaunchDirect<MODE, 1>(&cfg, plan.stages, p);
+    return LaunchDirect<MODE>(&cfg, plan.stages, p);
   }
   return cudaLaunchKernelEx(&cfg, SkinnyGemmRingKernel<MODE>, p);
 }
@@ -2048,18 +2149,17 @@ int QueryMaxActiveClusters(int mode, int direct, int threads, size_t smem, int c
   switch (mode) {
     case kBf16:
       fn = direct == 4 ? (const void*)SkinnyGemmRegKernel<kBf16>
-           : direct    ? (const void*)SkinnyGemmDirectKernel<kBf16, 4, 1>
+           : direct    ? (const void*)SkinnyGemmDirectKernel<kBf16, 2>
                        : (const void*)SkinnyGemmRingKernel<kBf16>;
       break;
     case kFp8:
       fn = direct == 4 ? (const void*)SkinnyGemmRegKernel<kFp8>
-           : direct    ? (const void*)SkinnyGemmDirectKernel<kFp8, 4, 1>
+           : direct    ? (const void*)SkinnyGemmDirectKernel<kFp8, 2>
                        : (const void*)SkinnyGemmRingKernel<kFp8>;
       break;
     default:
       fn = direct == 3   ? (const void*)SkinnyGemmTcKernel<4>
-           : direct == 2 ? (const void*)SkinnyGemmDirectKernel<kNvfp4, 4, 2>
-           : direct == 1 ? (const void*)SkinnyGemmDirectKernel<kNvfp4, 4, 1>
+           : direct >= 1 ? (const void*)SkinnyGemmDirectKernel<kNvfp4, 2>
                          : (const void*)SkinnyGemmRingKernel<kNvfp4>;
       break;
   }
@@ -2097,10 +2197,9 @@ cudaError_t ConfigureSkinnyGemmKernels() {
   static std::once_flag once;
   static cudaError_t status = cudaSuccess;
   std::call_once(once, [] {
-    status = ConfigureDirect<kBf16, 1>();
-    if (status == cudaSuccess) status = ConfigureDirect<kFp8, 1>();
-    if (status == cudaSuccess) status = ConfigureDirect<kNvfp4, 1>();
-    if (status == cudaSuccess) status = ConfigureDirect<kNvfp4, 2>();
+    status = ConfigureDirect<kBf16>();
+    if (status == cudaSuccess) status = ConfigureDirect<kFp8>();
+    if (status == cudaSuccess) status = ConfigureDirect<kNvfp4>();
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRegKernel<kBf16>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRegKernel<kFp8>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmTcKernel<3>);
@@ -2127,7 +2226,7 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
   p.stage_bytes = (R * (p.tile_row_bytes + p.scale_row_bytes) + 127) & ~127;
   const int TNc = PlanMaxCols(plan, mode);
   const int red_bytes = (plan.wk + (plan.cluster > 1 ? 1 : 0)) * p.M * TNc * 4;
-  const int direct_slot = DirectSlotBytes(mode, plan.wide);
+  const int direct_slot = plan.tc ? DirectSlotBytes(mode, 1) : RingSlotBytes(mode);
   const int ring_warps = plan.tc ? plan.wn * plan.wk + plan.wk : plan.wn * plan.wk;
   const int ring = plan.direct == 2 ? 0 : plan.direct ? ring_warps * plan.stages * direct_slot : plan.stages * p.stage_bytes;
   p.ring_bytes = (std::max(ring, red_bytes) + 127) & ~127;

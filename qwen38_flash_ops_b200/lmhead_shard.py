@@ -86,6 +86,17 @@ class PeerExchange:
         _lib.check(self._lib.qfg_lmhead_exchange_status(self.own, ctypes.byref(s)))
         return s.value
 
+    def times(self):
+        """Device timer (ns) of this rank's last sharded call: (keys ready, stores to the peers issued, all
+        ranks' words seen).  Synchronises the device."""
+        import ctypes
+
+        from . import _lib
+
+        t = (ctypes.c_uint64 * 3)()
+        _lib.check(self._lib.qfg_lmhead_exchange_times(self.own, t))
+        return int(t[0]), int(t[1]), int(t[2])
+
     def close(self):
         for ptr in self._opened:
             self._lib.qfg_peer_close(ptr)
@@ -140,14 +151,20 @@ class ShardedLmHead:
     def column_range(n_total: int, rank: int, world: int, granule: int = 128):
         return packing.shard_columns(n_total, world, granule)[rank]
 
-    def step(self, x):
+    def step(self, x, checked: bool = False):
         """x: BF16 [m, K] on this rank's GPU (replicated).  Returns (idx int64 [m], val float32 [m]),
-        identical on every rank."""
+        identical on every rank.  `checked` (peer-memory exchange only): synchronise and raise if a wait for a
+        peer's keys ran out, in which case the ranks may hold different winners."""
         from .ops import lmhead_combine
 
         torch = self._torch
         if self.peer is not None:
-            return self.head.call_sharded(x, self.shard, self.n_local, self.col_begin, self.peer.struct)
+            out = self.head.call_sharded(x, self.shard, self.n_local, self.col_begin, self.peer.struct)
+            if checked and self.peer.status() != 0:
+                from ._lib import QFG_FAIL, QfgError
+
+                raise QfgError(QFG_FAIL, "LmHead: the wait for a peer's keys ran out; the result lacks that peer")
+            return out
         idx, val, key = self.head(x, self.shard, self.n_local, col_offset=self.col_begin)
         if self.world == 1:
             return idx, val

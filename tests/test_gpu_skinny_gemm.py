@@ -95,18 +95,20 @@ def test_every_plan_shape(cuda, mode, plan):
     run_case(rng, mode, 3, 2304, [[1280, 256], [512]], with_scale=True, plan=plan)
 
 
-@pytest.mark.parametrize("wide", [1, 2])
+@pytest.mark.parametrize("stages", [4, 6, 8])
 @pytest.mark.parametrize("plan", [
-    "wn=1,wk=16,cluster=1", "wn=2,wk=4,cluster=2", "wn=5,wk=3,cluster=1,stages=3", "wn=1,wk=2,cluster=8,stages=8",
-    "wn=3,wk=4,cluster=1,stages=6,ctas=7"])
-def test_nvfp4_thread_widths_on_misaligned_rows(cuda, wide, plan):
-    """Both thread widths of the NVFP4 direct kernel, on weights whose packed row pitch is 8 mod 16
-    (odd rows start half a 16-byte piece off, as in the 151936-column LM head) and on one whose
-    pitch is 0 mod 16, with K not a multiple of 16 (zero-filled last k-step)."""
-    rng = np.random.default_rng(sum(map(ord, plan)) + wide)
-    spec = f"direct=1,wide={wide}," + plan
+    "wn=1,wk=16,cluster=1", "wn=2,wk=4,cluster=2", "wn=5,wk=3,cluster=1", "wn=1,wk=2,cluster=8",
+    "wn=3,wk=4,cluster=1,ctas=7"])
+def test_nvfp4_ring_depths_on_misaligned_rows(cuda, stages, plan):
+    """Every ring depth of the NVFP4 warp-ring kernel (2, 3 and 4 pairs of k-steps), on weights whose packed
+    row pitch is 8 mod 16 (odd rows start half a 16-byte piece off, as in the 151936-column LM head) and on
+    one whose pitch is 0 mod 16, with K not a multiple of 16 (zero-filled last k-step) and with odd and even
+    numbers of k-steps per warp (a last pair with a single step)."""
+    rng = np.random.default_rng(sum(map(ord, plan)) + stages)
+    spec = f"direct=1,stages={stages}," + plan
     run_case(rng, 2, 3, 2312, [[640, 384], [896]], plan=spec)
     run_case(rng, 2, 8, 1000, [[1280], [128, 128]], plan=spec)
+    run_case(rng, 2, 2, 16 * 7, [[384]], plan=spec)
 
 
 @pytest.mark.parametrize("mode", [0, 1, 2])
@@ -430,3 +432,20 @@ def test_dense_branch_tiles_wide_outputs_and_skips_odd_widths(cuda):
     one = op2(to_dev(x[17:18], "bf16"), U.dev_weight(w2, 0))
     torch.cuda.synchronize()
     assert np.array_equal(bits(one[0]).reshape(-1), bits(out2[0]).reshape(M, 100)[17])
+
+
+def test_trigger_attribute_and_its_environment_override(cuda, monkeypatch):
+    """SKINNY_TRIGGER_FORCE=<n> replaces a non-zero `trigger` attribute when the node is created and leaves a
+    zero attribute alone (fused_gemm.cu:105-113)."""
+    w = to_dev(np.zeros((64, 128), np.uint16), "bf16")
+
+    def resolved(trigger):
+        fields = dict(item.split("=") for item in SkinnyGemm([1], [128], trigger=trigger).describe(64, w).split(","))
+        return int(fields["trigger"])
+
+    monkeypatch.delenv("SKINNY_TRIGGER_FORCE", raising=False)
+    assert [resolved(t) for t in (0, 1, 2)] == [0, 1, 2]
+    monkeypatch.setenv("SKINNY_TRIGGER_FORCE", "1")
+    assert [resolved(t) for t in (0, 1, 2)] == [0, 1, 1]
+    monkeypatch.setenv("SKINNY_TRIGGER_FORCE", "0")
+    assert [resolved(t) for t in (0, 2)] == [0, 0]
