@@ -242,7 +242,7 @@ qfg::Plan ComputePlan(const qfg_skinny_gemm& op, const qfg::PlanInput& in) {
     if (e != nullptr) spec = e;
   }
   if (!spec.empty() && !qfg::ApplyPlanOverrides(spec, in, &plan)) throw InvalidArgument("SkinnyGemm: bad plan override");
-  qfg::ChooseTail(in, spec.find("tail=") != std::string::npos, &plan);
+  qfg::FinishPlan(in, spec, &plan);
   return plan;
 }
 
@@ -496,7 +496,7 @@ int qfg_plan_describe(int dtype, int64_t k, const int64_t* n, int nseg, int row_
   qfg::Plan plan = qfg::ChoosePlan(in);
   if (!overrides.empty() && !qfg::ApplyPlanOverrides(overrides, in, &plan))
     return Fail(QFG_INVALID_ARGUMENT, "plan_describe: bad plan override");
-  qfg::ChooseTail(in, overrides.find("tail=") != std::string::npos, &plan);
+  qfg::FinishPlan(in, overrides, &plan);
   std::string d = qfg::DescribePlan(plan, in);
   d += ",seg_tiles=";
   for (int s = 0; s < nseg; ++s) d += (s ? "/" : "") + std::to_string(plan.tiles[s]);

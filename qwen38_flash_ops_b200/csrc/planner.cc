@@ -66,10 +66,12 @@ void FitRing(const PlanInput& in, int rows, Plan* p) {
     p->ks = 1;
     // the warp-ring kernel is compiled for rings of 8, 6 and 4 k-steps, the tcgen05 kernel for 6, 4 and 3
     static const int kDepths[] = {8, 6, 4, 3};
+    // NVFP4 warp rings keep their scale bytes in L1: stay within the carve-out that leaves L1 room where a depth fits it
+    const size_t want = (in.mode == kNvfp4 && !p->tc) ? std::min(budget, kL1FriendlySmem) : budget;
     for (int d : kDepths) {
       if (p->tc ? d == 8 : d == 3) continue;
       p->stages = d;
-      if (SmemBytes(*p, in.mode, rows, in.K) <= budget) break;
+      if (SmemBytes(*p, in.mode, rows, in.K) <= want) break;
     }
     return;
   }
@@ -377,6 +379,10 @@ void ChooseTail(const PlanInput& in, bool forced, Plan* plan) {
   if (tail < 1 || tail > kMaxTailGroups || tail >= groups || (groups - tail) % ctas != 0) return;
   if ((groups - tail) / ctas > plan->wn - 1) return;
   plan->tail = tail;
+}
+
+void FinishPlan(const PlanInput& in, const std::string& spec, Plan* plan) {
+  ChooseTail(in, spec.find("tail=") != std::string::npos, plan);
 }
 
 std::string DescribePlan(const Plan& plan, const PlanInput& in) {

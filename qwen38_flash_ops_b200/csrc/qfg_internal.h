@@ -38,6 +38,11 @@ inline ModeGeom GeomOf(int mode, int wide = 1) {
     default: return wide == 2 ? ModeGeom{16, 8, 256, 128} : ModeGeom{16, 8, 128, 64};
   }
 }
+// Dynamic shared memory up to which a CTA leaves the SM a useful L1 (the 164 KB carve-out less the kernels' static
+// shared memory).  The NVFP4 warp rings copy their scale bytes through L1, where the four column warps that share a
+// 32-byte sector of scales fetch it from L2 once; with a larger carve-out the lines are evicted before they are shared
+// and the same copies were measured 40 % slower, so the ring depth stays within this budget.
+constexpr size_t kL1FriendlySmem = 161 * 1024;
 // Bytes of one k-step of one warp in the ring of the direct kernel.
 inline int RingSlotBytes(int mode) { return mode == kNvfp4 ? 1584 : 2048; }
 // The same for the tcgen05 kernel, which keeps the older slot layout.
@@ -107,6 +112,7 @@ struct GemmParams {
   unsigned long long* phase_times = nullptr;  // [CTA][16] timer stamps; written only by builds with -DQFG_PHASE_TIMES
   // plan
   int wn = 4, wk = 2, ks = 1, stages = 4, cluster = 1, gran = 16;
+  int scales_l1 = 0;    // NVFP4 warp rings: copy the scale pieces through L1 (set where the CTA's shared memory leaves L1 room)
   int xpitch = 0;       // elements per x row in shared memory
   int ring_bytes = 0;   // stages * stage_bytes
   int stage_bytes = 0;
@@ -179,6 +185,8 @@ Plan ChoosePlan(const PlanInput& in);
 // Applies "key=value,..." overrides (wn, wk, ks, stages, cluster, ctas, gran); returns false on a bad key.
 bool ApplyPlanOverrides(const std::string& spec, const PlanInput& in, Plan* plan);
 void FitRing(const PlanInput& in, int rows, Plan* plan);
+// The decisions that follow the launch shape (`spec`: the override string): the shared tail of a fused LM head.
+void FinishPlan(const PlanInput& in, const std::string& spec, Plan* plan);
 // Decides Plan::tail for a fused LM head (see GemmParams::tail_groups); `forced`: the override gave a value.
 void ChooseTail(const PlanInput& in, bool forced, Plan* plan);
 void DistributeTiles(const PlanInput& in, int total_tiles, Plan* plan);

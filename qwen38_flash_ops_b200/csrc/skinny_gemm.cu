@@ -1111,13 +1111,17 @@ struct Nvfp4Stream {
 // Slot of one k-step (RingSlot).  NVFP4 (column tiles start on multiples of 128 columns): 16 rows of
 // 5 aligned 16-byte pieces around the row's 64 nibble bytes - the fifth is needed only where the chunk
 // starts 8 bytes off a 16-byte boundary (odd rows of a weight whose packed pitch is 8 mod 16, like the
-// 151936-column LM head) - then 16 rows of the one aligned piece that holds the row's 8 scale bytes:
-// 96 pieces, three per lane (piece index lane + 32 j).  A lane whose index names an unneeded piece repeats
-// piece 0 of that row (same source, same destination), so no copy is predicated.  Rows 8..15 of both
-// areas are displaced (32 / 16 bytes), which puts the four rows a warp-wide load touches into distinct
-// banks.  BF16 / FP8: [4 rows][32 lanes][16 bytes], a lane copies exactly the bytes it consumes.
-// The last k-step of a K slice is copied by a careful path (rows past K read as zero, pieces clamped to
-// the end of the tensor); a pair that contains it, or has no second step, takes that path for both steps.
+// 151936-column LM head) - then 16 rows of the one aligned piece that holds the row's 8 scale bytes.  The
+// 160 nibble pieces of a pair are five copy instructions (piece index lane + 32 j), its 32 scale pieces a
+// sixth, which keeps its lines in L1 (.ca): the four column warps whose scale bytes share a 32-byte sector
+// then fetch it from L2 once, and the stream is bound by the sectors that cross from L2 to the SM (measured:
+// 9.4 TB/s of sector traffic at 2.07 sector bytes per payload byte without this, 4.5 TB/s of weights).
+// A lane whose index names an unneeded piece repeats piece 0 of that row (same source, same destination), so
+// no copy is predicated.  Rows 8..15 of both areas are displaced (32 / 16 bytes), which puts the four rows a
+// warp-wide load touches into distinct banks.  BF16 / FP8: [4 rows][32 lanes][16 bytes] per step, a lane
+// copies exactly the bytes it consumes.  The last k-step of a K slice is copied by a careful path (rows past
+// K read as zero, pieces clamped to the end of the tensor); a pair that contains it, or has no second step,
+// takes that path for both steps.
 template <int MODE>
 struct RingSlot {
   static constexpr int kNibPitch = 80;
@@ -1125,35 +1129,32 @@ struct RingSlot {
   static constexpr int kSclPitch = 16;
   static constexpr int kSclBytes = MODE == kNvfp4 ? 16 * kSclPitch + 16 : 0;
   static constexpr int kBytes = kNibBytes + kSclBytes;
-  static constexpr int NP = MODE == kNvfp4 ? 3 : 4;
+  static constexpr int NP = MODE == kNvfp4 ? 6 : 8;  // copy instructions per pair of k-steps
   __device__ static constexpr int NibRow(int r) { return r * kNibPitch + ((r >> 3) & 1) * 32; }
   __device__ static constexpr int SclRow(int r) { return kNibBytes + r * kSclPitch + ((r >> 3) & 1) * 16; }
 };
 static_assert(RingSlot<kNvfp4>::kBytes == 1584 && RingSlot<kBf16>::kBytes == 2048, "keep RingSlotBytes() in step");
 
+// The pieces of a lane within a pair of k-steps: source offset from the pair's base, destination offset in the
+// ring, and (careful path) the row within the pair, 5 bits each.
 template <int NP>
 struct CopyPieces {
   uint32_t off[NP], dst[NP];
 };
-// Copies up to two consecutive local steps (those below `nsteps`) piece by piece with clamped sizes.
+// Copies the pieces of a pair that belong to existing steps, with clamped sizes.
 template <int NP>
-__device__ __noinline__ void IssueCareful(const uint8_t* w, long long total_bytes, const uint8_t* gbase, long long step_stride,
-                                          int kend, int row0, int row_step, uint32_t rows, CopyPieces<NP> pc, uint32_t slot_off,
-                                          uint32_t slot_bytes, int s0, int nsteps) {
-  for (int e = 0; e < 2; ++e) {
-    if (s0 + e < nsteps) {
+__device__ __noinline__ void IssueCareful(const uint8_t* w, long long total_bytes, const uint8_t* gbase, int kend, int row0,
+                                          int row_step, unsigned long long rows, CopyPieces<NP> pc, uint32_t slot_off, int steps) {
 #pragma unroll
-      for (int j = 0; j < NP; ++j) {
-        const int r = static_cast<int>((rows >> (4 * j)) & 15u);
-        const uint8_t* src = gbase + pc.off[j];
-        const long long room = total_bytes - (src - w);
-        const int bytes = (row0 + r >= kend) ? 0 : room >= 16 ? 16 : room > 0 ? static_cast<int>(room) : 0;
-        CpAsync16(pc.dst[j] + slot_off, bytes > 0 ? src : w, bytes);
-      }
+  for (int j = 0; j < NP; ++j) {
+    const int rr = static_cast<int>((rows >> (5 * j)) & 31u);  // step of the pair (bit 4) and row within it
+    const int e = rr >> 4, r = rr & 15;
+    if (e < steps) {
+      const uint8_t* src = gbase + pc.off[j];
+      const long long room = total_bytes - (src - w);
+      const int bytes = (row0 + e * row_step + r >= kend) ? 0 : room >= 16 ? 16 : room > 0 ? static_cast<int>(room) : 0;
+      CpAsync16(pc.dst[j] + slot_off, bytes > 0 ? src : w, bytes);
     }
-    gbase += step_stride;
-    row0 += row_step;
-    slot_off += slot_bytes;
   }
 }
 
@@ -1164,12 +1165,13 @@ struct WarpRing {
   static constexpr int kPairBytes = 2 * S::kBytes;
   static_assert(DEPTH >= 2 && DEPTH <= 4, "ring depth in pairs of k-steps");
 
-  const uint8_t* gbase;  // next step to copy, less 16 bytes (piece offsets are unsigned)
+  const uint8_t* gbase;  // next pair to copy, less 16 bytes (piece offsets are unsigned)
   long long step_stride;
   CopyPieces<NP> pc;     // dst includes the ring's address
-  uint32_t off2[NP];     // pc.off + step_stride: the second step of a pair
-  uint32_t rd_w[2], rd_s[2], rows;
+  uint32_t rd_w[2], rd_s[2];
+  unsigned long long rows;
   int nsteps, nfast, row_next, row_step;
+  bool scales_l1;  // NVFP4: keep the scale pieces' lines in L1 (pays only while the CTA leaves L1 room beside its shared memory)
 
   // Local step s is k-step k_first + s * k_stride of the CTA's K slice, k_count steps in all.  `colwarp`:
   // first column of the warp; `lane_cols_ok`: the lane's own columns exist (BF16 / FP8 lanes past the
@@ -1187,6 +1189,7 @@ struct WarpRing {
     row_step = k_stride * 16;
     step_stride = static_cast<long long>(k_stride) * 16 * pitch;
     rows = 0;
+    scales_l1 = false;
     if constexpr (MODE == kNvfp4) {
       const long long warp_col_byte = colwarp / 2;  // a multiple of 64
       gbase = sg.w + static_cast<long long>(row_next) * pitch + warp_col_byte - 16;
@@ -1195,22 +1198,29 @@ struct WarpRing {
       const int so_even = static_cast<int>(sabs & 15), so_odd = static_cast<int>((sabs + mis) & 15);
 #pragma unroll
       for (int j = 0; j < NP; ++j) {
-        const int q = lane + 32 * j;
-        if (q < 80) {
-          const int r = q / 5;
-          int c = q - r * 5;
+        int e, r;
+        long long src;
+        uint32_t dst;
+        if (j < 5) {  // nibble piece lane + 32 j of the pair's 2 x 16 x 5
+          const int q = lane + 32 * j;
+          e = q / 80;
+          const int qq = q - e * 80;
+          r = qq / 5;
+          int c = qq - r * 5;
           const int shift = (r & 1) ? mis : 0;
           if (c == 4 && shift == 0) c = 0;
-          pc.off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (c * 16 - shift) + 16);
-          pc.dst[j] = ring + static_cast<uint32_t>(S::NibRow(r) + c * 16);
-          rows |= static_cast<uint32_t>(r) << (4 * j);
-        } else {
-          const int r = q - 80;
+          src = c * 16 - shift;
+          dst = static_cast<uint32_t>(S::NibRow(r) + c * 16);
+        } else {      // scale piece of row lane % 16 of step lane / 16
+          e = lane >> 4;
+          r = lane & 15;
           const int o = (r & 1) ? so_odd : so_even;
-          pc.off[j] = static_cast<uint32_t>(static_cast<long long>(r) * pitch + (sabs - o - warp_col_byte) + 16);
-          pc.dst[j] = ring + static_cast<uint32_t>(S::SclRow(r));
-          rows |= static_cast<uint32_t>(r) << (4 * j);
+          src = sabs - o - warp_col_byte;
+          dst = static_cast<uint32_t>(S::SclRow(r));
         }
+        pc.off[j] = static_cast<uint32_t>(static_cast<long long>(e) * step_stride + static_cast<long long>(r) * pitch + src + 16);
+        pc.dst[j] = ring + dst + static_cast<uint32_t>(e * S::kBytes);
+        rows |= static_cast<unsigned long long>(e * 16 + r) << (5 * j);
       }
       const int rbase = S::NibRow(4 * t) + g * 8, sbase = S::SclRow(4 * t) + g;
       rd_w[0] = ring + static_cast<uint32_t>(rbase);
@@ -1222,28 +1232,30 @@ struct WarpRing {
       gbase = sg.w + static_cast<long long>(row_next) * pitch + warp_col_byte - 16;
       const int gsrc = lane_cols_ok ? g : 0;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        pc.off[i] = static_cast<uint32_t>(static_cast<long long>(4 * t + i) * pitch + gsrc * 16 + 16);
-        pc.dst[i] = ring + static_cast<uint32_t>(i * 512 + lane * 16);
-        rows |= static_cast<uint32_t>(4 * t + i) << (4 * i);
+      for (int j = 0; j < NP; ++j) {
+        const int e = j >> 2, i = j & 3;
+        pc.off[j] = static_cast<uint32_t>(static_cast<long long>(e) * step_stride + static_cast<long long>(4 * t + i) * pitch + gsrc * 16 + 16);
+        pc.dst[j] = ring + static_cast<uint32_t>(e * S::kBytes + i * 512 + lane * 16);
+        rows |= static_cast<unsigned long long>(e * 16 + 4 * t + i) << (5 * j);
       }
       rd_w[0] = rd_w[1] = ring + static_cast<uint32_t>(lane * 16);
       rd_s[0] = rd_s[1] = 0;
     }
-#pragma unroll
-    for (int j = 0; j < NP; ++j) off2[j] = pc.off[j] + static_cast<uint32_t>(step_stride);
   }
 
   // copies the pair of local steps (s0, s0 + 1) - the next ones in order - into the slots at `slot_off`
   __device__ __forceinline__ void IssuePair(const Tile& tl, const Segment& sg, int s0, uint32_t slot_off) {
     if (s0 + 1 < nfast) {
 #pragma unroll
-      for (int j = 0; j < NP; ++j) CpAsync16At<0, false>(pc.dst[j] + slot_off, gbase, pc.off[j]);
-#pragma unroll
-      for (int j = 0; j < NP; ++j) CpAsync16At<S::kBytes, false>(pc.dst[j] + slot_off, gbase, off2[j]);
+      for (int j = 0; j < NP; ++j) {
+        if (MODE == kNvfp4 && j == NP - 1 && scales_l1) {
+          CpAsync16At<0, true>(pc.dst[j] + slot_off, gbase, pc.off[j]);
+        } else {
+          CpAsync16At<0, false>(pc.dst[j] + slot_off, gbase, pc.off[j]);
+        }
+      }
     } else if (s0 < nsteps) {
-      IssueCareful<NP>(sg.w, sg.total_bytes, gbase, step_stride, tl.kend, row_next, row_step, rows, pc, slot_off,
-                       static_cast<uint32_t>(S::kBytes), s0, nsteps);
+      IssueCareful<NP>(sg.w, sg.total_bytes, gbase, tl.kend, row_next, row_step, rows, pc, slot_off, nsteps - s0);
     }
     gbase += 2 * step_stride;
     row_next += 2 * row_step;
@@ -1347,6 +1359,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const _
   // weights do not depend on the predecessor kernel: get the first k-steps in flight, then wait
   WarpRing<MODE, DEPTH> ring;
   ring.Setup(tl, sg, stream_col, cvalid, first_step, step_count, step_stride, ring_addr);
+  ring.scales_l1 = p.scales_l1 != 0;
   ring.Prologue(tl, sg);
   if (p.pdl_wait) GridDependencyWait();
   Stamp(p, 1);
@@ -2241,6 +2254,7 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
     if (smem < 120 * 1024) smem = 120 * 1024;
   }
   if (g_max_dynamic_smem > 0 && smem > static_cast<size_t>(g_max_dynamic_smem)) return cudaErrorInvalidConfiguration;
+  p.scales_l1 = smem <= kL1FriendlySmem ? 1 : 0;
   p.tail_groups = plan.tail;
   // K slices per shared group: one per idle warp as far as they go, at most kMaxTailSplit
   p.tail_split = plan.tail > 0 ? std::max(1, std::min(kMaxTailSplit, plan.tiles[0] * plan.wk / plan.tail)) : 1;
