@@ -6,15 +6,17 @@
 Headline workload: the NVFP4 LM head (K 5120, vocabulary 151936, `UINT8 [5120, 85464]`, 437.6 MB
 of packed weights - larger than L2, so every step streams from HBM) fused with ArgmaxRows.  One
 step is one call on one batch of M rows; with N > 1 GPUs the vocabulary is split by columns
-(128-column granules), every rank runs the fused kernel on its shard and the ranks all-gather
-their per-row (max, index) keys over NCCL - total work is fixed, so scaling is strong.  The metric
-is weight bytes per second over all GPUs.  Rank 0 prints one JSON line.
+(128-column granules), every rank runs the fused kernel on its shard and the ranks exchange their
+per-row (max, index) keys - inside the fused kernel, whose last CTA stores them into every rank's
+peer-mapped buffer and folds what arrives (the timed path), with the NCCL all-gather + fold kernel
+timed beside it (`exchange_alt`).  Total work is fixed, so scaling is strong.  The metric is weight
+bytes per second over all GPUs.  Rank 0 prints one JSON line.
 
 `--impl reference` times the CPU restatement of the unfused chain the op replaces (dequantise ->
-MatMul with FP32 accumulation -> ArgMax) on the host cores, on a bounded column sample of the
-same workload; the reference project has no CPU implementation of its own, and ONNX Runtime is
-not installed here.  Where the reference's CUDA kernels were compiled for sm_100a
-(oracle/_ref) their time on the same workload is reported beside it.
+MatMul with FP32 accumulation -> ArgMax) on all host cores over the whole head, once per step; the
+reference project has no CPU implementation of its own, and ONNX Runtime is not installed here.
+Where the reference's CUDA kernels were compiled for sm_100a (oracle/_ref) their time on the same
+workload is reported beside it.
 """
 from __future__ import annotations
 
@@ -35,7 +37,9 @@ UNIT = "TB/s"
 HEAD = "C5_nvfp4_lmhead_5120x151936"
 
 
-NCU_DRAM_BYTES_PER_WEIGHT_BYTE = 1.0121  # (438.99 MB read + 3.89 MB written) / 437.58 MB of packed weights
+# DRAM sectors per launch of the fused LM-head kernel, from an ncu capture of this workload:
+# (439.07 MB read + 3.89 MB written) / 437.58 MB of packed weights
+NCU_DRAM_BYTES_PER_WEIGHT_BYTE = 1.0123
 
 
 def peaks():
@@ -209,6 +213,70 @@ def bench_small_configs(torch, quick=False):
     return out
 
 
+def read_ceiling(torch):
+    """GB/s of a read-only sweep (128-bit loads, nothing written) over 2 GiB, 16x L2: the streaming ceiling
+    a weight stream is compared with, besides the copy bandwidth."""
+    import ctypes
+
+    from qwen38_flash_ops_b200 import _lib
+
+    lib = _lib.load()
+    nbytes = 2 << 30
+    buf = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    buf.fill_(1)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def sweep():
+        _lib.check(lib.qfg_stream_read_probe(buf.data_ptr(), nbytes, None, ctypes.c_void_p(stream)))
+
+    ms = time_region(torch, sweep, 10, 3)
+    del buf
+    torch.cuda.empty_cache()
+    return round(nbytes * 10 / ms / 1e6, 1)
+
+
+def bench_argmax_and_dequant(torch):
+    """ArgmaxRows over LM-head logits (1 / 4 / 8 / 64 rows, the reference's kernel beside it) and
+    DequantWeightBf16 (bytes in + bytes out per second): device time per call from a CUDA graph of 20 calls."""
+    from qwen38_flash_ops_b200 import ArgmaxRows, DequantWeightBf16
+    from qwen38_flash_ops_b200 import workloads as W
+
+    peak, _ = peaks()
+    out = {"ArgmaxRows_bf16_151936": {}, "DequantWeightBf16": {}}
+    ref = _ref_util()
+    vocab = 151936
+    op = ArgmaxRows()
+    for rows in (1, 4, 8, 64):
+        gen = torch.Generator(device="cuda").manual_seed(rows)
+        x = (torch.randn((rows, vocab), generator=gen, device="cuda") * 1.43).to(torch.bfloat16)
+        idx = torch.empty(rows, dtype=torch.int64, device="cuda")
+        val = torch.empty(rows, dtype=torch.float32, device="cuda")
+        med, best = time_graph_rotation(torch, lambda i: op(x, out=(idx, val)), 20)
+        line = {"us": round(med, 3), "us_best": round(best, 3), "GBps": round(x.numel() * 2 / med / 1e3, 1)}
+        if ref is not None:
+            rmed, _ = time_graph_rotation(torch, lambda i: ref.ref_argmax_rows(x), 20)
+            line["reference_kernel_sm100a_us"] = round(rmed, 3)
+        out["ArgmaxRows_bf16_151936"][f"rows{rows}"] = line
+    for label, mode, k, n in (("nvfp4_5120x17408", W.MODE_NVFP4, 5120, 17408), ("nvfp4_5120x151936", W.MODE_NVFP4, 5120, 151936),
+                              ("fp8_5120x10240", W.MODE_FP8, 5120, 10240)):
+        copies = max(2, min(16, -(-(1 << 30) // (k * n * 3))))
+        ws, scale = [], None
+        for c in range(copies):
+            w, s_ = W.make_weight(mode, k, n, seed=50 + c)
+            ws.append(w)
+            scale = s_ if c == 0 else scale
+        dq = DequantWeightBf16(n, w_scale=scale.cpu().numpy() if scale is not None else None)
+        dst = torch.empty((k, n), dtype=torch.bfloat16, device="cuda")
+        med, best = time_graph_rotation(torch, lambda i: dq(ws[i], out=[dst]), copies)
+        moved = ws[0].numel() * ws[0].element_size() + k * n * 2
+        out["DequantWeightBf16"][label] = {"us": round(med, 2), "GBps": round(moved / med / 1e3, 1),
+                                           "frac_of_measured_hbm": round(moved / med / 1e3 / peak, 4),
+                                           "bytes": moved}
+        del ws, dst
+        torch.cuda.empty_cache()
+    return out
+
+
 def _ref_util():
     """tests/_util when the reference project's kernels were compiled (oracle/_ref), else None."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -219,12 +287,22 @@ def _ref_util():
     return U if U.ref_lib() is not None else None
 
 
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_baseline(m, k, sample_cols, seed=11, reps=1):
     """The unfused chain on the host cores over the first `sample_cols` columns of the head."""
     import numpy as np
 
     from oracle import cpu as C
     from qwen38_flash_ops_b200 import packing as P
+
+    # the launcher of multi-rank runs exports OMP_NUM_THREADS=1: the CPU arm uses every core it may run on
+    C.set_num_threads(host_cores())
 
     rng = np.random.default_rng(seed)
     x = P.synth_x(rng, m, k)
@@ -346,15 +424,15 @@ def run_ours(args):
     verified = None
     exchange_note = None
     if world > 1:
-        ok = verify_sharded(torch, dist, head, x, shard, n_local, c0, world)
+        ok = all(verify_sharded(torch, dist, head, xr, shard, n_local, c0, world) for xr in sharded_check_inputs(torch, dist, W, x, k))
         if not ok and head.peer is not None:
             # the in-kernel exchange failed its check on this machine: fall back to the collective and say so
             exchange_note = f"peer-memory exchange failed verification (status {head.peer.status()}); NCCL used instead"
             head = ShardedLmHead(shard, n_local, c0, exchange="nccl")
-            ok = verify_sharded(torch, dist, head, x, shard, n_local, c0, world)
+            ok = all(verify_sharded(torch, dist, head, xr, shard, n_local, c0, world) for xr in sharded_check_inputs(torch, dist, W, x, k))
         if not ok:
             raise SystemExit("sharded LM head disagrees with the fold of the per-rank unfused results")
-        verified = "sharded step == fold of per-rank SkinnyGemm + ArgmaxRows"
+        verified = "sharded step == fold of per-rank SkinnyGemm + ArgmaxRows, rows 1, 2, 4 and the timed batch"
 
     sampler = ClockSampler(local)
     if rank == 0:
@@ -364,6 +442,27 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
     us_step = ms * 1000.0 / args.steps
     value = total_bytes / us_step / 1e6
+
+    # inside the exchange of the last timed step, per rank: stores issued after the keys were ready, all ranks' words
+    # seen after the stores; the slowest rank waits least, so the minimum over ranks of the wait is the latency of
+    # the exchange itself and the rest of a rank's wait is time spent waiting for the slowest rank's kernel
+    exchange_times = None
+    exchange_alt = None
+    if world > 1 and head.peer is not None:
+        t_ready, t_sent, t_done = head.peer.times()
+        mine = torch.tensor([(t_sent - t_ready) / 1000.0, (t_done - t_sent) / 1000.0], dtype=torch.float64, device="cuda")
+        allt = torch.empty((world, 2), dtype=torch.float64, device="cuda")
+        dist.all_gather_into_tensor(allt, mine)
+        a = allt.cpu().numpy()
+        exchange_times = {"store_us": {"min": round(float(a[:, 0].min()), 2), "max": round(float(a[:, 0].max()), 2)},
+                          "wait_us": {"min": round(float(a[:, 1].min()), 2), "median": round(float(sorted(a[:, 1])[world // 2]), 2),
+                                      "max": round(float(a[:, 1].max()), 2)},
+                          "what": "last timed step, per rank, device timer: keys ready -> stores issued -> all ranks' words seen"}
+        # the exchange the north star names, timed the same way: one NCCL all-gather of the keys and a fold kernel
+        nccl_head = ShardedLmHead(shard, n_local, c0, exchange="nccl")
+        ms_n = time_region(torch, lambda: nccl_head.step(x), args.steps, args.warmup, dist)
+        exchange_alt = {"kind": "nccl_all_gather + fold kernel", "us_per_step": round(ms_n * 1000.0 / args.steps, 2),
+                        "value": round(total_bytes / (ms_n * 1000.0 / args.steps) / 1e6, 4), "unit": UNIT}
 
     # the fused kernel alone on this rank (no collective): the roofline figure
     ms_k = time_region(torch, lambda: head.head(x, shard, n_local, col_offset=c0, out=head_out(head, m, torch)),
@@ -393,7 +492,7 @@ def run_ours(args):
         return
     peak, peak_kind = peaks()
     # DRAM bytes per launch from the ncu capture of this kernel on this workload (read + write sectors
-    # over the packed weight bytes; see profiles/skinny_gemm_nvfp4_lmhead_ncu_full.md), scaled to the shard
+    # over the packed weight bytes), scaled to the shard
     traffic = round(NCU_DRAM_BYTES_PER_WEIGHT_BYTE * shard_bytes)
     line = {
         "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -421,12 +520,23 @@ def run_ours(args):
                                       if head.peer is not None else "NCCL all-gather + fold kernel")
         if exchange_note is not None:
             line["config"]["exchange_note"] = exchange_note
+        if exchange_times is not None:
+            line["exchange_times"] = exchange_times
+        if exchange_alt is not None:
+            line["exchange_alt"] = exchange_alt
         if head.peer is not None and head.peer.status() != 0:
             raise SystemExit("a wait for a peer's keys ran out during the run")
     if world == 1 and not args.skip_cpu:
         line["cpu_baseline"] = cpu_baseline(m, k, n_total, reps=40)
+    if world == 1:
+        # third denominator: the read-only streaming ceiling of this GPU, measured now
+        ceiling = read_ceiling(torch)
+        line["roofline"]["read_ceiling_gbs"] = ceiling
+        line["roofline"]["frac_of_read_ceiling"] = round(shard_bytes / us_kernel / 1e3 / ceiling, 4)
+        line["roofline"]["frac_of_8TBps"] = round(shard_bytes / us_kernel / 1e3 / 8000.0, 4)
     if world == 1 and not args.headline_only:
         line["all_configs"] = bench_small_configs(torch, quick=args.quick)
+        line["all_configs"].update(bench_argmax_and_dequant(torch))
         per_m = {}
         for mm in (1, 2, 4):
             xm = W.make_x(mm, k, seed=7)
@@ -449,6 +559,16 @@ def run_ours(args):
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def sharded_check_inputs(torch, dist, W, x, k):
+    """The timed batch and batches of 1, 2 and 4 rows, identical on every rank."""
+    batches = [x]
+    for m in (1, 2, 4):
+        xm = W.make_x(m, k, seed=70 + m)
+        dist.broadcast(xm, 0)
+        batches.append(xm)
+    return batches
 
 
 def verify_sharded(torch, dist, head, x, shard, n_local, c0, world):

@@ -278,6 +278,12 @@ QFG_API int qfg_peer_free(void* ptr);
 /* Fold `ranks` gathered key rows (keys[rank * m + row]) into idx[row] / val[row]. */
 QFG_API int qfg_lmhead_combine(const uint64_t* keys, int ranks, int64_t m, int64_t* idx, float* val, void* stream);
 
+/* Measurement aid, no counterpart in the reference: sweeps `bytes` of device memory at `buf` (16-byte aligned) with
+ * 128-bit read-only loads and writes nothing (`sink`, 4 bytes of device memory or null, is never stored to on
+ * real data).  Timed over a buffer several times the size of L2 it gives the read-only streaming ceiling of the
+ * GPU, the denominator a weight-streaming kernel is compared with besides the copy bandwidth. */
+QFG_API int qfg_stream_read_probe(const void* buf, size_t bytes, void* sink, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

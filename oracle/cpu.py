@@ -21,6 +21,7 @@ def load():
             raise ImportError(f"{LIB_PATH} missing: run `make -C {_HERE}`")
         lib = ctypes.CDLL(LIB_PATH)
         lib.oracle_num_threads.restype = c_int
+        lib.oracle_set_num_threads.argtypes = [c_int]
         lib.oracle_dequant_bf16.argtypes = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
         lib.oracle_skinny_gemm.argtypes = [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                            c_void_p, c_void_p]
@@ -36,6 +37,11 @@ def _ptr(a):
 
 def num_threads() -> int:
     return load().oracle_num_threads()
+
+
+def set_num_threads(n: int) -> None:
+    """Threads of the OpenMP loops from here on (overrides OMP_NUM_THREADS)."""
+    load().oracle_set_num_threads(int(max(1, n)))
 
 
 def dequant_bf16(mode, w, n_cols, col_offset=0, w_scale=None):

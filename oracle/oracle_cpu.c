@@ -116,6 +116,8 @@ static long long pitch_of(int mode, int n_total) {
   return mode == MODE_BF16 ? 2LL * n_total : mode == MODE_FP8 ? (long long)n_total : (long long)n_total * 9 / 16;
 }
 
+void oracle_set_num_threads(int n) { omp_set_num_threads(n > 0 ? n : 1); }
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -32,6 +32,7 @@ EXPORTS = (
     "qfg_lmhead_exchange_times",
     "qfg_peer_alloc", "qfg_peer_open", "qfg_peer_close", "qfg_peer_free",
     "qfg_lmhead_host_create", "qfg_lmhead_host_run", "qfg_lmhead_host_destroy",
+    "qfg_stream_read_probe",
 )
 
 
@@ -102,6 +103,7 @@ def load() -> ctypes.CDLL:
     lib.qfg_lmhead_exchange_times.argtypes = [c_void_p, POINTER(c_uint64)]
     lib.qfg_lmhead_host_create.argtypes = [c_void_p, c_int64, c_int64, POINTER(Tensor2D), c_int64, c_int64, c_void_p,
                                            POINTER(LmExchange), c_void_p, c_void_p, c_void_p, c_void_p, POINTER(c_void_p)]
+    lib.qfg_stream_read_probe.argtypes = [c_void_p, c_size_t, c_void_p, c_void_p]
     lib.qfg_lmhead_host_run.argtypes = [c_void_p]
     lib.qfg_lmhead_host_destroy.argtypes = [c_void_p]
     lib.qfg_lmhead_host_destroy.restype = None

@@ -167,7 +167,7 @@ struct TunedShape {
 };
 const TunedShape kTunedB200[] = {
     {kBf16, 5120, 1, {5120, 0, 0, 0}, "direct=2,wn=1,wk=16,cluster=1,waves=1"},
-    {kFp8, 5120, 3, {8192, 1024, 1024, 0}, "direct=1,wn=1,wk=6,cluster=4,waves=1"},
+    {kFp8, 5120, 3, {8192, 1024, 1024, 0}, "direct=2,wn=1,wk=16,cluster=1,ctas=148"},
     {kNvfp4, 5120, 2, {17408, 17408, 0, 0}, "direct=1,wide=1,wn=2,wk=8,cluster=1,ctas=136"},
     {kNvfp4, 17408, 1, {5120, 0, 0, 0}, "direct=1,wide=1,wn=2,wk=8,cluster=6,ctas=120"},
     {kNvfp4, 5120, 1, {151936, 0, 0, 0}, "direct=1,wide=1,wn=9,wk=2,cluster=1,waves=1"},

@@ -414,7 +414,7 @@ __device__ __forceinline__ int XsIndex(int m, int k, int xpitch) {
 template <int MODE, int WORDS, bool TC = false, bool FUSE = false, bool WALK = true>
 __device__ __forceinline__ bool StageXImpl(const GemmParams& p, const Tile& tl, uint16_t* xs, SharedScratch& sh) {
   constexpr int kElems = 2 * WORDS;
-  constexpr int kBatch = 4;
+  constexpr int kBatch = 4;  // loads in flight per thread (eight measured slower: twice the cold code for one round trip less)
   // a CTA whose K slice is empty (more cluster ranks than k-steps) stages nothing and adds nothing
   if (tl.kslice <= 0) return false;
   const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31;
@@ -702,15 +702,35 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
     cluster.sync();
     const int cper = (TNc + C - 1) / C;  // the last rank's share may be short (any C <= 8)
     const int cb = tl.crank * cper;
-    for (int m = 0; m < M; ++m) {
-      for (int cc = tid; cc < cper; cc += nthreads) {
-        const int c = cb + cc;
-        if (c >= ncols) break;
-        float sum = 0.f;
-        for (int r = 0; r < C; ++r) sum += cluster.map_shared_rank(part, r)[m * TNc + c];
-        finalize(m, c, sum);
+    // The C partial sums of an output come from C CTAs' shared memory: all eight possible loads are issued
+    // before the first is used (one round trip through the cluster network instead of C), then added in rank order.
+    auto rank_sum = [&](int idx) {
+      float v[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) v[r] = r < C ? cluster.map_shared_rank(part, r)[idx] : 0.f;
+      float sum = 0.f;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < C) sum += v[r];
       }
-      flush_row(m);
+      return sum;
+    };
+    if (!lm) {
+      // without the argmax nothing ties an output to its row: every (row, column) of this rank's share is one item
+      const int items = M * cper;
+      for (int i = tid; i < items; i += nthreads) {
+        const int m = i / cper, c = cb + (i - m * cper);
+        if (c < ncols) finalize(m, c, rank_sum(m * TNc + c));
+      }
+    } else {
+      for (int m = 0; m < M; ++m) {
+        for (int cc = tid; cc < cper; cc += nthreads) {
+          const int c = cb + cc;
+          if (c >= ncols) break;
+          finalize(m, c, rank_sum(m * TNc + c));
+        }
+        flush_row(m);
+      }
     }
     cluster.sync();
   }

@@ -106,7 +106,8 @@ class ArgmaxRows:
     def __init__(self):
         self._lib = _lib.load()
 
-    def __call__(self, x: torch.Tensor, with_val: bool = True):
+    def __call__(self, x: torch.Tensor, with_val: bool = True, out=None):
+        """`out`: optional (idx, val) tensors to write into (val may be None)."""
         _require_cuda(x, "x")
         if x.dtype not in (torch.bfloat16, torch.float16, torch.float32):
             raise QfgError(_lib.QFG_INVALID_ARGUMENT, "ArgmaxRows: logits must be BF16/FP16/FP32")
@@ -115,8 +116,12 @@ class ArgmaxRows:
         vocab = x.shape[-1]
         lead = tuple(x.shape[:-1])
         rows = x.numel() // vocab
-        idx = torch.empty(lead, dtype=torch.int64, device=x.device)
-        val = torch.empty(lead, dtype=torch.float32, device=x.device) if with_val else None
+        if out is not None:
+            idx, val = out
+            with_val = val is not None
+        else:
+            idx = torch.empty(lead, dtype=torch.int64, device=x.device)
+            val = torch.empty(lead, dtype=torch.float32, device=x.device) if with_val else None
         check(self._lib.qfg_argmax_rows(_DTYPES[x.dtype], x.data_ptr(), rows, vocab, idx.data_ptr(),
                                         val.data_ptr() if with_val else None, _stream_ptr()))
         return (idx, val) if with_val else idx
@@ -141,9 +146,9 @@ class DequantWeightBf16:
         check(lib.qfg_dequant_create(int(n_cols), int(col_offset), wi, len(widths), ptr, n, ctypes.byref(self._h)))
         self.widths = widths if widths else [int(n_cols)]
 
-    def __call__(self, w: torch.Tensor):
+    def __call__(self, w: torch.Tensor, out=None):
         t = _tensor2d(w)
-        outs = [torch.empty((w.shape[0], wd), dtype=torch.bfloat16, device=w.device) for wd in self.widths]
+        outs = out if out is not None else [torch.empty((w.shape[0], wd), dtype=torch.bfloat16, device=w.device) for wd in self.widths]
         ptrs = (c_void_p * len(outs))(*[o.data_ptr() for o in outs])
         check(self._lib.qfg_dequant_compute(self._h, ctypes.byref(t), ptrs, len(outs), _stream_ptr()))
         return outs
@@ -218,7 +223,7 @@ class UntileHcBf16:
             keep, ptr, n = None, None, 0
         check(lib.qfg_untile_hc_create(self.kind, ptr, n, ctypes.byref(self._h)))
 
-    def __call__(self, w: torch.Tensor):
+    def __call__(self, w: torch.Tensor, out=None):
         _require_cuda(w, "w")
         t = _tensor2d(w)
         shape = (10240, 320) if self.kind == 0 else (320, 10240)
