@@ -1,160 +1,173 @@
 // ArgmaxRows for B200: idx[r] = argmax_v x[r, v] with numpy semantics (lowest index on ties, the
 // first NaN wins over everything, -0 == +0), optionally with the maximum as FP32.
 //
-// One thread-block cluster per row.  Each CTA scans a contiguous range of the row with 16-byte
-// loads (a scalar head and tail absorb any misalignment, so odd vocabulary sizes and unaligned
-// rows still take the vector body), six to ten loads in flight per thread; (value, index) pairs are
-// reduced with the same total order at every level - lanes, warps, then the CTAs of the cluster
-// through distributed shared memory - so the result does not depend on the launch geometry.
-// No workspace, no atomics.
-#include <cooperative_groups.h>
+// At decode row counts the op is latency, not bandwidth: a row of 151936 BF16 logits is 304 KB that is
+// already in L2.  The kernel is built around that.
+//   * One cluster of up to eight CTAs per row; a CTA issues all the 16-byte loads of its share of the row at
+//     once (a scalar head and tail keep the vector body for odd vocabularies and unaligned rows), so a row
+//     costs one round trip to L2.
+//   * Candidates travel as 64-bit keys whose unsigned maximum is the winner (argmax_key.cuh): a thread packs
+//     its best pair once, a warp needs two redux.sync.max, warps meet in one shared-memory atomicMax.
+//   * The CTAs of a cluster do not meet at a barrier at the end.  CTA 0 owns one mbarrier and one key slot
+//     per peer; a peer stores its key into CTA 0's shared memory, arrives on the barrier with release
+//     semantics at cluster scope, and exits; CTA 0 alone waits (bounded), folds and writes.  The one cluster
+//     barrier that must precede a remote arrival (the mbarrier has to exist) is split: every CTA arrives
+//     right after it has issued its loads and waits only when its own result is ready, so the barrier's
+//     latency lies under the memory latency.
+// No workspace, no global atomics; the result does not depend on the launch geometry.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <climits>
 
+#include "argmax_key.cuh"
 #include "qfg_internal.h"
 
 namespace qfg {
 namespace {
 
-namespace cg = cooperative_groups;
-
-constexpr int kThreads = 512;  // 1024 threads per CTA measured slower at every row count (5.7 us against 4.8 for one row)
-constexpr int kNone = INT_MAX;
-
-__device__ __forceinline__ bool Better(float av, int ai, float bv, int bi) {
-  if (av != av) return (bv == bv) || ai < bi;
-  if (bv != bv) return false;
-  return av > bv || (av == bv && ai < bi);
-}
+constexpr int kThreads = 512;   // 1024 threads per CTA measured slower at every row count
+constexpr int kMaxCluster = 8;
+constexpr int kPeerSpin = 1 << 24;  // bound of CTA 0's wait for its peers (iterations of about 30 ns)
 
 __device__ __forceinline__ float ToFloat(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ float ToFloat(__half v) { return __half2float(v); }
 __device__ __forceinline__ float ToFloat(float v) { return v; }
 
-// Order-independent update: keeps the best pair under `Better`.
-__device__ __forceinline__ void Consider(float& bv, int& bi, float v, int idx) {
-  if (bi == kNone || Better(v, idx, bv, bi)) {
-    bv = v;
-    bi = idx;
-  }
-}
+__device__ __forceinline__ uint32_t SharedAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
-// The same update for a candidate whose index exceeds every index seen so far by this thread: a strict
-// comparison keeps the lowest index of equal values, and a NaN is never replaced.
-__device__ __forceinline__ void ConsiderInOrder(float& bv, int& bi, float v, int idx) {
-  if (bi == kNone || v > bv || (v != v && bv == bv)) {
-    bv = v;
-    bi = idx;
-  }
-}
-
-__device__ __forceinline__ void WarpReduce(float& v, int& i) {
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, v, off);
-    const int oi = __shfl_xor_sync(0xffffffffu, i, off);
-    if (oi != kNone && (i == kNone || Better(ov, oi, v, i))) {
-      v = ov;
-      i = oi;
+// A thread's running best.  `InOrder`: the candidate's index exceeds every index this thread has seen, so a
+// strict comparison keeps the lowest index of equal values and a NaN is never replaced; `Any`: full order.
+struct Best {
+  float v = 0.f;
+  long long i = -1;
+  __device__ __forceinline__ void InOrder(float c, long long idx) {
+    if (i < 0 || c > v || (c != c && v == v)) {
+      v = c;
+      i = idx;
     }
   }
-}
+  __device__ __forceinline__ void Any(float c, long long idx) {
+    const bool c_nan = c != c, v_nan = v != v;
+    const bool better = c_nan ? (!v_nan || idx < i) : (!v_nan && (c > v || (c == v && idx < i)));
+    if (i < 0 || better) {
+      v = c;
+      i = idx;
+    }
+  }
+  __device__ __forceinline__ unsigned long long Key() const { return i < 0 ? 0ull : PackKey(v, i); }
+};
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads) ArgmaxRowsKernel(const T* __restrict__ x, long long V,
                                                              long long* __restrict__ idx_out,
                                                              float* __restrict__ val_out) {
   constexpr int kVecElems = 16 / sizeof(T);
-  constexpr int kWarps = kThreads / 32;
-  __shared__ float s_wv[kWarps];
-  __shared__ int s_wi[kWarps];
-  __shared__ float s_cv;
-  __shared__ int s_ci;
+  constexpr int kInFlight = sizeof(T) == 4 ? 10 : 6;  // 8 CTAs x 512 threads x 6 (10) loads cover 151936 columns
+  __shared__ unsigned long long s_best;               // this CTA's best key
+  __shared__ unsigned long long s_slot[kMaxCluster];  // CTA 0: the peers' keys
+  __shared__ unsigned long long s_bar;                // CTA 0: mbarrier, one arrival per peer
 
-  const int C = static_cast<int>(gridDim.x);
+  const int C = static_cast<int>(gridDim.x);  // the cluster spans the grid's x extent
   const int c = static_cast<int>(blockIdx.x);
   const long long row = blockIdx.y;
   const T* xr = x + row * V;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31;
 
-  // Row layout: `head` scalar elements up to the first 16-byte boundary, `nvec` vectors, a scalar tail.
+  // Row layout: `head` scalar elements up to the first 16-byte boundary, `nvec` vectors, a scalar tail;
+  // the vectors are split evenly over the CTAs of the cluster.
   const uintptr_t addr = reinterpret_cast<uintptr_t>(xr);
   long long head = ((16 - (addr & 15)) & 15) / sizeof(T);
   if (head > V) head = V;
   const long long nvec = (V - head) / kVecElems;
-  const long long tail_begin = head + nvec * kVecElems;
-
-  float bv = 0.f;
-  int bi = kNone;
-
-  // vectors are split evenly over the CTAs of the cluster
   const long long per = (nvec + C - 1) / C;
-  const long long vbeg = min(nvec, per * c);
-  const long long vend = min(nvec, vbeg + per);
+  const long long vbeg = min(nvec, per * c), vend = min(nvec, vbeg + per);
   const uint4* xv = reinterpret_cast<const uint4*>(xr + head);
-  // 8 CTAs x 512 threads x 6 (10 for FP32) loads cover a 151936-column row in one round trip to L2: the
-  // kernel is a few microseconds of latency and a second, mostly empty trip through the loop adds one more.
-  constexpr int kInFlight = sizeof(T) == 4 ? 10 : 6;
-  for (long long v0 = vbeg + tid; v0 < vend; v0 += static_cast<long long>(kThreads) * kInFlight) {
-    uint4 q[kInFlight];
+
+  // ---- the first batch of loads goes out before anything else
+  uint4 q[kInFlight];
+  long long v0 = vbeg + tid;
 #pragma unroll
-    for (int i = 0; i < kInFlight; ++i) {
-      const long long v = v0 + static_cast<long long>(i) * kThreads;
-      q[i] = v < vend ? __ldg(xv + v) : make_uint4(0, 0, 0, 0);
+  for (int k = 0; k < kInFlight; ++k) {
+    const long long v = v0 + static_cast<long long>(k) * kThreads;
+    q[k] = v < vend ? __ldg(xv + v) : make_uint4(0, 0, 0, 0);
+  }
+  if (tid == 0) {
+    s_best = 0ull;
+    if (c == 0 && C > 1) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(SharedAddr(&s_bar)), "r"(C - 1) : "memory");
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+  }
+  __syncthreads();
+  if (C > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+
+  Best best;
+  for (;;) {
 #pragma unroll
-    for (int i = 0; i < kInFlight; ++i) {
-      const long long v = v0 + static_cast<long long>(i) * kThreads;
+    for (int k = 0; k < kInFlight; ++k) {
+      const long long v = v0 + static_cast<long long>(k) * kThreads;
       if (v < vend) {
-        const T* e = reinterpret_cast<const T*>(&q[i]);
+        const T* e = reinterpret_cast<const T*>(&q[k]);
 #pragma unroll
-        for (int j = 0; j < kVecElems; ++j) {
-          ConsiderInOrder(bv, bi, ToFloat(e[j]), static_cast<int>(head + v * kVecElems + j));
-        }
+        for (int j = 0; j < kVecElems; ++j) best.InOrder(ToFloat(e[j]), head + v * kVecElems + j);
       }
+    }
+    v0 += static_cast<long long>(kThreads) * kInFlight;
+    if (v0 >= vend) break;  // rows longer than one batch per thread take further round trips
+#pragma unroll
+    for (int k = 0; k < kInFlight; ++k) {
+      const long long v = v0 + static_cast<long long>(k) * kThreads;
+      q[k] = v < vend ? __ldg(xv + v) : make_uint4(0, 0, 0, 0);
     }
   }
   // head goes to the first CTA, tail to the last
   if (c == 0) {
-    for (long long i = tid; i < head; i += kThreads) Consider(bv, bi, ToFloat(xr[i]), static_cast<int>(i));
+    for (long long i = tid; i < head; i += kThreads) best.Any(ToFloat(xr[i]), i);
   }
   if (c == C - 1) {
-    for (long long i = tail_begin + tid; i < V; i += kThreads) Consider(bv, bi, ToFloat(xr[i]), static_cast<int>(i));
+    for (long long i = head + nvec * kVecElems + tid; i < V; i += kThreads) best.Any(ToFloat(xr[i]), i);
   }
 
-  WarpReduce(bv, bi);
-  if (lane == 0) {
-    s_wv[warp] = bv;
-    s_wi[warp] = bi;
-  }
+  const unsigned long long wkey = WarpMaxKey(best.Key());
+  if (lane == 0 && wkey != 0ull) atomicMax(&s_best, wkey);
   __syncthreads();
-  if (warp == 0) {
-    float v = lane < kWarps ? s_wv[lane] : 0.f;
-    int i = lane < kWarps ? s_wi[lane] : kNone;
-    WarpReduce(v, i);
-    if (lane == 0) {
-      s_cv = v;
-      s_ci = i;
-    }
+
+  // the key of a NaN carries no payload: a NaN winner's value is read back from the row, bit for bit
+  auto write_out = [&](unsigned long long key, bool ok) {
+    const long long i = KeyIndex(key);
+    idx_out[row] = ok ? i : -1;
+    if (val_out != nullptr) val_out[row] = (ok && (key >> 32) == 0xFFFFFFFFull) ? ToFloat(xr[i]) : KeyValue(key);
+  };
+  if (C == 1) {
+    if (tid == 0) write_out(s_best, true);
+    return;
   }
-  cg::cluster_group cluster = cg::this_cluster();
-  cluster.sync();
-  if (c == 0 && warp == 0) {
-    float v = 0.f;
-    int i = kNone;
-    if (lane < C) {
-      v = *cluster.map_shared_rank(&s_cv, lane);
-      i = *cluster.map_shared_rank(&s_ci, lane);
+  // every CTA of the cluster has started (so CTA 0's mbarrier exists) before anybody arrives on it
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (c != 0) {
+    if (tid == 0) {
+      uint32_t slot, bar;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(slot) : "r"(SharedAddr(&s_slot[c])));
+      asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(bar) : "r"(SharedAddr(&s_bar)));
+      asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(slot), "l"(s_best) : "memory");
+      asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
     }
-    WarpReduce(v, i);
-    if (lane == 0) {
-      idx_out[row] = i;
-      if (val_out != nullptr) val_out[row] = v;
-    }
+    return;  // nobody reads this CTA's shared memory: it may leave
   }
-  cluster.sync();
+  if (tid < 32) {
+    uint32_t done = 0;
+    for (int spin = 0; spin < kPeerSpin && !done; ++spin) {
+      asm volatile("{ .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], 0;\n selp.u32 %0, 1, 0, p;\n}"
+                   : "=r"(done)
+                   : "r"(SharedAddr(&s_bar))
+                   : "memory");
+    }
+    unsigned long long key = 0ull;
+    if (done) key = lane == 0 ? s_best : (lane < C ? s_slot[lane] : 0ull);
+    key = WarpMaxKey(key);
+    if (lane == 0) write_out(key, done != 0);  // a wait that ran out (a peer CTA never arrived) leaves an index no row can have
+  }
 }
 
 template <typename T>
@@ -162,7 +175,7 @@ cudaError_t LaunchT(const T* x, int64_t rows, int64_t V, int64_t* idx, float* va
   // enough CTAs per row that each thread sees a few vectors; at most the portable cluster size
   const long long vecs = V / (16 / static_cast<long long>(sizeof(T)));
   int cluster = 1;
-  while (cluster < 8 && vecs > static_cast<long long>(cluster) * kThreads * 2) cluster *= 2;
+  while (cluster < kMaxCluster && vecs > static_cast<long long>(cluster) * kThreads * 2) cluster *= 2;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(cluster), static_cast<unsigned>(rows), 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
@@ -188,10 +201,8 @@ __global__ void LmheadCombineKernel(const unsigned long long* __restrict__ keys,
     const unsigned long long k = keys[static_cast<size_t>(r) * m + row];
     best = k > best ? k : best;
   }
-  const uint32_t ord = static_cast<uint32_t>(best >> 32);
-  const uint32_t bits = (ord == 0xFFFFFFFFu) ? 0x7FC00000u : ((ord & 0x80000000u) ? (ord & 0x7FFFFFFFu) : ~ord);
-  if (idx != nullptr) idx[row] = static_cast<long long>(0xFFFFFFFFu - static_cast<uint32_t>(best));
-  if (val != nullptr) val[row] = __uint_as_float(bits);
+  if (idx != nullptr) idx[row] = KeyIndex(best);
+  if (val != nullptr) val[row] = KeyValue(best);
 }
 
 }  // namespace

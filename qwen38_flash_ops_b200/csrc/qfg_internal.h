@@ -38,11 +38,14 @@ inline ModeGeom GeomOf(int mode, int wide = 1) {
     default: return wide == 2 ? ModeGeom{16, 8, 256, 128} : ModeGeom{16, 8, 128, 64};
   }
 }
-// Dynamic shared memory up to which a CTA leaves the SM a useful L1 (the 164 KB carve-out less the kernels' static
-// shared memory).  The NVFP4 warp rings copy their scale bytes through L1, where the four column warps that share a
-// 32-byte sector of scales fetch it from L2 once; with a larger carve-out the lines are evicted before they are shared
-// and the same copies were measured 40 % slower, so the ring depth stays within this budget.
+// The NVFP4 warp rings copy their scale bytes through L1, where the four column warps that share a 32-byte sector of
+// scales fetch it from L2 once.  That needs L1 room beside the CTA's shared memory: measured on the 151936-column
+// head, 102.6 us with a 132 KB carve-out, 108 us with 196 KB, 153 us with 228 KB (the lines are evicted before they
+// are shared).  The ring depth is chosen to stay within the 164 KB carve-out where a depth fits it (kL1FriendlySmem:
+// that carve-out less the kernels' static shared memory), and past the 196 KB carve-out (kL1UsableSmem) the scale
+// bytes bypass L1 like everything else.
 constexpr size_t kL1FriendlySmem = 161 * 1024;
+constexpr size_t kL1UsableSmem = 193 * 1024;
 // Bytes of one k-step of one warp in the ring of the direct kernel.
 inline int RingSlotBytes(int mode) { return mode == kNvfp4 ? 1584 : 2048; }
 // The same for the tcgen05 kernel, which keeps the older slot layout.

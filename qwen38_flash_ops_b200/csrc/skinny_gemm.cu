@@ -40,6 +40,7 @@
 #include <type_traits>
 #include <utility>
 
+#include "argmax_key.cuh"
 #include "qfg_internal.h"
 
 namespace qfg {
@@ -216,18 +217,6 @@ __device__ __forceinline__ bool Better(float av, long long ai, float bv, long lo
   if (bv != bv) return false;
   return av > bv || (av == bv && ai < bi);
 }
-// A 64-bit word whose unsigned order is the Better order; every real candidate maps above 0.
-__device__ __forceinline__ unsigned long long PackKey(float v, long long idx) {
-  uint32_t ord;
-  if (v != v) {
-    ord = 0xFFFFFFFFu;
-  } else {
-    const uint32_t b = (v == 0.f) ? 0u : __float_as_uint(v);
-    ord = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-  }
-  return (static_cast<unsigned long long>(ord) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(idx));
-}
-
 // W: 16-column groups a thread of the NVFP4 direct kernel owns.  With W = 2 a warp covers 256
 // columns and thread group g owns groups g and g + 8 of them, i.e. two 8-byte runs 64 bytes
 // apart in every row: fewer partly used sectors and less loop overhead per weight, and the
@@ -670,11 +659,8 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
   // of the high words, then the maximum of the low words among the lanes that hold that high word.
   auto flush_row = [&](int m) {
     if (!lm) return;
-    const unsigned long long key = cur_i < 0 ? 0ull : PackKey(cur_v, cur_i);
-    const uint32_t hi = static_cast<uint32_t>(key >> 32);
-    const uint32_t top = __reduce_max_sync(0xffffffffu, hi);
-    const uint32_t low = __reduce_max_sync(0xffffffffu, hi == top ? static_cast<uint32_t>(key) : 0u);
-    if (lane == 0) sh.best_i[warp][m] = static_cast<long long>((static_cast<unsigned long long>(top) << 32) | low);
+    const unsigned long long key = WarpMaxKey(cur_i < 0 ? 0ull : PackKey(cur_v, cur_i));
+    if (lane == 0) sh.best_i[warp][m] = static_cast<long long>(key);
     cur_v = 0.f;
     cur_i = -1;
   };
@@ -881,10 +867,8 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
         key = tail_best > key ? tail_best : key;
       }
       if (tid < M) {
-        const uint32_t ord = static_cast<uint32_t>(key >> 32);
-        const uint32_t bits = (ord == 0xFFFFFFFFu) ? 0x7FC00000u : ((ord & 0x80000000u) ? (ord & 0x7FFFFFFFu) : ~ord);
-        if (p.lm_idx != nullptr) p.lm_idx[tid] = static_cast<long long>(0xFFFFFFFFu - static_cast<uint32_t>(key));
-        if (p.lm_val != nullptr) p.lm_val[tid] = __uint_as_float(bits);
+        if (p.lm_idx != nullptr) p.lm_idx[tid] = KeyIndex(key);
+        if (p.lm_val != nullptr) p.lm_val[tid] = KeyValue(key);
         if (p.lm_key_out != nullptr) p.lm_key_out[tid] = key;
       }
       if (tid == 0) *p.lm_count = 0u;
@@ -2274,7 +2258,7 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
     if (smem < 120 * 1024) smem = 120 * 1024;
   }
   if (g_max_dynamic_smem > 0 && smem > static_cast<size_t>(g_max_dynamic_smem)) return cudaErrorInvalidConfiguration;
-  p.scales_l1 = smem <= kL1FriendlySmem ? 1 : 0;
+  p.scales_l1 = smem <= kL1UsableSmem ? 1 : 0;
   p.tail_groups = plan.tail;
   // K slices per shared group: one per idle warp as far as they go, at most kMaxTailSplit
   p.tail_split = plan.tail > 0 ? std::max(1, std::min(kMaxTailSplit, plan.tiles[0] * plan.wk / plan.tail)) : 1;
