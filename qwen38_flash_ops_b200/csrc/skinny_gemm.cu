@@ -349,6 +349,7 @@ struct SharedScratch {
   float gate[kMaxRows];  // SharedExpertDown: the BF16 sigmoid gate of every row (best_v holds its partial sums first)
   int last;
   int xfail;  // sharded LM head: a wait for a peer's keys ran out in this call
+  unsigned long long rowkey[kMaxRows];  // fused LM head: the CTA's best key of every row (atomicMax of the warps' bests)
 };
 
 // The BF16 arithmetic of SharedExpertDown (src/common/sigmoid_acc.cuh:12-21, skinny_gemm.cuh:73-80): sigmoid
@@ -655,26 +656,40 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
       }
     }
   };
-  // The warp's best of row m as a key whose unsigned order is the Better order (0 = no candidate): the maximum
-  // of the high words, then the maximum of the low words among the lanes that hold that high word.
+  // The warp's best of row m joins the CTA's best of that row: keys (argmax_key.cuh), two redux per warp, one
+  // shared-memory atomicMax.
   auto flush_row = [&](int m) {
     if (!lm) return;
     const unsigned long long key = WarpMaxKey(cur_i < 0 ? 0ull : PackKey(cur_v, cur_i));
-    if (lane == 0) sh.best_i[warp][m] = static_cast<long long>(key);
+    if (lane == 0 && key != 0ull) atomicMax(&sh.rowkey[m], key);
     cur_v = 0.f;
     cur_i = -1;
   };
+  if (tid < kMaxRows) sh.rowkey[tid] = 0ull;
+  __syncthreads();
+
+  // All rows are finished side by side: a warp works on one row at a time - wpr warps per row, every lane on
+  // columns 32 wpr apart in increasing order - so the rows' shared-memory (or cluster) round trips overlap
+  // instead of following one another, and a warp reduces its candidates once per row it touches.
+  const int nwarps = nthreads >> 5;
+  const int wpr = max(1, nwarps / M), rows_per_pass = max(1, nwarps / wpr);
+  const int my_row = warp / wpr, my_part = warp - my_row * wpr;
+  auto for_my_columns = [&](int share, auto&& value) {  // value(m, j): column j of this CTA's share, 0 <= j < share
+    for (int m0 = 0; m0 < M; m0 += rows_per_pass) {
+      const int m = m0 + my_row;
+      if (my_row < rows_per_pass && m < M) {
+        for (int j = my_part * 32 + lane; j < share; j += wpr * 32) value(m, j);
+        flush_row(m);
+      }
+    }
+  };
 
   if (C == 1) {
-    for (int m = 0; m < M; ++m) {
-      const float inv = sh.inv_scale[m];
-      for (int c = tid; c < ncols; c += nthreads) {
-        float sum = 0.f;
-        for (int w = 0; w < nparts; ++w) sum += red[(w * M + m) * TNc + RedCol(c, m)];
-        finalize(m, c, sum * inv);
-      }
-      flush_row(m);
-    }
+    for_my_columns(ncols, [&](int m, int c) {
+      float sum = 0.f;
+      for (int w = 0; w < nparts; ++w) sum += red[(w * M + m) * TNc + RedCol(c, m)];
+      finalize(m, c, sum * sh.inv_scale[m]);
+    });
   } else {
     for (int m = 0; m < M; ++m) {
       const float inv = sh.inv_scale[m];
@@ -688,9 +703,11 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
     cluster.sync();
     const int cper = (TNc + C - 1) / C;  // the last rank's share may be short (any C <= 8)
     const int cb = tl.crank * cper;
+    const int share = max(0, min(cper, ncols - cb));
     // The C partial sums of an output come from C CTAs' shared memory: all eight possible loads are issued
     // before the first is used (one round trip through the cluster network instead of C), then added in rank order.
-    auto rank_sum = [&](int idx) {
+    for_my_columns(share, [&](int m, int j) {
+      const int idx = m * TNc + cb + j;
       float v[8];
 #pragma unroll
       for (int r = 0; r < 8; ++r) v[r] = r < C ? cluster.map_shared_rank(part, r)[idx] : 0.f;
@@ -699,25 +716,8 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
       for (int r = 0; r < 8; ++r) {
         if (r < C) sum += v[r];
       }
-      return sum;
-    };
-    if (!lm) {
-      // without the argmax nothing ties an output to its row: every (row, column) of this rank's share is one item
-      const int items = M * cper;
-      for (int i = tid; i < items; i += nthreads) {
-        const int m = i / cper, c = cb + (i - m * cper);
-        if (c < ncols) finalize(m, c, rank_sum(m * TNc + c));
-      }
-    } else {
-      for (int m = 0; m < M; ++m) {
-        for (int cc = tid; cc < cper; cc += nthreads) {
-          const int c = cb + cc;
-          if (c >= ncols) break;
-          finalize(m, c, rank_sum(m * TNc + c));
-        }
-        flush_row(m);
-      }
-    }
+      finalize(m, cb + j, sum);
+    });
     cluster.sync();
   }
 
@@ -726,11 +726,8 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
     auto fold_into_keys = [&]() {
       __syncthreads();
       if (tid < M) {
-        unsigned long long best = 0ull;
-        for (int w = 0; w < (nthreads >> 5); ++w) {
-          const unsigned long long k = static_cast<unsigned long long>(sh.best_i[w][tid]);
-          best = k > best ? k : best;
-        }
+        const unsigned long long best = sh.rowkey[tid];
+        sh.rowkey[tid] = 0ull;
         if (best != 0ull) atomicMax(p.lm_keys + tid, best);
         __threadfence();
       }
@@ -792,12 +789,7 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
         }
         // no other CTA is left to see these keys: they join the global ones in registers below
         __syncthreads();
-        if (tid < M) {
-          for (int w = 0; w < (nthreads >> 5); ++w) {
-            const unsigned long long k = static_cast<unsigned long long>(sh.best_i[w][tid]);
-            tail_best = k > tail_best ? k : tail_best;
-          }
-        }
+        if (tid < M) tail_best = sh.rowkey[tid];
       }
       unsigned long long key = 0ull;  // thread m < M: the winning key of row m
       if (p.xworld > 1) {
