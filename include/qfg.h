@@ -194,7 +194,7 @@ QFG_API void qfg_untile_hc_destroy(qfg_untile_hc* op);
  * orders (value, index) pairs exactly like ArgmaxRows does - larger is better - which is the
  * payload the N-sharded LM head all-gathers; qfg_lmhead_combine folds the gathered words.
  *
- * `workspace` is qfg_lmhead_workspace_bytes() bytes of device memory (about 256 KB: 256 bytes of
+ * `workspace` is qfg_lmhead_workspace_bytes() bytes of device memory (about 512 KB: 256 bytes of
  * keys and a counter, then room for the FP32 partial sums of column groups that the CTAs share
  * when the vocabulary does not divide evenly among them).  Its first 256 bytes must be zero
  * before the first call; each call leaves them zero again.  Calls that share a workspace must

@@ -378,6 +378,7 @@ void ChooseTail(const PlanInput& in, bool forced, Plan* plan) {
   if (forced) tail = want;  // tests: any count that leaves whole groups per CTA
   if (tail < 1 || tail > kMaxTailGroups || tail >= groups || (groups - tail) % ctas != 0) return;
   if ((groups - tail) / ctas > plan->wn - 1) return;
+  if (tail > ctas * plan->wk) return;  // every left-over group needs an idle warp of its own
   plan->tail = tail;
 }
 

@@ -91,6 +91,8 @@ struct Segment {
   int tile_begin = 0;
   int tiles = 0;
   int granules = 0;
+  int gran_quot = 0;  // granules / tiles and granules % tiles: tile t starts at granule t * quot + t * rem / tiles
+  int gran_rem = 0;   // (32-bit arithmetic on the device; tiles < 65536)
   int out_begin = 0;
   int out_end = 0;
   int tail_cols = 0;  // trailing columns left out of the column tiles (fused LM head, see GemmParams::tail_groups)
@@ -134,9 +136,12 @@ struct GemmParams {
   // CTAs, which would then run 12 % longer than the rest: warps that have no columns of their own (the last
   // warp column of every CTA) each take one of `tail_split` slices of the K range of one left-over group,
   // store the FP32 partial sums to `lm_tail` ([group][slice][8 rows][128]), and the last CTA to arrive adds
-  // the slices up in slice order.
+  // the slices up in slice order.  `tail_stride` > 0: slice j of the groups * split runs in CTA j * tail_stride
+  // (one per CTA, evenly spread: a CTA that hosts several runs that much longer than the rest); 0: the idle
+  // warps take the slices in order, CTA by CTA (launches with fewer CTAs than slices).
   int tail_groups = 0;
   int tail_split = 1;
+  int tail_stride = 0;
   float* lm_tail = nullptr;
 
   // SharedExpertDown (fuse != 0): x is replaced by swish_mul(x, x2) while it is staged, and the output is
@@ -166,7 +171,7 @@ struct LmExchange {
 };
 
 constexpr int kMaxTailGroups = 8;
-constexpr int kMaxTailSplit = 8;
+constexpr int kMaxTailSplit = 16;
 constexpr size_t kLmHeaderBytes = 256;  // keys, counter, padding
 constexpr size_t kLmTailBytes = static_cast<size_t>(kMaxTailGroups) * kMaxTailSplit * kMaxRows * 128 * 4;
 

@@ -327,14 +327,21 @@ __device__ __forceinline__ Tile LocateTile(const GemmParams& p) {
   for (int i = 1; i < kMaxSeg; ++i) s += (i < p.nseg && static_cast<int>(blockIdx.x) >= p.seg[i].tile_begin) ? 1 : 0;
   tl.seg = s;
   const Segment& sg = p.seg[s];
-  const int t = static_cast<int>(blockIdx.x) - sg.tile_begin;
-  tl.n0 = static_cast<int>(static_cast<long long>(t) * sg.granules / sg.tiles) * p.gran;
-  tl.n1 = min(sg.n - sg.tail_cols, static_cast<int>(static_cast<long long>(t + 1) * sg.granules / sg.tiles) * p.gran);
+  // tile t covers granules [t G / T, (t + 1) G / T): in 32 bits, from G = quot T + rem (a 64-bit division is
+  // a hundred instructions, and this is the first thing every CTA does)
+  const unsigned t = blockIdx.x - static_cast<unsigned>(sg.tile_begin), T = static_cast<unsigned>(sg.tiles);
+  const unsigned g0 = t * sg.gran_quot + t * sg.gran_rem / T, g1 = (t + 1) * sg.gran_quot + (t + 1) * sg.gran_rem / T;
+  tl.n0 = static_cast<int>(g0) * p.gran;
+  tl.n1 = min(sg.n - sg.tail_cols, static_cast<int>(g1) * p.gran);
   tl.C = static_cast<int>(gridDim.y);
   tl.crank = static_cast<int>(blockIdx.y);
-  const int ksteps_total = (p.K + 15) >> 4;
-  tl.kbeg = static_cast<int>(static_cast<long long>(tl.crank) * ksteps_total / tl.C) * 16;
-  tl.kend = min(p.K, static_cast<int>(static_cast<long long>(tl.crank + 1) * ksteps_total / tl.C) * 16);
+  tl.kbeg = 0;
+  tl.kend = p.K;
+  if (tl.C > 1) {
+    const unsigned ksteps_total = static_cast<unsigned>(p.K + 15) >> 4, C = gridDim.y, r = blockIdx.y;
+    tl.kbeg = static_cast<int>(r * ksteps_total / C) * 16;
+    tl.kend = min(p.K, static_cast<int>((r + 1) * ksteps_total / C) * 16);
+  }
   tl.kslice = max(0, tl.kend - tl.kbeg);
   return tl;
 }
@@ -369,6 +376,19 @@ __device__ __forceinline__ uint32_t SwishMulWord(uint32_t g2, uint32_t u2) {  //
 }
 
 // max / min-nonzero of the two BF16 magnitudes packed in a word
+// Measurement aid, compiled in only with -DQFG_PHASE_TIMES: thread 0 of every CTA records the global timer
+// at the phase boundaries into GemmParams::phase_times ([CTA][16]).
+#ifdef QFG_PHASE_TIMES
+__device__ __forceinline__ void Stamp(const GemmParams& p, int slot) {
+  if (p.phase_times != nullptr && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.phase_times[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16 + slot] = t;
+  }
+}
+#else
+__device__ __forceinline__ void Stamp(const GemmParams&, int) {}
+#endif
 __device__ __forceinline__ void TrackWord(uint32_t w, uint32_t& mx, uint32_t& mn) {
   const uint32_t lo = w & 0x7FFFu, hi = (w >> 16) & 0x7FFFu;
   mx = max(mx, max(lo, hi));
@@ -549,6 +569,132 @@ __device__ __forceinline__ bool StageXImpl(const GemmParams& p, const Tile& tl, 
       }
       __syncthreads();
     }
+    return slow;
+  }
+}
+
+// Asynchronous staging of x for the warp-ring kernel.  The x loads of the staging above are issued after the
+// ring prologue and queue behind its weight copies (50 - 130 KB per SM, one to three microseconds of the SM's
+// share of the bandwidth) while every warp waits for them.  Here the CTA's K slice of x is copied raw into its
+// place in shared memory with 16-byte cp.async BEFORE the weight copies are issued - the copy group is the
+// oldest, so `cp.async.wait_group <weight groups>` completes it - and converted in place afterwards, while the
+// weights are in flight.  Needs 16-byte rows of x (x 16-byte aligned, K % 8 == 0).
+__device__ __forceinline__ bool XRowsAre16ByteAligned(const GemmParams& p) {
+  return (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.K % 8 == 0);
+}
+// Which 16-byte items of the staged x a thread handles.  A warp works on one row at a time (warp w on row
+// w mod M, the warps of a row sharing its items; with fewer warps than rows, on rows w, w + warps, ...), so a
+// row's maximum is reduced once per warp, and nothing here divides per item.  f(live, kk): elements kk .. kk + 7
+// of the row, `live` false past the row's end (the trip count is warp-uniform); row_done(m) after each row.
+template <class F, class G>
+__device__ __forceinline__ void ForMyXItems(const GemmParams& p, const Tile& tl, F&& f, G&& row_done) {
+  const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5, M = static_cast<unsigned>(p.M);
+  const int chunks = ((tl.kslice + 15) & ~15) >> 3;
+  const unsigned part = warp / M, row0 = warp - part * M;
+  const unsigned cnt = nwarps > M ? (nwarps - row0 + M - 1) / M : 1u;  // warps that share row0
+#pragma unroll 1
+  for (unsigned m = row0; m < M; m += nwarps) {
+#pragma unroll 1
+    for (int c0 = static_cast<int>(32u * part); c0 < chunks; c0 += static_cast<int>(32u * cnt)) {
+      const int c = c0 + static_cast<int>(lane);
+      f(c < chunks, static_cast<int>(m), c * 8);
+    }
+    row_done(static_cast<int>(m));
+  }
+}
+__device__ __forceinline__ void XCopyIssue(const GemmParams& p, const Tile& tl, uint16_t* xs) {
+  if (tl.kslice <= 0) return;
+  const uint32_t base = SmemAddr(xs);
+  ForMyXItems(
+      p, tl,
+      [&](bool live, int m, int kk) {
+        if (!live) return;
+        const bool in = kk < tl.kslice;  // the slice is padded to whole k-steps with zeros
+        const uint16_t* src = p.x + static_cast<size_t>(m) * p.K + tl.kbeg + kk;
+        CpAsync16(base + static_cast<uint32_t>(m * p.xpitch + kk) * 2u, in ? src : p.x, in ? 16 : 0);
+      },
+      [](int) {});
+}
+// Second half: every thread's copies have completed (cp.async.wait_group).  Must be called by every thread of
+// the CTA.  Returns true if the CTA must take the BF16 path.
+template <int MODE>
+__device__ __forceinline__ bool StageXConvert(const GemmParams& p, const Tile& tl, uint16_t* xs, SharedScratch& sh) {
+  const int tid = threadIdx.x, lane = tid & 31, M = p.M;
+  if (tid < kMaxRows) {
+    sh.rmax[tid] = 0;
+    sh.rmin[tid] = 0x7FFFu;
+    sh.inv_scale[tid] = 1.f;
+  }
+  __syncthreads();  // the raw rows are visible to every thread
+  if constexpr (MODE == kBf16) {
+    return false;
+  } else {
+    if (tl.kslice <= 0) return false;
+    uint32_t* xw = reinterpret_cast<uint32_t*>(xs);
+    uint32_t mx = 0, mn = 0x7FFFu;
+    ForMyXItems(
+        p, tl,
+        [&](bool live, int m, int kk) {
+          if (live) {
+            const uint4 q = *reinterpret_cast<const uint4*>(xw + ((m * p.xpitch + kk) >> 1));
+            TrackWord(q.x, mx, mn);
+            TrackWord(q.y, mx, mn);
+            TrackWord(q.z, mx, mn);
+            TrackWord(q.w, mx, mn);
+          }
+        },
+        [&](int m) {
+          mx = __reduce_max_sync(0xffffffffu, mx);
+          mn = __reduce_min_sync(0xffffffffu, mn);
+          if (lane == 0) {
+            atomicMax(&sh.rmax[m], mx);
+            atomicMin(&sh.rmin[m], mn);
+          }
+          mx = 0;
+          mn = 0x7FFFu;
+        });
+    __syncthreads();
+    // Power-of-two scale per row that puts the slice maximum in [2^14, 2^15).  Every non-zero element must
+    // land in the normal FP16 range: exponent no more than 28 below the maximum's.
+    bool ok = !p.force_slow;
+#pragma unroll 1
+    for (int m = 0; m < M; ++m) {
+      const uint32_t a = sh.rmax[m];
+      const int e = static_cast<int>(a >> 7);  // BF16 exponent field of the row maximum
+      if (a != 0 && (e < 32 || e >= 255 || static_cast<int>(sh.rmin[m] >> 7) < e - 28)) ok = false;
+    }
+    const bool slow = !ok;
+    auto scale_of = [&](int m) {
+      const uint32_t a = sh.rmax[m];
+      return (!slow && a != 0) ? __uint_as_float((268u - (a >> 7)) << 23) : 1.f;
+    };
+    if (tid < M) {  // for the epilogue, which runs behind further barriers
+      const float sc = scale_of(tid);
+      sh.scale[tid] = sc;
+      sh.inv_scale[tid] = 1.f / sc;
+    }
+    if (!slow) {
+      float sc = 1.f;
+      int sc_row = -1;
+      ForMyXItems(
+          p, tl,
+          [&](bool live, int m, int kk) {
+            if (!live) return;
+            if (m != sc_row) {
+              sc = scale_of(m);
+              sc_row = m;
+            }
+            uint4* px = reinterpret_cast<uint4*>(xw + ((m * p.xpitch + kk) >> 1));
+            uint4 q = *px;
+            q.x = ScaleToHalf2(q.x, sc);
+            q.y = ScaleToHalf2(q.y, sc);
+            q.z = ScaleToHalf2(q.z, sc);
+            q.w = ScaleToHalf2(q.w, sc);
+            *px = q;
+          },
+          [](int) {});
+    }
+    __syncthreads();
     return slow;
   }
 }
@@ -749,43 +895,22 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
         __threadfence();
         const int n_main = sg.n - p.tail_groups * 128;
         const int tcols = p.tail_groups * 128;
-        if (tcols <= nthreads) {
-          // This runs after every other CTA has finished, so it is all on the critical path: a thread owns one
-          // column, and the loads of all its rows and slices are issued before the first sum is used (one
-          // round trip to L2 instead of one per row).  The slices are still added in slice order.
-          float sums[kMaxRows];
+        // This runs after every other CTA has finished, so it is all on the critical path.  One output (row,
+        // shared column) per thread and pass: all its slices are loaded before the first is added (one round
+        // trip to L2), still in slice order.  A group is 128 columns wide, so the 32 outputs of a warp belong
+        // to one row, which flush_row needs.
+        const int outs = M * tcols;
+        for (int o = tid; o < outs; o += nthreads) {
+          const int m = o / tcols, j = o - m * tcols;
+          const float* src = p.lm_tail + (static_cast<size_t>(j >> 7) * p.tail_split * kMaxRows + m) * 128 + (j & 127);
+          float part[kMaxTailSplit];
 #pragma unroll
-          for (int m = 0; m < kMaxRows; ++m) {
-            float part[kMaxTailSplit];
+          for (int c = 0; c < kMaxTailSplit; ++c) part[c] = c < p.tail_split ? __ldcg(src + static_cast<size_t>(c) * kMaxRows * 128) : 0.f;
+          float sum = 0.f;
 #pragma unroll
-            for (int c = 0; c < kMaxTailSplit; ++c) {
-              part[c] = 0.f;
-              if (m < M && tid < tcols && c < p.tail_split)
-                part[c] = __ldcg(p.lm_tail + ((static_cast<size_t>(tid >> 7) * p.tail_split + c) * kMaxRows + m) * 128 + (tid & 127));
-            }
-            float sum = 0.f;
-#pragma unroll
-            for (int c = 0; c < kMaxTailSplit; ++c) sum += part[c];
-            sums[m] = sum;
-          }
-#pragma unroll
-          for (int m = 0; m < kMaxRows; ++m) {
-            if (m < M) {
-              if (tid < tcols) finalize(m, n_main + tid - n0, sums[m] * sh.inv_scale[m]);
-              flush_row(m);
-            }
-          }
-        } else {
-          for (int m = 0; m < M; ++m) {
-            for (int j = tid; j < tcols; j += nthreads) {
-              const int col = j & 127, tg = j >> 7;
-              const float* src = p.lm_tail + (static_cast<size_t>(tg) * p.tail_split * kMaxRows + m) * 128 + col;
-              float sum = 0.f;
-              for (int c = 0; c < p.tail_split; ++c) sum += __ldcg(src + static_cast<size_t>(c) * kMaxRows * 128);
-              finalize(m, n_main + j - n0, sum * sh.inv_scale[m]);
-            }
-            flush_row(m);
-          }
+          for (int c = 0; c < kMaxTailSplit; ++c) sum += part[c];
+          finalize(m, n_main + j - n0, sum * sh.inv_scale[m]);
+          flush_row(m);
         }
         // no other CTA is left to see these keys: they join the global ones in registers below
         __syncthreads();
@@ -922,19 +1047,6 @@ __device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, fl
 //     groups a warp-wide shared-memory load touches into distinct banks.
 // A lane owns up to kPieces pieces; their sources are one 64-bit base, advanced by a k-step
 // stride per step, plus a 32-bit offset each.
-// Measurement aid, compiled in only with -DQFG_PHASE_TIMES: thread 0 of every CTA records the global timer
-// at the phase boundaries into GemmParams::phase_times ([CTA][16]).
-#ifdef QFG_PHASE_TIMES
-__device__ __forceinline__ void Stamp(const GemmParams& p, int slot) {
-  if (p.phase_times != nullptr && threadIdx.x == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    p.phase_times[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 16 + slot] = t;
-  }
-}
-#else
-__device__ __forceinline__ void Stamp(const GemmParams&, int) {}
-#endif
 template <typename T>
 __device__ __forceinline__ void Pin(T& v) {
   asm volatile("" : "+r"(v));  // keeps a loop invariant in its register instead of being recomputed
@@ -1340,18 +1452,33 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const _
   int stream_col = colwarp;
   if constexpr (MODE == kNvfp4) {
     if (p.tail_groups > 0 && !warp_has_cols && wn == p.wn - 1) {
-      tail_index = static_cast<int>(blockIdx.x) * p.wk + wk;  // one (group, K slice) per idle warp
-      if (tail_index < p.tail_groups * p.tail_split) {
+      // one (group, K slice) per idle warp: spread over the CTAs, or in order where the CTAs are few
+      bool mine = true;
+      if (p.tail_stride > 0) {
+        tail_index = static_cast<int>(blockIdx.x) / p.tail_stride;
+        mine = tail_index * p.tail_stride == static_cast<int>(blockIdx.x) && wk == tail_index % p.wk;
+      } else {
+        tail_index = static_cast<int>(blockIdx.x) * p.wk + wk;
+      }
+      if (mine && tail_index < p.tail_groups * p.tail_split) {
         tail_worker = true;
         const int tg = tail_index / p.tail_split, slice = tail_index - tg * p.tail_split;
-        first_step = static_cast<int>(static_cast<long long>(slice) * ksteps / p.tail_split);
-        step_count = static_cast<int>(static_cast<long long>(slice + 1) * ksteps / p.tail_split) - first_step;
+        const unsigned split = static_cast<unsigned>(p.tail_split);
+        first_step = static_cast<int>(static_cast<unsigned>(slice) * ksteps / split);
+        step_count = static_cast<int>(static_cast<unsigned>(slice + 1) * ksteps / split) - first_step;
         step_stride = 1;
         stream_col = sg.n - p.tail_groups * 128 + tg * 128;
       }
     }
   }
 
+  // x first (unless it is still the predecessor kernel's to write): its copies then do not queue behind the weights
+  uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
+  const bool x_async = !p.fuse && XRowsAre16ByteAligned(p);
+  if (x_async && !p.pdl_wait) {
+    XCopyIssue(p, tl, xs);
+    CpAsyncCommit();
+  }
   // weights do not depend on the predecessor kernel: get the first k-steps in flight, then wait
   WarpRing<MODE, DEPTH> ring;
   ring.Setup(tl, sg, stream_col, cvalid, first_step, step_count, step_stride, ring_addr);
@@ -1360,8 +1487,19 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const _
   if (p.pdl_wait) GridDependencyWait();
   Stamp(p, 1);
 
-  uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
-  const bool slow = StageX<MODE>(p, tl, xs, sh);
+  bool slow;
+  if (x_async) {
+    if (p.pdl_wait) {  // x belongs to the predecessor until now
+      XCopyIssue(p, tl, xs);
+      CpAsyncCommit();
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
+    }
+    slow = StageXConvert<MODE>(p, tl, xs, sh);
+  } else {
+    slow = StageX<MODE>(p, tl, xs, sh);
+  }
   Stamp(p, 2);
 
   float acc[NM][4];
@@ -2252,8 +2390,18 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
   if (g_max_dynamic_smem > 0 && smem > static_cast<size_t>(g_max_dynamic_smem)) return cudaErrorInvalidConfiguration;
   p.scales_l1 = smem <= kL1UsableSmem ? 1 : 0;
   p.tail_groups = plan.tail;
-  // K slices per shared group: one per idle warp as far as they go, at most kMaxTailSplit
-  p.tail_split = plan.tail > 0 ? std::max(1, std::min(kMaxTailSplit, plan.tiles[0] * plan.wk / plan.tail)) : 1;
+  // K slices per shared group: at most kMaxTailSplit, one per CTA where there are enough CTAs, else one per idle warp
+  p.tail_split = 1;
+  p.tail_stride = 0;
+  if (plan.tail > 0) {
+    const int ctas = plan.tiles[0];
+    if (ctas >= 2 * plan.tail) {
+      p.tail_split = std::min(kMaxTailSplit, ctas / plan.tail);
+      p.tail_stride = ctas / (plan.tail * p.tail_split);
+    } else {
+      p.tail_split = std::max(1, std::min(kMaxTailSplit, ctas * plan.wk / plan.tail));
+    }
+  }
   if (plan.tail > 0 && (!p.lm || p.lm_tail == nullptr || p.nseg != 1 || plan.cluster != 1)) return cudaErrorInvalidValue;
   int tiles = 0;
   for (int s = 0; s < p.nseg; ++s) {
@@ -2261,6 +2409,9 @@ cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStre
     p.seg[s].tiles = plan.tiles[s];
     p.seg[s].tail_cols = (s == 0) ? plan.tail * 128 : 0;
     p.seg[s].granules = (p.seg[s].n - p.seg[s].tail_cols + plan.gran - 1) / plan.gran;
+    if (plan.tiles[s] < 1 || plan.tiles[s] > 65535) return cudaErrorInvalidValue;
+    p.seg[s].gran_quot = p.seg[s].granules / plan.tiles[s];
+    p.seg[s].gran_rem = p.seg[s].granules % plan.tiles[s];
     tiles += plan.tiles[s];
   }
   switch (mode) {
