@@ -1647,6 +1647,13 @@ __global__ void __launch_bounds__(kRegThreads, 1) SkinnyGemmRegKernel(const __gr
     }
   };
 
+  // x first (unless it is still the predecessor kernel's to write): its copies then do not queue behind the weights
+  uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
+  const bool x_async = !p.fuse && XRowsAre16ByteAligned(p);
+  if (x_async && !p.pdl_wait) {
+    XCopyIssue(p, tl, xs);
+    CpAsyncCommit();
+  }
   // weights do not depend on the predecessor kernel: get the first k-steps in flight, then wait
   Raw<MODE> buf[D];
 #pragma unroll
@@ -1656,8 +1663,17 @@ __global__ void __launch_bounds__(kRegThreads, 1) SkinnyGemmRegKernel(const __gr
   Stamp(p, 1);
   if (p.pdl_wait) GridDependencyWait();
 
-  uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
-  const bool slow = StageX<MODE, false, false>(p, tl, xs, sh);
+  bool slow;
+  if (x_async) {
+    if (p.pdl_wait) {
+      XCopyIssue(p, tl, xs);
+      CpAsyncCommit();
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    slow = StageXConvert<MODE>(p, tl, xs, sh);
+  } else {
+    slow = StageX<MODE, false, false>(p, tl, xs, sh);
+  }
   Stamp(p, 2);
 
   float acc[NM][4];
