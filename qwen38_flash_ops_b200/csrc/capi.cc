@@ -549,14 +549,14 @@ int qfg_shared_expert_down_create(const float* w_scale, size_t n_w_scale, int tr
 int qfg_shared_expert_down_compute(const qfg_shared_expert_down* op, const void* g, const void* u, int64_t m, int64_t k,
                                    const qfg_tensor2d* weight, const void* gx, int64_t gk, const void* gw,
                                    const void* routed, int64_t n, void* out, void* stream) {
-  if (op == nullptr || weight == nullptr) return Fail(QFG_FAIL, "SharedExpertDown: null argument");
+  if (op == nullptr || weight == nullptr) return Fail(QFG_INVALID_ARGUMENT, "SharedExpertDown: null argument");
   try {
     if (m < 1 || n < 1 || n > INT_MAX || n % 8 != 0 || gk < 0 || gk > INT_MAX || gk % 2 != 0)
-      throw std::runtime_error("SharedExpertDown: shape mismatch");
+      throw InvalidArgument("SharedExpertDown: shape mismatch");
     if (g == nullptr || u == nullptr || gx == nullptr || gw == nullptr || out == nullptr ||
         reinterpret_cast<uintptr_t>(u) % 4 != 0 || reinterpret_cast<uintptr_t>(gx) % 2 != 0 ||
         reinterpret_cast<uintptr_t>(gw) % 2 != 0 || reinterpret_cast<uintptr_t>(routed) % 2 != 0) {
-      throw std::runtime_error("SharedExpertDown: null or misaligned input");
+      throw InvalidArgument("SharedExpertDown: null or misaligned input");
     }
     void* outs[1] = {out};
     Prepared pr = Prepare(op->gemm, g, m, k, weight, 1, outs, 1, true, n);
@@ -569,7 +569,7 @@ int qfg_shared_expert_down_compute(const qfg_shared_expert_down* op, const void*
     Run(op->gemm, pr, m, static_cast<cudaStream_t>(stream), "SharedExpertDown");
     return QFG_OK;
   } catch (const InvalidArgument& e) {
-    return Fail(QFG_FAIL, e.what());
+    return Fail(QFG_INVALID_ARGUMENT, e.what());
   } catch (const std::exception& e) {
     return Fail(QFG_FAIL, e.what());
   }

@@ -69,10 +69,13 @@ int64_t OptionalAttribute(const Ort::ConstKernelInfo& k, const char* name, int64
   }
 }
 
-// qfg status -> OrtStatus: INVALID_ARGUMENT and FAIL carry the same numeric codes as OrtErrorCode.
+// qfg status of a compute call -> OrtStatus.  Every compute-time error of the reference's ComputeV2 is ORT_FAIL
+// (fused_gemm.cu:589-591, :723-725, :775-777, :950-952, :1065-1067), whatever went wrong; the library's finer
+// code (QFG_INVALID_ARGUMENT / QFG_FAIL) stays in the message's source, qfg_last_error().  Errors of kernel
+// creation are ORT_INVALID_ARGUMENT, as in the reference's CreateKernelV2.
 OrtStatus* ToStatus(const OrtApi& api, int code) {
   if (code == QFG_OK) return nullptr;
-  return api.CreateStatus(code == QFG_INVALID_ARGUMENT ? ORT_INVALID_ARGUMENT : ORT_FAIL, qfg_last_error());
+  return api.CreateStatus(ORT_FAIL, qfg_last_error());
 }
 
 struct SkinnyGemmState {

@@ -46,3 +46,25 @@ def test_static_scratch_matches_workspace_entry_point(cuda):
     b = head(x1, pk, N)
     torch.cuda.synchronize()
     assert torch.equal(a[0], b[0]) and torch.equal(a[2], b[2])
+
+
+def test_static_scratch_on_a_side_stream_and_a_width_the_workspace_entry_would_share(cuda):
+    """594 column groups on 148 SMs leave two groups over: qfg_lmhead_compute shares them among its CTAs
+    (partial sums in the workspace), the static entry point has no room for that and runs the plain launch
+    shape, whose logits are SkinnyGemm's.  So its winners equal ArgmaxRows(SkinnyGemm(x)) bit for bit, on a
+    non-blocking side stream as well as on the default one."""
+    from qwen38_flash_ops_b200 import ArgmaxRows, SkinnyGemm
+
+    rng = np.random.default_rng(77)
+    K, N, m = 256, 128 * (148 * 4 + 2), 2
+    pk = to_dev(P.pack_nvfp4(P.synth_weight(rng, K, N)), "u8")
+    x = to_dev(P.synth_x(rng, m, K), "bf16")
+    eidx, eval_ = ArgmaxRows()(SkinnyGemm([1], [N])(x, pk)[0])
+    head = LmHeadArgmax()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    for stream in (torch.cuda.current_stream(), side, side):
+        with torch.cuda.stream(stream):
+            idx, val, _ = head.call_static(x, pk, N)
+        stream.synchronize()
+        assert torch.equal(idx, eidx) and torch.equal(val.view(torch.int32), eval_.view(torch.int32))
