@@ -79,6 +79,12 @@ struct qfg_skinny_gemm {
   // plans already computed for this node, keyed by the shape of the call
   mutable std::mutex plan_mu;
   mutable std::map<std::string, qfg::Plan> plans;
+  // the shape of the last call and its plan: a decode loop repeats one shape, and comparing a few integers is
+  // cheaper than building the map's key
+  mutable bool last_valid = false;
+  mutable qfg::PlanInput last_in;
+  mutable std::string last_spec;
+  mutable qfg::Plan last_plan;
   qfg_skinny_gemm() = default;
   qfg_skinny_gemm(const qfg_skinny_gemm& o)
       : seg_outs(o.seg_outs), widths(o.widths), trigger(o.trigger), d_w_scale(o.d_w_scale), w_scale_len(o.w_scale_len),
@@ -218,19 +224,44 @@ Prepared Prepare(const qfg_skinny_gemm& op, const void* x, int64_t m, int64_t k,
 
 qfg::Plan ComputePlan(const qfg_skinny_gemm& op, const qfg::PlanInput& in);
 
+bool SamePlanInput(const qfg::PlanInput& a, const qfg::PlanInput& b) {
+  if (a.K != b.K || a.nseg != b.nseg || a.mode != b.mode || a.row_align != b.row_align || a.sm_count != b.sm_count ||
+      a.max_rows != b.max_rows || a.max_clusters != b.max_clusters || a.allow_tail != b.allow_tail) {
+    return false;
+  }
+  for (int s = 0; s < a.nseg; ++s) {
+    if (a.n[s] != b.n[s]) return false;
+  }
+  return true;
+}
+
 qfg::Plan PlanFor(const qfg_skinny_gemm& op, qfg::PlanInput in, int rows) {
   in.max_rows = rows;
+  {
+    std::lock_guard<std::mutex> lock(op.plan_mu);
+    if (op.last_valid && SamePlanInput(op.last_in, in) && op.last_spec == op.plan_spec) return op.last_plan;
+  }
+  auto remember = [&](const qfg::Plan& plan) {  // caller holds plan_mu
+    op.last_in = in;
+    op.last_spec = op.plan_spec;
+    op.last_plan = plan;
+    op.last_valid = true;
+  };
   std::string key = std::to_string(in.K) + "/" + std::to_string(in.mode) + "/" + std::to_string(in.row_align) + "/" +
                     std::to_string(rows) + "/" + (in.max_clusters != nullptr ? "d" : "h") + (in.allow_tail ? "t" : "");
   for (int s = 0; s < in.nseg; ++s) key += "/" + std::to_string(in.n[s]);
   {
     std::lock_guard<std::mutex> lock(op.plan_mu);
     auto it = op.plans.find(key + "|" + op.plan_spec);
-    if (it != op.plans.end()) return it->second;
+    if (it != op.plans.end()) {
+      remember(it->second);
+      return it->second;
+    }
   }
   qfg::Plan plan = ComputePlan(op, in);
   std::lock_guard<std::mutex> lock(op.plan_mu);
   op.plans[key + "|" + op.plan_spec] = plan;
+  remember(plan);
   return plan;
 }
 
