@@ -420,6 +420,11 @@ def run_ours(args):
         dist.broadcast(x, 0)
     shard_bytes = k * n_local * 9 // 16
     total_bytes = wl.weight_bytes
+    # the generated inputs, so that a run elsewhere can be checked to stream the same bytes (torch's CUDA generator,
+    # seeds 100 + rank and 7); hashed on the host, outside every timed region
+    import hashlib
+    data_sha256 = {"x": hashlib.sha256(x.cpu().view(torch.int16).numpy()).hexdigest(),
+                   "weights_rank0": hashlib.sha256(shard.cpu().numpy()).hexdigest() if rank == 0 else None}
 
     verified = None
     exchange_note = None
@@ -498,6 +503,7 @@ def run_ours(args):
         "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(us_step / 1000.0, 6), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 weights, f16 x f16 -> f32 mma", "data": "synthetic",
+        "data_sha256": data_sha256,
         "config": {"workload": HEAD, "rows": m, "k": k, "n": n_total, "weight_bytes": total_bytes,
                    "parallelism": f"vocab-sharded x{world}" if world > 1 else "single GPU",
                    "l2": "inputs larger than L2 (437.6 MB of weights per step" +

@@ -2356,11 +2356,14 @@ int QueryMaxActiveClusters(int mode, int direct, int threads, size_t smem, int c
 
 // Raises the dynamic shared-memory limit of the kernels once per process.  Called from the
 // *_create entry points, i.e. outside any stream capture.
+int g_configured_device = -1;
+
 cudaError_t ConfigureSkinnyGemmKernels() {
   static std::once_flag once;
   static cudaError_t status = cudaSuccess;
   std::call_once(once, [] {
-    status = ConfigureDirect<kBf16>();
+    status = cudaGetDevice(&g_configured_device);
+    if (status == cudaSuccess) status = ConfigureDirect<kBf16>();
     if (status == cudaSuccess) status = ConfigureDirect<kFp8>();
     if (status == cudaSuccess) status = ConfigureDirect<kNvfp4>();
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRegKernel<kBf16>);
@@ -2376,6 +2379,11 @@ cudaError_t ConfigureSkinnyGemmKernels() {
 }
 
 cudaError_t LaunchSkinnyGemm(int mode, GemmParams& p, const Plan& plan, cudaStream_t stream) {
+  // The kernels' attributes (shared-memory limits, co-resident cluster counts, SM count) were set up for one
+  // device: one process drives one GPU, and a call with another device current is refused rather than launched
+  // with the wrong limits.
+  int dev = -1;
+  if (g_configured_device >= 0 && (cudaGetDevice(&dev) != cudaSuccess || dev != g_configured_device)) return cudaErrorInvalidDevice;
   const ModeGeom geom = GeomOf(mode, plan.direct ? plan.wide : 1);
   p.wn = plan.wn;
   p.wk = plan.wk;
