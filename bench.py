@@ -213,6 +213,43 @@ def bench_small_configs(torch, quick=False):
     return out
 
 
+def bench_model_shapes(torch):
+    """Shapes outside the benchmark's own five, taken from the launch table of the reference operator
+    (src/fused_gemm/fused_gemm.cu:132-156: the projections of a K = 2560 model) plus two NVFP4 ones: none of
+    them is in this build's tuned table, so the scoring rule of the planner picks their launch shapes.  One row,
+    device time per call under buffer rotation, the reference's kernel (generic configuration) beside it."""
+    from qwen38_flash_ops_b200 import SkinnyGemm
+    from qwen38_flash_ops_b200 import workloads as W
+
+    ref = _ref_util()
+    shapes = [(W.MODE_BF16, 2560, 16480), (W.MODE_BF16, 2560, 12800), (W.MODE_BF16, 2560, 1792), (W.MODE_BF16, 6144, 2560),
+              (W.MODE_BF16, 640, 2560), (W.MODE_BF16, 10240, 320), (W.MODE_BF16, 320, 10240),
+              (W.MODE_FP8, 2560, 16480), (W.MODE_FP8, 2560, 2560), (W.MODE_FP8, 6144, 2560),
+              (W.MODE_NVFP4, 2560, 12800), (W.MODE_NVFP4, 6144, 2560)]
+    names = {W.MODE_BF16: "bf16", W.MODE_FP8: "fp8", W.MODE_NVFP4: "nvfp4"}
+    bpc = {W.MODE_BF16: 2.0, W.MODE_FP8: 1.0, W.MODE_NVFP4: 0.5625}
+    out = {}
+    for mode, k, n in shapes:
+        nbytes = int(k * n * bpc[mode])
+        copies = max(4, min(48, (1 << 30) // nbytes))
+        made = [W.make_weight(mode, k, n, seed=300 + c) for c in range(copies)]
+        ws = [w for (w, _) in made]
+        scales = made[0][1].cpu().numpy() if mode == W.MODE_FP8 else None
+        x = W.make_x(1, k, seed=7)
+        op = SkinnyGemm([1], [n], w_scale=scales)
+        outs = [torch.empty((1, n), dtype=torch.bfloat16, device="cuda")]
+        med, best = time_graph_rotation(torch, lambda i: op(x, ws[i], out=outs), copies)
+        line = {"weight_bytes": nbytes, "us": round(med, 3), "GBps": round(nbytes / med / 1e3, 1), "plan": op.describe(k, ws[0])}
+        if ref is not None:
+            sc_dev = [made[0][1]] if mode == W.MODE_FP8 else [None]
+            rmed, _ = time_graph_rotation(torch, lambda i: ref.ref_skinny_gemm(x, [ws[i]], [mode], [n], sc_dev, [1], [n]), copies)
+            line["reference_kernel_sm100a_us"] = round(rmed, 3)
+        out[f"{names[mode]}_{k}x{n}"] = line
+        del made, ws
+        torch.cuda.empty_cache()
+    return out
+
+
 def read_ceiling(torch):
     """GB/s of a read-only sweep (128-bit loads, nothing written) over 2 GiB, 16x L2: the streaming ceiling
     a weight stream is compared with, besides the copy bandwidth."""
@@ -543,6 +580,8 @@ def run_ours(args):
     if world == 1 and not args.headline_only:
         line["all_configs"] = bench_small_configs(torch, quick=args.quick)
         line["all_configs"].update(bench_argmax_and_dequant(torch))
+        if not args.quick:
+            line["all_configs"]["model_shapes_scored_planner"] = bench_model_shapes(torch)
         per_m = {}
         for mm in (1, 2, 4):
             xm = W.make_x(mm, k, seed=7)
