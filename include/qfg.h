@@ -256,8 +256,11 @@ QFG_API int qfg_lmhead_exchange_times(const void* own_buffer, uint64_t out[3]);
  * `x_host` (pinned, device-addressable, BF16 [m, k]) to `x_dev`, and the fused kernel as its programmatic
  * dependent (it streams its first weight tiles while x crosses the host link), which stores the winners
  * straight into `idx_host` / `val_host` (pinned, device-addressable; val_host may be null).  qfg_lmhead_host_run
- * launches the graph and waits for it: one call per decode step, after which idx_host / val_host hold
- * the result.  `exchange` is null on one GPU, or the peer-memory exchange of the sharded head, in which
+ * launches the graph and returns as soon as the results are in idx_host / val_host: it marks those words
+ * with values the kernel never stores and reads them until all have changed (bounded; past 20 ms, or on an
+ * error, it synchronises the stream instead), so the call does not pay for the stream to drain and the
+ * synchronising thread to be woken.  One call per decode step; the private stream may still be finishing
+ * when the call returns, which the next call and qfg_lmhead_host_destroy order themselves after.  `exchange` is null on one GPU, or the peer-memory exchange of the sharded head, in which
  * case every rank must create and run in step with the others.  create runs the step once before it
  * records it, so the workspace header must be zero at that point, as for qfg_lmhead_compute. */
 typedef struct qfg_lmhead_host qfg_lmhead_host;

@@ -6,6 +6,8 @@
 // entry points neither allocate nor copy, so they are legal inside a stream capture.
 #include <cuda_runtime.h>
 
+#include <chrono>
+
 #include <climits>
 #include <cstdio>
 #include <cstdlib>
@@ -776,7 +778,17 @@ struct qfg_lmhead_host {
   cudaGraphExec_t exec = nullptr;
   qfg_lmhead op;  // the caller's node with pdl_wait set (shares, and does not own, its w_scale)
   unsigned int* status_host = nullptr;  // pinned, device-addressable: 1 if the step's wait for a peer ran out
+  // where the kernel stores the step's results (pinned host memory): polled by qfg_lmhead_host_run
+  int64_t rows = 0;
+  volatile int64_t* idx_host = nullptr;
+  volatile uint32_t* val_host = nullptr;
 };
+
+// Values the kernel never stores: an index of -1, and a float whose low 16 bits are set (the maximum is a BF16
+// logit widened to FP32, or the canonical NaN, so its low half is zero); the status word is 0 or 1.
+constexpr int64_t kIdxSentinel = -1;
+constexpr uint32_t kValSentinel = 0xFFC0DEADu;
+constexpr unsigned int kStatusSentinel = 0xFFFFFFFFu;
 
 
 int qfg_lmhead_host_create(const qfg_lmhead* op, int64_t m, int64_t k, const qfg_tensor2d* weight, int64_t n,
@@ -790,6 +802,9 @@ int qfg_lmhead_host_create(const qfg_lmhead* op, int64_t m, int64_t k, const qfg
     return Fail(QFG_INVALID_ARGUMENT, "LmHead: x must be 4-byte aligned with an even K");
   qfg_lmhead_host* h = new qfg_lmhead_host{nullptr, nullptr, nullptr, *op, nullptr};
   h->op.gemm.pdl_wait = 1;
+  h->rows = m;
+  h->idx_host = idx_host;
+  h->val_host = reinterpret_cast<volatile uint32_t*>(val_host);
   if (exchange != nullptr && exchange->world > 1) {
     // the sharded step reports a wait that ran out through one word of pinned memory, read after the synchronise
     if (cudaHostAlloc(reinterpret_cast<void**>(&h->status_host), sizeof(unsigned int), cudaHostAllocMapped) != cudaSuccess) {
@@ -834,16 +849,39 @@ int qfg_lmhead_host_create(const qfg_lmhead* op, int64_t m, int64_t k, const qfg
 
 int qfg_lmhead_host_run(qfg_lmhead_host* h) {
   if (h == nullptr || h->exec == nullptr) return Fail(QFG_INVALID_ARGUMENT, "LmHead: null host-step handle");
+  // The kernel's last CTA stores the results straight into pinned host memory.  The host marks every result
+  // word with a value the kernel never stores, launches, and reads the words until all have changed: the call
+  // returns when the results are there, not when the stream has drained and the synchronising thread has been
+  // woken (5-8 us later).  The wait is bounded; past the bound, and on any error, the stream is synchronised.
+  for (int64_t i = 0; i < h->rows; ++i) {
+    h->idx_host[i] = kIdxSentinel;
+    if (h->val_host != nullptr) h->val_host[i] = kValSentinel;
+  }
+  volatile unsigned int* status = h->status_host;
+  if (status != nullptr) *status = kStatusSentinel;
   cudaError_t err = cudaGraphLaunch(h->exec, h->stream);
-  if (err == cudaSuccess) err = cudaStreamSynchronize(h->stream);
   if (err != cudaSuccess) return Fail(QFG_FAIL, std::string("LmHead: ") + cudaGetErrorString(err));
-  if (h->status_host != nullptr && *h->status_host != 0)
+  bool there = false;
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(20);
+  for (unsigned spin = 0; !there; ++spin) {
+    there = status == nullptr || *status != kStatusSentinel;
+    for (int64_t i = 0; there && i < h->rows; ++i) {
+      there = h->idx_host[i] != kIdxSentinel && (h->val_host == nullptr || h->val_host[i] != kValSentinel);
+    }
+    if (!there && (spin & 1023u) == 1023u && std::chrono::steady_clock::now() > deadline) break;
+  }
+  if (!there) {
+    err = cudaStreamSynchronize(h->stream);
+    if (err != cudaSuccess) return Fail(QFG_FAIL, std::string("LmHead: ") + cudaGetErrorString(err));
+  }
+  if (status != nullptr && *status != 0)
     return Fail(QFG_FAIL, "LmHead: the wait for a peer's keys ran out; the result lacks that peer");
   return QFG_OK;
 }
 
 void qfg_lmhead_host_destroy(qfg_lmhead_host* h) {
   if (h == nullptr) return;
+  if (h->stream != nullptr) cudaStreamSynchronize(h->stream);  // a step may have returned before the stream drained
   if (h->status_host != nullptr) cudaFreeHost(h->status_host);
   if (h->exec != nullptr) cudaGraphExecDestroy(h->exec);
   if (h->graph != nullptr) cudaGraphDestroy(h->graph);
