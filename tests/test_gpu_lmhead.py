@@ -135,6 +135,7 @@ def test_lmhead_full_vocabulary(cuda, M):
         torch.cuda.synchronize()
         d = np.abs(bits(r).astype(np.int32) - bits(logits).astype(np.int32))
         assert np.mean(d <= 1) > 0.999
+        assert np.mean(d == 0) > 0.999  # observed: 0.9998 of the logits bit-identical to the reference kernel's
         assert _oracle_near_tie_ok(ridx.cpu().numpy(), sums, obits, oidx) == 0
 
 

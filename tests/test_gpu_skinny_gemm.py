@@ -310,6 +310,8 @@ def test_baseline_configs_full_size(cuda, name):
         for a, b in zip(outs, r):
             d = np.abs(bits(a).astype(np.int32) - bits(b).astype(np.int32))
             assert np.mean(d <= 1) > 0.999, f"{name}: differs from the reference kernel by more than one BF16 ULP"
+            # observed: 0.9995 - 0.99995 of the outputs bit-identical (different FP32 summation orders)
+            assert np.mean(d == 0) > 0.999, f"{name}: only {np.mean(d == 0):.5f} of the outputs equal the reference kernel's"
 
 
 def test_linearity_at_full_size(cuda):
