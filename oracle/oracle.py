@@ -16,7 +16,10 @@ project).  The restatement is pinned three ways:
     argmax_rows.cuh) compiled for sm_100a and run on a B200, stored as fixtures under
     tests/golden/ together with the script that generated them.
 NVFP4 and BF16 SkinnyGemm have no test in the reference; for those the compiled kernels and
-the cited source lines are the only pin.
+the cited source lines are the only pin.  DequantWeightBf16's kernel sits in the reference's ONNX
+Runtime translation unit, which cannot be compiled without ONNX Runtime: its FP8 arithmetic is pinned by
+the reference's own test formula, its NVFP4 arithmetic is PARITY UNPINNED by any reference output (held by
+the cited source lines and the ml_dtypes tables only).
 
 Conventions: BF16 / FP16 tensors travel as uint16 bit patterns, FP8 and packed NVFP4 as
 uint8.  A packed NVFP4 row of an [K, N] weight is N/2 nibble bytes (column 2b in the low
