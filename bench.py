@@ -250,6 +250,66 @@ def bench_model_shapes(torch):
     return out
 
 
+def bench_next_ops(torch):
+    """The two further ops of the domain: SharedExpertDown (K 640 -> N 2560 with a 2560-long gate, the shape class
+    the reference operator is tuned for: K <= 1024, rows 1 and 4; the reference's fused kernel beside it where it
+    was compiled) and UntileHcBf16 (its one fixed shape; bytes in + out per second)."""
+    import ctypes
+
+    from qwen38_flash_ops_b200 import SharedExpertDown, UntileHcBf16
+    from qwen38_flash_ops_b200 import workloads as W
+
+    peak, _ = peaks()
+    ref = _ref_util()
+    lib = ref.ref_lib() if ref is not None else None
+    if lib is not None and not hasattr(lib, "ref_shared_expert_down"):
+        lib = None
+    out = {"SharedExpertDown_640x2560_gate2560": {}, "UntileHcBf16_160x20480": {}}
+    k, n, gk = 640, 2560, 2560
+    names = {W.MODE_BF16: "bf16", W.MODE_FP8: "fp8", W.MODE_NVFP4: "nvfp4"}
+    gen = torch.Generator(device="cuda").manual_seed(11)
+
+    def bf16(*shape, scale=1.0):
+        return (torch.randn(*shape, generator=gen, device="cuda") * scale).to(torch.bfloat16)
+
+    for mode in (W.MODE_BF16, W.MODE_FP8, W.MODE_NVFP4):
+        copies = 48
+        made = [W.make_weight(mode, k, n, seed=500 + c) for c in range(copies)]
+        ws = [w for (w, _) in made]
+        scales = made[0][1] if mode == W.MODE_FP8 else None
+        op = SharedExpertDown(w_scale=scales.cpu().numpy() if scales is not None else None)
+        for m in (1, 4):
+            g, u, gx, routed = bf16(m, k), bf16(m, k), bf16(m, gk), bf16(m, n)
+            gw = bf16(gk, 1, scale=0.02)
+            med, _ = time_graph_rotation(torch, lambda i: op(g, u, ws[i], gx, gw, routed), copies)
+            line = {"us": round(med, 3)}
+            if lib is not None:
+                res = torch.empty_like(routed)
+                vp = ctypes.c_void_p
+
+                def ref_call(i):
+                    err = lib.ref_shared_expert_down(vp(g.data_ptr()), vp(u.data_ptr()), m, k, vp(ws[i].data_ptr()), mode, n,
+                                                     vp(scales.data_ptr() if scales is not None else None), vp(gx.data_ptr()), gk,
+                                                     vp(gw.data_ptr()), vp(routed.data_ptr()), vp(res.data_ptr()), 0,
+                                                     vp(torch.cuda.current_stream().cuda_stream))
+                    assert err == 0
+
+                rmed, _ = time_graph_rotation(torch, ref_call, copies)
+                line["reference_kernel_sm100a_us"] = round(rmed, 3)
+            out["SharedExpertDown_640x2560_gate2560"][f"{names[mode]}_M{m}"] = line
+        del made, ws
+        torch.cuda.empty_cache()
+    src = [bf16(160, 20480) for _ in range(24)]
+    for kind in (0, 1):
+        op = UntileHcBf16(kind)
+        dst = torch.empty((10240, 320) if kind == 0 else (320, 10240), dtype=torch.bfloat16, device="cuda")
+        med, _ = time_graph_rotation(torch, lambda i: op(src[i], out=dst), len(src))
+        nbytes = 2 * 160 * 20480 * 2
+        out["UntileHcBf16_160x20480"][f"kind{kind}"] = {"us": round(med, 3), "GBps": round(nbytes / med / 1e3, 1),
+                                                        "frac_of_measured_hbm": round(nbytes / med / 1e3 / peak, 4)}
+    return out
+
+
 def read_ceiling(torch):
     """GB/s of a read-only sweep (128-bit loads, nothing written) over 2 GiB, 16x L2: the streaming ceiling
     a weight stream is compared with, besides the copy bandwidth."""
@@ -582,6 +642,7 @@ def run_ours(args):
         line["all_configs"].update(bench_argmax_and_dequant(torch))
         if not args.quick:
             line["all_configs"]["model_shapes_scored_planner"] = bench_model_shapes(torch)
+            line["all_configs"].update(bench_next_ops(torch))
         per_m = {}
         for mm in (1, 2, 4):
             xm = W.make_x(mm, k, seed=7)

@@ -172,6 +172,8 @@ QFG_API int qfg_shared_expert_down_create(const float* w_scale, size_t n_w_scale
 QFG_API int qfg_shared_expert_down_compute(const qfg_shared_expert_down* op, const void* g, const void* u, int64_t m,
                                            int64_t k, const qfg_tensor2d* weight, const void* gx, int64_t gk,
                                            const void* gw, const void* routed, int64_t n, void* out, void* stream);
+/* The launch options of qfg_skinny_gemm_set_option ("plan", "pdl_wait", ...) for this node. */
+QFG_API int qfg_shared_expert_down_set_option(qfg_shared_expert_down* op, const char* key, const char* value);
 QFG_API void qfg_shared_expert_down_destroy(qfg_shared_expert_down* op);
 
 /* ---------------------------------------------------------------- UntileHcBf16

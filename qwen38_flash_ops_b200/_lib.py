@@ -24,7 +24,8 @@ EXPORTS = (
     "qfg_argmax_rows",
     "qfg_dequant_create", "qfg_dequant_compute", "qfg_dequant_destroy",
     "qfg_untile_hc_create", "qfg_untile_hc_compute", "qfg_untile_hc_destroy",
-    "qfg_shared_expert_down_create", "qfg_shared_expert_down_compute", "qfg_shared_expert_down_destroy",
+    "qfg_shared_expert_down_create", "qfg_shared_expert_down_compute", "qfg_shared_expert_down_set_option",
+    "qfg_shared_expert_down_destroy",
     "qfg_lmhead_workspace_bytes", "qfg_lmhead_create", "qfg_lmhead_compute", "qfg_lmhead_static_max_rows",
     "qfg_lmhead_compute_static", "qfg_lmhead_set_option",
     "qfg_lmhead_destroy", "qfg_lmhead_combine",
@@ -90,6 +91,7 @@ def load() -> ctypes.CDLL:
     lib.qfg_shared_expert_down_create.argtypes = [POINTER(c_float), c_size_t, c_int, POINTER(c_void_p)]
     lib.qfg_shared_expert_down_compute.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, POINTER(Tensor2D), c_void_p,
                                                    c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]
+    lib.qfg_shared_expert_down_set_option.argtypes = [c_void_p, c_char_p, c_char_p]
     lib.qfg_shared_expert_down_destroy.argtypes = [c_void_p]
     lib.qfg_shared_expert_down_destroy.restype = None
     lib.qfg_untile_hc_create.argtypes = [c_int, POINTER(c_float), c_size_t, POINTER(c_void_p)]

@@ -608,6 +608,11 @@ int qfg_shared_expert_down_compute(const qfg_shared_expert_down* op, const void*
   }
 }
 
+int qfg_shared_expert_down_set_option(qfg_shared_expert_down* op, const char* key, const char* value) {
+  if (op == nullptr) return Fail(QFG_INVALID_ARGUMENT, "SharedExpertDown: null node");
+  return SetGemmOption(&op->gemm, key, value);
+}
+
 void qfg_shared_expert_down_destroy(qfg_shared_expert_down* op) {
   if (op == nullptr) return;
   cudaFree(op->gemm.d_w_scale);

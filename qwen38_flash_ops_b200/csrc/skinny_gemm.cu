@@ -730,7 +730,7 @@ __device__ __noinline__ bool StageXFused(const GemmParams& p, const Tile& tl, ui
 }
 
 // Must be called by every thread of the CTA; sh.rmax / sh.rmin are initialised here.
-template <int MODE, bool TC = false, bool WALK = true>
+template <int MODE, bool TC = false, bool WALK = true, bool FUSE = false>
 __device__ __forceinline__ bool StageX(const GemmParams& p, const Tile& tl, uint16_t* xs, SharedScratch& sh) {
   if (threadIdx.x < kMaxRows) {
     sh.rmax[threadIdx.x] = 0;
@@ -738,7 +738,7 @@ __device__ __forceinline__ bool StageX(const GemmParams& p, const Tile& tl, uint
     sh.inv_scale[threadIdx.x] = 1.f;
   }
   __syncthreads();
-  if (p.fuse) return StageXFused<MODE, TC>(p, tl, xs, sh);
+  if constexpr (FUSE) return StageXFused<MODE, TC>(p, tl, xs, sh);
   const bool vec8 = (reinterpret_cast<uintptr_t>(p.x) % 16 == 0) && (p.K % 8 == 0);
   if (vec8) return StageXImpl<MODE, 4, TC, false, WALK>(p, tl, xs, sh);
   return StageXImpl<MODE, 1, TC, false, WALK>(p, tl, xs, sh);
@@ -754,7 +754,7 @@ __device__ __forceinline__ int RedCol(int c, int m) { return c ^ ((((c >> 5) & 3
 // [nparts][M][TNc] floats (part w = the sum over the k-steps of K-group w), the cluster partials
 // follow it.  Every thread of the CTA must call this after a __syncthreads() that follows the
 // last write to `red`.
-template <int MODE>
+template <int MODE, bool FUSE = false>
 __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl, uint8_t* smem, SharedScratch& sh,
                                              int nparts, int TNc) {
   const int tid = threadIdx.x, nthreads = blockDim.x;
@@ -772,14 +772,14 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
   long long cur_i = -1;
   // what every element needs from the parameter block, read once
   const float* const w_scale = sg.w_scale;
-  const bool fuse = p.fuse != 0, lm = p.lm != 0;
+  const bool lm = p.lm != 0;
   const int out_begin = sg.out_begin, out_end = sg.out_end;
   const bool store = !lm || p.out[out_begin] != nullptr;
   const long long col_offset = p.lm_col_offset;
   auto finalize = [&](int m, int c, float v) {
     const int n = n0 + c;
     if (w_scale != nullptr) v *= w_scale[n];
-    if (fuse) {
+    if constexpr (FUSE) {
       // SharedExpertDown: routed + bf16(bf16(sum) * gate), every step rounded to BF16 (skinny_gemm.cuh:226-240)
       const float shared = RoundBf16(RoundBf16(v) * sh.gate[m]);
       v = p.routed != nullptr ? __uint_as_float(static_cast<uint32_t>(p.routed[static_cast<size_t>(m) * sg.n + n]) << 16) + shared
@@ -996,7 +996,7 @@ __device__ __forceinline__ void EpilogueTail(const GemmParams& p, const Tile& tl
 // Reduction of the accumulators (wk warps, then the cluster), scaling, rounding, stores, and the
 // fused argmax.  `smem` is reused for the partial sums; every thread of the CTA must call this
 // after a __syncthreads() that ends all use of the shared memory by the main loop.
-template <int MODE, int W = 1>
+template <int MODE, int W = 1, bool FUSE = false>
 __device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, float (&acc)[Geom<MODE, W>::kMmas][4],
                                          uint8_t* smem, SharedScratch& sh, bool warp_has_cols) {
   using G = Geom<MODE, W>;
@@ -1025,7 +1025,7 @@ __device__ __forceinline__ void Epilogue(const GemmParams& p, const Tile& tl, fl
       for (int c = lane; c < cols_per_warp; c += 32) red[(wk * M + m) * TNc + wn * cols_per_warp + c] = 0.f;
   }
   __syncthreads();
-  EpilogueTail<MODE>(p, tl, smem, sh, p.wk, TNc);
+  EpilogueTail<MODE, FUSE>(p, tl, smem, sh, p.wk, TNc);
 }
 
 // ------------------------------------------------------------------------------ direct kernel
@@ -1421,7 +1421,10 @@ struct WarpRing {
 };
 
 // DEPTH: pairs of k-steps in every warp's ring (2, 3 or 4)
-template <int MODE, int DEPTH>
+// FUSE: the SharedExpertDown form (x = swish_mul(g, u) and the gate while x is staged, the gated rounding chain
+// in the epilogue).  A kernel of its own, so that the plain kernels carry none of that code: they were measured
+// to lose 2-3 % whenever it changed, run or not.
+template <int MODE, int DEPTH, bool FUSE = false>
 __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const __grid_constant__ GemmParams p) {
   using G = Geom<MODE, 1>;
   using S = RingSlot<MODE>;
@@ -1474,7 +1477,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const _
 
   // x first (unless it is still the predecessor kernel's to write): its copies then do not queue behind the weights
   uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
-  const bool x_async = !p.fuse && XRowsAre16ByteAligned(p);
+  const bool x_async = !FUSE && XRowsAre16ByteAligned(p);
   if (x_async && !p.pdl_wait) {
     XCopyIssue(p, tl, xs);
     CpAsyncCommit();
@@ -1498,7 +1501,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const _
     }
     slow = StageXConvert<MODE>(p, tl, xs, sh);
   } else {
-    slow = StageX<MODE>(p, tl, xs, sh);
+    slow = StageX<MODE, false, true, FUSE>(p, tl, xs, sh);
   }
   Stamp(p, 2);
 
@@ -1550,7 +1553,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const _
   if (p.trigger == 2) GridLaunchDependents();
   __syncthreads();
   Stamp(p, 4);
-  Epilogue<MODE, 1>(p, tl, acc, smem, sh, warp_has_cols);
+  Epilogue<MODE, 1, FUSE>(p, tl, acc, smem, sh, warp_has_cols);
   Stamp(p, 5);
 }
 
@@ -1562,7 +1565,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmDirectKernel(const _
 // than the deeper prefetch of the warp rings; on long streams the rings win.
 constexpr int kRegThreads = 512;
 
-template <int MODE>
+template <int MODE, bool FUSE = false>
 __global__ void __launch_bounds__(kRegThreads, 1) SkinnyGemmRegKernel(const __grid_constant__ GemmParams p) {
   using G = Geom<MODE>;
   constexpr int NM = G::kMmas;
@@ -1649,7 +1652,7 @@ __global__ void __launch_bounds__(kRegThreads, 1) SkinnyGemmRegKernel(const __gr
 
   // x first (unless it is still the predecessor kernel's to write): its copies then do not queue behind the weights
   uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
-  const bool x_async = !p.fuse && XRowsAre16ByteAligned(p);
+  const bool x_async = !FUSE && XRowsAre16ByteAligned(p);
   if (x_async && !p.pdl_wait) {
     XCopyIssue(p, tl, xs);
     CpAsyncCommit();
@@ -1672,7 +1675,7 @@ __global__ void __launch_bounds__(kRegThreads, 1) SkinnyGemmRegKernel(const __gr
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     slow = StageXConvert<MODE>(p, tl, xs, sh);
   } else {
-    slow = StageX<MODE, false, false>(p, tl, xs, sh);
+    slow = StageX<MODE, false, false, FUSE>(p, tl, xs, sh);
   }
   Stamp(p, 2);
 
@@ -1714,7 +1717,7 @@ __global__ void __launch_bounds__(kRegThreads, 1) SkinnyGemmRegKernel(const __gr
   if (p.trigger == 2) GridLaunchDependents();
   __syncthreads();
   Stamp(p, 4);
-  Epilogue<MODE>(p, tl, acc, smem, sh, warp_has_cols);
+  Epilogue<MODE, 1, FUSE>(p, tl, acc, smem, sh, warp_has_cols);
   Stamp(p, 5);
 }
 
@@ -1869,7 +1872,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const __gri
   Stamp(p, 1);
 
   uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
-  const bool slow = StageX<kNvfp4, true>(p, tl, xs, sh);
+  const bool slow = p.fuse ? StageX<kNvfp4, true, true, true>(p, tl, xs, sh) : StageX<kNvfp4, true>(p, tl, xs, sh);
   TcFenceBefore();
   __syncthreads();
   TcFenceAfter();
@@ -2028,7 +2031,11 @@ __global__ void __launch_bounds__(kMaxThreads, 1) SkinnyGemmTcKernel(const __gri
   if (is_issuer) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(alloc_cols) : "memory");
   }
-  EpilogueTail<kNvfp4>(p, tl, smem, sh, p.wk, TNc);
+  if (p.fuse) {
+    EpilogueTail<kNvfp4, true>(p, tl, smem, sh, p.wk, TNc);
+  } else {
+    EpilogueTail<kNvfp4>(p, tl, smem, sh, p.wk, TNc);
+  }
   Stamp(p, 5);
 }
 
@@ -2133,7 +2140,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) SkinnyGemmRingKernel(const __
   if (p.pdl_wait) GridDependencyWait();
 
   uint16_t* xs = reinterpret_cast<uint16_t*>(smem + p.ring_bytes);
-  const bool slow = StageX<MODE>(p, tl, xs, sh);
+  const bool slow = p.fuse ? StageX<MODE, false, true, true>(p, tl, xs, sh) : StageX<MODE>(p, tl, xs, sh);
 
   float acc[NM][4];
 #pragma unroll
@@ -2203,7 +2210,11 @@ __global__ void __launch_bounds__(kRingThreads, 2) SkinnyGemmRingKernel(const __
   CpAsyncWait(0);
   if (p.trigger == 2) GridLaunchDependents();
   __syncthreads();
-  Epilogue<MODE>(p, tl, acc, smem, sh, warp_has_cols);
+  if (p.fuse) {
+    Epilogue<MODE, 1, true>(p, tl, acc, smem, sh, warp_has_cols);
+  } else {
+    Epilogue<MODE>(p, tl, acc, smem, sh, warp_has_cols);
+  }
 }
 
 // Largest dynamic shared-memory request any of the kernels accepts: the opt-in limit of the
@@ -2230,12 +2241,23 @@ cudaError_t ConfigureDirect() {
   cudaError_t err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 2>);
   if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 3>);
   if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 4>);
+  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 2, true>);
+  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 3, true>);
+  if (err == cudaSuccess) err = ConfigureKernel(SkinnyGemmDirectKernel<MODE, 4, true>);
   return err;
 }
 
 // the direct kernel is compiled for rings of 4, 6 and 8 k-steps (2, 3, 4 pairs)
 template <int MODE>
 cudaError_t LaunchDirect(const cudaLaunchConfig_t* cfg, int stages, const GemmParams& p) {
+  if (p.fuse) {
+    switch (stages) {
+      case 4: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 2, true>, p);
+      case 6: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 3, true>, p);
+      case 8: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 4, true>, p);
+      default: return cudaErrorInvalidValue;
+    }
+  }
   switch (stages) {
     case 4: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 2>, p);
     case 6: return cudaLaunchKernelEx(cfg, SkinnyGemmDirectKernel<MODE, 3>, p);
@@ -2269,7 +2291,9 @@ cudaError_t LaunchMode(const GemmParams& p, const Plan& plan, size_t smem, cudaS
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
   if constexpr (MODE != kNvfp4) {
-    if (plan.direct == 2) return cudaLaunchKernelEx(&cfg, SkinnyGemmRegKernel<MODE>, p);
+    if (plan.direct == 2) {
+      return p.fuse ? cudaLaunchKernelEx(&cfg, SkinnyGemmRegKernel<MODE, true>, p) : cudaLaunchKernelEx(&cfg, SkinnyGemmRegKernel<MODE>, p);
+    }
   }
   if (plan.direct) {
     if constexpr (MODE == kNvfp4) {
@@ -2368,6 +2392,8 @@ cudaError_t ConfigureSkinnyGemmKernels() {
     if (status == cudaSuccess) status = ConfigureDirect<kNvfp4>();
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRegKernel<kBf16>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRegKernel<kFp8>);
+    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRegKernel<kBf16, true>);
+    if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmRegKernel<kFp8, true>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmTcKernel<3>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmTcKernel<4>);
     if (status == cudaSuccess) status = ConfigureKernel(SkinnyGemmTcKernel<6>);

@@ -176,6 +176,9 @@ class SharedExpertDown:
             keep, ptr, n = None, None, 0
         check(lib.qfg_shared_expert_down_create(ptr, n, int(trigger), ctypes.byref(self._h)))
 
+    def set_option(self, key: str, value) -> None:
+        check(self._lib.qfg_shared_expert_down_set_option(self._h, key.encode(), str(value).encode()))
+
     def __call__(self, g, u, w, gx, gw, routed):
         for name, t in (("g", g), ("u", u), ("gx", gx), ("gw", gw), ("routed", routed)):
             _require_cuda(t, name)
@@ -227,7 +230,10 @@ class UntileHcBf16:
         _require_cuda(w, "w")
         t = _tensor2d(w)
         shape = (10240, 320) if self.kind == 0 else (320, 10240)
-        out = torch.empty(shape, dtype=torch.bfloat16, device=w.device)
+        if out is None:
+            out = torch.empty(shape, dtype=torch.bfloat16, device=w.device)
+        elif tuple(out.shape) != shape or out.dtype != torch.bfloat16 or not out.is_contiguous():
+            raise QfgError(_lib.QFG_INVALID_ARGUMENT, "UntileHcBf16: out must be a contiguous BF16 tensor of the untiled shape")
         check(self._lib.qfg_untile_hc_compute(self._h, ctypes.byref(t), out.data_ptr(), _stream_ptr()))
         return out
 
