@@ -211,6 +211,13 @@ Plan ChoosePlan(const PlanInput& in) {
     while (cluster < 8 && natural_tiles * cluster < in.sm_count * 7 / 8) cluster *= 2;
     int wk = (in.mode == kFp8 && cluster == 1) ? 16 : 8;
     while (cluster > 1 && ksteps < 2 * cluster * wk) cluster /= 2;
+    // short K (32 to 64 k-steps, the SharedExpertDown class): the whole call is fixed phases, and a cluster
+    // epilogue costs more than the idle SMs (640 x 2560: 5.6 us with sixteen warps and no cluster, 6.5 with two CTAs
+    // per column tile; SharedExpertDown 8.4 against 10.3 us)
+    if (ksteps >= 32 && ksteps <= 64) {
+      cluster = 1;
+      wk = 16;
+    }
     char spec[96];
     std::snprintf(spec, sizeof(spec), "direct=2,wn=1,wk=%d,cluster=%d,waves=1", wk, cluster);
     Plan streaming;
